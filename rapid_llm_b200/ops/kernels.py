@@ -1,0 +1,335 @@
+"""Python entry points of the CUDA kernels: tensors in, launches on the current stream.
+
+Each function checks shapes, dtypes and devices, then calls the ``extern "C"`` launcher
+with raw pointers.  Nothing here has a CPU or library fallback: a tensor that is not on a
+CUDA device, or an extension that cannot be built, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+
+FAULT_BITS = {
+    1: "a token id outside the vocabulary",
+    2: "a page id outside the cache pool",
+    4: "a position outside the rotary table or block table",
+    8: "a slot outside the block table",
+    16: "a bounded wait inside a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    """A launch was refused (bad size or argument) or failed."""
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+def _ptr(tensor: torch.Tensor | None) -> c_void_p:
+    if tensor is None:
+        return c_void_p(0)
+    return c_void_p(tensor.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor | None) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError(
+                "kernel arguments must live on a CUDA device; there is no CPU path "
+                f"(got a tensor on {tensor.device})"
+            )
+
+
+def _contig(name: str, tensor: torch.Tensor | None) -> None:
+    if tensor is not None and not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _expect(name: str, tensor: torch.Tensor | None, dtype: torch.dtype) -> None:
+    if tensor is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+
+
+_CUDA_ERRORS = {1: "invalid value (a size or argument the kernel refuses)"}
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        detail = _CUDA_ERRORS.get(code, f"CUDA error {code}")
+        raise KernelError(f"{what}: {detail}")
+
+
+_SIGNATURES_SET = False
+
+
+def core() -> ctypes.CDLL:
+    """The core kernel library, with argument types declared once."""
+    global _SIGNATURES_SET
+    lib = load_library("core")
+    if not _SIGNATURES_SET:
+        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+        lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_void_p]
+        lib.rl_qk_norm_rope_write.argtypes = [
+            c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_float, c_void_p, c_void_p,
+        ]
+        lib.rl_attention_generic.argtypes = [
+            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+        ]
+        lib.rl_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rl_sample.argtypes = [
+            c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+        for name in (
+            "rl_embedding", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
+            "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
+        ):
+            getattr(lib, name).restype = c_int
+        _SIGNATURES_SET = True
+    return lib
+
+
+# --------------------------------------------------------------------------- ops
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: torch.Tensor) -> torch.Tensor:
+    """``out[t] = table[ids[t]]``; ``ids`` int32 ``[T]``; bad ids set the fault word."""
+    _need_cuda(out, table, ids, fault)
+    _expect("ids", ids, torch.int32)
+    _contig("out", out), _contig("table", table), _contig("ids", ids)
+    if out.dtype != table.dtype or out.shape != (ids.numel(), table.shape[1]):
+        raise KernelError(f"embedding: out {tuple(out.shape)} {out.dtype} does not fit table {tuple(table.shape)} {table.dtype}")
+    _check(
+        core().rl_embedding(dtype_tag(table.dtype), _ptr(out), _ptr(table), _ptr(ids), ids.numel(),
+                            table.shape[1], table.shape[0], _ptr(fault), _stream()),
+        "embedding",
+    )
+    return out
+
+
+def add_rmsnorm(
+    x: torch.Tensor,
+    residual: torch.Tensor | None,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    eps: float,
+    *,
+    mode: int,
+    write_residual: bool,
+    row_index: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """RMSNorm of ``x`` (mode 0 or 2) or of ``x + residual`` (mode 1), float32 math.
+
+    ``residual`` is the float32 residual stream ``[T, H]``; with ``write_residual`` the
+    sum is stored back into it.  ``row_index`` (int32) selects the input rows; ``out`` then
+    has one row per index.
+    """
+    _need_cuda(x, residual, weight, out, row_index)
+    _expect("weight", weight, torch.float32), _expect("residual", residual, torch.float32)
+    _expect("row_index", row_index, torch.int32)
+    _contig("x", x), _contig("residual", residual), _contig("out", out)
+    hidden = x.shape[-1]
+    rows = row_index.numel() if row_index is not None else x.shape[0]
+    if weight.numel() != hidden or out.shape != (rows, hidden) or out.dtype != x.dtype:
+        raise KernelError("add_rmsnorm: shapes of x, weight and out do not agree")
+    if residual is not None and residual.shape != x.shape:
+        raise KernelError("add_rmsnorm: residual must have the shape of x")
+    _check(
+        core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out),
+                              _ptr(row_index), rows, hidden, float(eps), mode, int(write_residual), _stream()),
+        f"add_rmsnorm(hidden={hidden})",
+    )
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    _need_cuda(gate_up, out)
+    _contig("gate_up", gate_up), _contig("out", out)
+    rows, width = gate_up.shape
+    if width % 2 or out.shape != (rows, width // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("silu_mul: out must be [rows, width / 2] of the input's dtype")
+    _check(core().rl_silu_mul(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), rows, width // 2, _stream()), "silu_mul")
+    return out
+
+
+def to_float(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need_cuda(src, out)
+    _contig("src", src), _contig("out", out)
+    _expect("out", out, torch.float32)
+    if out.numel() != src.numel():
+        raise KernelError("to_float: sizes differ")
+    _check(core().rl_to_float(dtype_tag(src.dtype), _ptr(src), _ptr(out), src.numel(), _stream()), "to_float")
+    return out
+
+
+def qk_norm_rope_write(
+    qkv: torch.Tensor,
+    q_out: torch.Tensor,
+    *,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rotary_dim: int,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    positions: torch.Tensor,
+    eps: float,
+    fault: torch.Tensor,
+    q_weight: torch.Tensor | None = None,
+    k_weight: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
+    kv_dest: torch.Tensor | None = None,
+    cache: torch.Tensor | None = None,
+    page_size: int = 1,
+) -> torch.Tensor:
+    """Per-head q/k RMSNorm, rotation by position, q to ``q_out``, k and v into the pages.
+
+    ``qkv`` is ``[T, (Hq + 2 Hkv) D]`` (or ``[T, Hq D]`` when ``kv_dest`` is ``None`` and
+    only queries are produced).  ``cache`` is one layer's ``[pages, 2, Hkv, page, D]``;
+    ``kv_dest[t] = page * page_size + offset``.
+    """
+    _need_cuda(qkv, q_out, cos, sin, positions, fault, q_weight, k_weight, bias, kv_dest, cache)
+    _contig("qkv", qkv), _contig("q_out", q_out), _contig("cache", cache)
+    _contig("cos", cos), _contig("sin", sin)
+    for name, tensor in (("cos", cos), ("sin", sin), ("q_weight", q_weight), ("k_weight", k_weight), ("bias", bias)):
+        _expect(name, tensor, torch.float32)
+    _expect("positions", positions, torch.int32), _expect("kv_dest", kv_dest, torch.int32)
+    tokens, row_width = qkv.shape
+    heads_in = num_heads + 2 * num_kv_heads if kv_dest is not None else num_heads
+    if row_width != heads_in * head_dim:
+        raise KernelError(f"qk_norm_rope_write: qkv width {row_width} is not {heads_in} heads of {head_dim}")
+    if q_out.numel() != tokens * num_heads * head_dim or q_out.dtype != qkv.dtype:
+        raise KernelError("qk_norm_rope_write: q_out does not fit")
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] * 2 != rotary_dim:
+        raise KernelError("qk_norm_rope_write: cos/sin must be [positions, rotary_dim / 2]")
+    num_pages = 0
+    if kv_dest is not None:
+        if cache is None or cache.dtype != qkv.dtype or cache.shape[1:] != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError("qk_norm_rope_write: cache must be [pages, 2, kv_heads, page_size, head_dim] of qkv's dtype")
+        num_pages = cache.shape[0]
+    _check(
+        core().rl_qk_norm_rope_write(
+            dtype_tag(qkv.dtype), _ptr(qkv), row_width, _ptr(bias), _ptr(q_weight), _ptr(k_weight),
+            _ptr(cos), _ptr(sin), _ptr(positions), _ptr(kv_dest), _ptr(q_out), _ptr(cache), tokens,
+            num_heads, num_kv_heads, head_dim, rotary_dim, cos.shape[0], page_size, num_pages,
+            float(eps), _ptr(fault), _stream(),
+        ),
+        f"qk_norm_rope_write(head_dim={head_dim})",
+    )
+    return q_out
+
+
+def attention_generic(
+    q: torch.Tensor,
+    cache: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    token_slot: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    window: int,
+    scale: float,
+    fault: torch.Tensor,
+) -> torch.Tensor:
+    """Causal attention of every token of the step over its request's cached keys."""
+    _need_cuda(q, cache, out, positions, token_slot, block_table, fault)
+    _contig("q", q), _contig("cache", cache), _contig("out", out), _contig("block_table", block_table)
+    for name, tensor in (("positions", positions), ("token_slot", token_slot), ("block_table", block_table)):
+        _expect(name, tensor, torch.int32)
+    tokens = positions.numel()
+    if q.numel() != tokens * num_heads * head_dim or out.numel() != q.numel():
+        raise KernelError("attention: q/out do not hold [tokens, heads, head_dim]")
+    if cache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, cache and out must share a dtype")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+    _check(
+        core().rl_attention_generic(
+            dtype_tag(q.dtype), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(token_slot),
+            _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3],
+            cache.shape[0], block_table.shape[1], block_table.shape[0], int(window), float(scale),
+            _ptr(fault), _stream(),
+        ),
+        f"attention_generic(head_dim={head_dim})",
+    )
+    return out
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ w[N, K]^T`` in true float32."""
+    _need_cuda(a, w, out, bias)
+    for name, tensor in (("a", a), ("w", w), ("out", out), ("bias", bias)):
+        _expect(name, tensor, torch.float32)
+    _contig("w", w)
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or out.shape != (a.shape[0], w.shape[0]):
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_f32: rows of a and out must be contiguous")
+    _check(
+        core().rl_gemm_f32(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), a.shape[0], w.shape[0], a.shape[1],
+                           a.stride(0), out.stride(0), _stream()),
+        "gemm_f32",
+    )
+    return out
+
+
+def sample(
+    logits: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    temperature: torch.Tensor | None = None,
+    top_p: torch.Tensor | None = None,
+    penalty: torch.Tensor | None = None,
+    seeds: torch.Tensor | None = None,
+    counters: torch.Tensor | None = None,
+    seen_tokens: torch.Tensor | None = None,
+    seen_offsets: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """One token per row of ``logits`` into ``out`` (int32); no ``temperature`` = greedy."""
+    _need_cuda(logits, out, temperature, top_p, penalty, seeds, counters, seen_tokens, seen_offsets)
+    _expect("out", out, torch.int32)
+    for name, tensor in (("temperature", temperature), ("top_p", top_p), ("penalty", penalty)):
+        _expect(name, tensor, torch.float32)
+    _expect("seeds", seeds, torch.int64), _expect("counters", counters, torch.int32)
+    _expect("seen_tokens", seen_tokens, torch.int32), _expect("seen_offsets", seen_offsets, torch.int32)
+    if logits.dim() != 2 or logits.stride(1) != 1 or out.numel() != logits.shape[0]:
+        raise KernelError("sample: logits must be [rows, vocab] with contiguous rows and out [rows]")
+    _check(
+        core().rl_sample(
+            dtype_tag(logits.dtype), _ptr(logits), logits.shape[0], logits.shape[1], logits.stride(0),
+            _ptr(temperature), _ptr(top_p), _ptr(penalty), _ptr(seeds), _ptr(counters),
+            _ptr(seen_tokens), _ptr(seen_offsets), _ptr(out), _stream(),
+        ),
+        f"sample(vocab={logits.shape[1]})",
+    )
+    return out
+
+
+def describe_fault(word: int) -> str:
+    parts = [text for bit, text in FAULT_BITS.items() if word & bit]
+    return "; ".join(parts) if parts else "no fault"

@@ -1,0 +1,184 @@
+"""Interfaces and registries of the parts a layer is put together from.
+
+A part is built from a :class:`~rapid_llm_b200.config.model_spec.PartSpec`: its class is
+looked up by kind in the registry of its role and constructed with the spec's parameters
+plus ``dtype`` and ``device``.  A part owns its weights, names them relative to its own
+checkpoint prefix, and never learns which model it is in.  The reference reaches the same
+seam through factory methods and class flags on the model skeleton
+(``rapid_llm/models/base.py:393-404,449-478``).
+
+Roles and what each must provide:
+
+* **Mixer** — ``forward(x, batch, cache) -> y`` over the packed tokens of a step;
+  ``cache_need()`` says which pages it wants (all keys, a window of them, none) and
+  ``state_need()`` which per-request state of fixed size.
+* **FeedForward** — ``forward(x, batch) -> y``.
+* **Norm** — ``forward(x, residual, batch, mode, ...) -> normed``; the residual stream is a
+  float32 buffer the norm adds into.
+* **PositionEncoding** — ``tables() -> (cos, sin)`` float32 ``[positions, rotary_dim / 2]``.
+* **Block** (arrangement) — ``forward(x, residual, batch, cache) -> (x, residual)``; builds
+  its mixer, feed-forward and norms from the layer's specification.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+
+from ..config.model_spec import PartSpec
+
+MATRIX = "matrix"   # operand of a matrix product: kept in the engine dtype
+VECTOR = "vector"   # scale or bias vector: kept in float32 (a 16-bit value widens exactly)
+TABLE = "table"     # integer table: kept in int32
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """One checkpoint tensor a part expects.
+
+    Attributes:
+        shape: Shape in the checkpoint.
+        kind: :data:`MATRIX`, :data:`VECTOR` or :data:`TABLE`; decides the dtype it is kept in.
+        init: How the random-weights mode draws it: ``"normal"`` is N(0, std),
+            ``"ones_normal"`` is 1 + N(0, std), ``"zeros"``.
+        optional: May be absent from the checkpoint (the part then has a rule for it).
+    """
+
+    shape: tuple[int, ...]
+    kind: str = MATRIX
+    init: str = "normal"
+    optional: bool = False
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """Pages a mixer wants: ``kind`` is ``"full"`` (all keys) or ``"window"``."""
+
+    kind: str
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+    def group_key(self) -> tuple:
+        return (self.kind, self.window, self.num_kv_heads, self.head_dim)
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size: one ``shape`` tensor of ``dtype`` per slot."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype
+
+
+class Part:
+    """Base of every part: construction parameters and weights by checkpoint name."""
+
+    def __init__(self, *, dtype: torch.dtype, device: torch.device | str) -> None:
+        self.dtype = dtype
+        self.device = torch.device(device)
+
+    # -- weights ------------------------------------------------------------ #
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        """Checkpoint tensors of this part, named relative to its prefix."""
+        return {}
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        """Place one checkpoint tensor (already shape-checked) into device storage."""
+        raise KeyError(name)
+
+    def finalize(self, loaded: set[str]) -> None:
+        """Called once after loading, with the names that were present."""
+
+    def parameter_bytes(self) -> int:
+        return 0
+
+    # -- helpers ------------------------------------------------------------ #
+    def storage_dtype(self, kind: str) -> torch.dtype:
+        if kind == MATRIX:
+            return self.dtype
+        if kind == VECTOR:
+            return torch.float32
+        if kind == TABLE:
+            return torch.int32
+        raise ValueError(f"unknown tensor kind {kind!r}")
+
+    def new_storage(self, shape: tuple[int, ...], kind: str) -> torch.Tensor:
+        return torch.zeros(shape, dtype=self.storage_dtype(kind), device=self.device)
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x, residual, batch, *, mode: int, write_residual: bool, row_index=None, name="normed"):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, x, residual, batch, cache):
+        raise NotImplementedError
+
+
+class Registry:
+    """Kind name -> class, for one role."""
+
+    def __init__(self, role: str) -> None:
+        self.role = role
+        self._classes: dict[str, type] = {}
+
+    def register(self, kind: str) -> Callable[[type], type]:
+        def decorator(cls: type) -> type:
+            self._classes[kind] = cls
+            return cls
+
+        return decorator
+
+    def get(self, kind: str) -> type:
+        try:
+            return self._classes[kind]
+        except KeyError:
+            raise ValueError(
+                f"no {self.role} registered as {kind!r}; known: {sorted(self._classes)}"
+            ) from None
+
+    def build(self, spec: PartSpec, **context: Any):
+        return self.get(spec.kind)(**dict(spec.params), **context)
+
+    def kinds(self) -> list[str]:
+        return sorted(self._classes)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
