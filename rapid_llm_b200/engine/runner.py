@@ -92,7 +92,9 @@ class ModelRunner:
         ]
         self._meta_flip = 0
         self._meta_device = torch.zeros(self._meta_capacity, dtype=torch.int32, device=self.device)
-        self.fault = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # word 0: the kernels' fault word; words 1..: the step's sampled tokens (one read brings both)
+        self.result = torch.zeros(config.max_num_seqs + 2, dtype=torch.int32, device=self.device)
+        self.fault = self.result[:1]
         self.steps_run = 0
         self.kernel_launches = 0
 

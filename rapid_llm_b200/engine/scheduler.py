@@ -1,0 +1,301 @@
+"""Continuous batching above the step function: admit, cut prompts, decode, finish, free.
+
+Each call of :meth:`Scheduler.step` plans ONE packed batch under a token budget: the next
+token of every request that is decoding, then the next portion of every prompt that is
+under way, then new admissions in arrival order; runs it; harvests the sampled tokens;
+finishes and frees.  The policy is the reference's (``rapid_llm/engine/batch_planner.py:
+462-523,579-666,683-698``), with the budget counted in real tokens instead of a padded
+rectangle, and one pass per step instead of up to three (``rapid_llm/engine/scheduler.py:964-988``).
+
+When pages run out:
+
+* a waiting request stays waiting (admission never evicts);
+* a running request that cannot grow evicts the *youngest* running request, which gives
+  back its pages, folds the tokens it has generated into its prompt and goes to the front
+  of the queue to be recomputed (``rapid_llm/engine/batch_planner.py:849-888,972-1023``);
+  if the request that cannot grow is itself the youngest, it is the one evicted;
+* with eviction off, it waits for others to finish; if every running request is stuck,
+  :class:`CacheExhausted` is raised rather than spinning;
+* a request that could never fit the pool even alone is refused when it is submitted.
+"""
+
+from __future__ import annotations
+
+import itertools
+import time
+import zlib
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Hashable, Protocol, Sequence
+
+from ..cache import CacheManager
+from ..config import EngineConfig
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+class CacheExhausted(RuntimeError):
+    """No running request can make progress and eviction is off."""
+
+
+@dataclass
+class Request:
+    """One generation request; token ids in, token ids out."""
+
+    request_id: Hashable
+    prompt_token_ids: list[int]
+    params: SamplingParams
+    max_new_tokens: int
+    seed: int
+    status: str = WAITING
+    output_token_ids: list[int] = field(default_factory=list)
+    num_computed_tokens: int = 0
+    finish_reason: str | None = None
+    num_preemptions: int = 0
+    arrival_time: float = 0.0
+    first_scheduled_time: float | None = None
+    first_token_time: float | None = None
+    finish_time: float | None = None
+
+    @property
+    def all_token_ids(self) -> list[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def finished(self) -> bool:
+        return self.status == FINISHED
+
+
+@dataclass
+class PlannedEntry:
+    """A request's share of the planned step; ``samples`` = its last token is fed, so the
+    step's logits there choose its next token."""
+
+    request: Request
+    start: int
+    tokens: list[int]
+    samples: bool
+
+
+@dataclass
+class StepPlan:
+    entries: list[PlannedEntry] = field(default_factory=list)
+    preempted: list[Request] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(len(entry.tokens) for entry in self.entries)
+
+
+class Executor(Protocol):
+    """What the scheduler needs below it; the device executor and the tests' fake provide it."""
+
+    cache: CacheManager
+
+    def admit(self, request_id: Hashable) -> bool: ...
+
+    def release(self, request_id: Hashable) -> None: ...
+
+    def execute(self, entries: Sequence[PlannedEntry]) -> list[int]:
+        """Run the entries as one batch; one sampled token per entry with ``samples`` set, in order."""
+
+
+class Scheduler:
+    def __init__(self, executor: Executor, config: EngineConfig, stop_token_ids: Sequence[int] = ()) -> None:
+        self.executor = executor
+        self.cache = executor.cache
+        self.config = config
+        self.stop_token_ids = set(int(t) for t in stop_token_ids)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []      # in admission order: the last is the youngest
+        self._ids = itertools.count()
+        self.num_steps = 0
+        self.num_preemptions = 0
+
+    # -- submission ------------------------------------------------------------------ #
+    def add_request(
+        self,
+        prompt_token_ids: Sequence[int],
+        params: SamplingParams | None = None,
+        request_id: Hashable | None = None,
+    ) -> Request:
+        """Queue a request.  An empty prompt, or one that leaves no room to generate, is refused
+        (``rapid_llm/engine/batch_planner.py:403-427``); so is one the pool could never hold."""
+        params = params or SamplingParams()
+        prompt = [int(t) for t in prompt_token_ids]
+        limit = self.config.max_seq_len
+        if not prompt:
+            raise ValueError("the prompt is empty")
+        if len(prompt) >= limit:
+            raise ValueError(f"the prompt has {len(prompt)} tokens, max_seq_len is {limit}")
+        room = limit - len(prompt)
+        max_new = min(params.max_gen_len or room, room)
+        page = self.cache.page_size
+        most = len(prompt) + max_new - 1          # tokens cached when the last one is sampled
+        for index, pool in enumerate(self.cache.pools):
+            if -(-most // page) > pool.num_pages:
+                raise ValueError(
+                    f"the request needs {-(-most // page)} pages of cache group {index} by itself, "
+                    f"the pool has {pool.num_pages}"
+                )
+        if request_id is None:
+            request_id = f"req-{next(self._ids)}"
+        seed = params.seed if params.seed is not None else zlib.crc32(repr(request_id).encode())
+        request = Request(request_id, prompt, params, max_new, seed, arrival_time=time.perf_counter())
+        self.waiting.append(request)
+        return request
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # -- planning -------------------------------------------------------------------- #
+    def _chunk(self, request: Request, budget: int) -> int:
+        remaining = request.num_tokens - request.num_computed_tokens
+        if self.config.enable_chunked_prefill:
+            return min(remaining, self.config.max_chunk_size, budget)
+        return remaining if remaining <= budget else 0
+
+    def _fits(self, request: Request, upto: int, free: list[int]) -> list[int] | None:
+        """Pages per group the growth takes, or ``None`` if some pool is short."""
+        if self.cache.has(request.request_id):
+            needed = self.cache.pages_needed(request.request_id, upto)
+        else:
+            needed = [-(-upto // self.cache.page_size)] * len(self.cache.pools)
+        if any(n > f for n, f in zip(needed, free)):
+            return None
+        return needed
+
+    def _preempt(self, victim: Request, plan: StepPlan, free: list[int]) -> None:
+        """Evict: pages back to the pool, generated tokens kept, recompute from the start."""
+        before = [pool.num_free for pool in self.cache.pools]
+        self.executor.release(victim.request_id)
+        for index, pool in enumerate(self.cache.pools):
+            free[index] += pool.num_free - before[index]
+        self.running.remove(victim)
+        victim.status = WAITING
+        victim.num_computed_tokens = 0
+        victim.num_preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(victim)
+        plan.preempted.append(victim)
+
+    def plan(self) -> StepPlan:
+        plan = StepPlan()
+        budget = self.config.max_num_batched_tokens
+        free = [pool.num_free for pool in self.cache.pools]
+        planned: set[Hashable] = set()
+
+        # running requests, oldest first: single decoded tokens and resumed portions
+        decoding = [r for r in self.running if r.num_tokens - r.num_computed_tokens == 1]
+        resumed = [r for r in self.running if r.num_tokens - r.num_computed_tokens > 1]
+        for request in decoding + resumed:
+            if request not in self.running:        # evicted while planning an older one
+                continue
+            while True:
+                size = self._chunk(request, budget)
+                if size <= 0:
+                    break
+                needed = self._fits(request, request.num_computed_tokens + size, free)
+                if needed is not None:
+                    self._take(plan, request, size, needed, free, planned)
+                    budget -= size
+                    break
+                if not self.config.enable_preemption:
+                    break
+                victim = next(
+                    (r for r in reversed(self.running) if r.request_id not in planned), None
+                )
+                if victim is None:
+                    break
+                self._preempt(victim, plan, free)
+                if victim is request:
+                    break
+
+        # admissions in arrival order; the queue never skips ahead
+        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
+            request = self.waiting[0]
+            if request in plan.preempted:
+                break                               # evicted this very step: let it wait one
+            size = self._chunk(request, budget)
+            if size <= 0 or self.cache.num_free_slots == 0:
+                break
+            needed = self._fits(request, size, free)
+            if needed is None:
+                break
+            if not self.executor.admit(request.request_id):
+                break
+            self.waiting.popleft()
+            request.status = RUNNING
+            request.num_computed_tokens = 0
+            if request.first_scheduled_time is None:
+                request.first_scheduled_time = time.perf_counter()
+            self.running.append(request)
+            self._take(plan, request, size, needed, free, planned)
+            budget -= size
+
+        if not plan.entries and self.running and not plan.preempted:
+            raise CacheExhausted(
+                f"{len(self.running)} running requests, none can grow: the cache pool "
+                f"({[pool.num_pages for pool in self.cache.pools]} pages) is exhausted and eviction is off"
+            )
+        return plan
+
+    def _take(self, plan, request, size, needed, free, planned) -> None:
+        start = request.num_computed_tokens
+        tokens = request.all_token_ids[start : start + size]
+        plan.entries.append(PlannedEntry(request, start, tokens, samples=start + size == request.num_tokens))
+        for index, count in enumerate(needed):
+            free[index] -= count
+        planned.add(request.request_id)
+
+    # -- one step -------------------------------------------------------------------- #
+    def step(self) -> list[Request]:
+        """Plan, run and harvest one batch; returns the requests that finished in it."""
+        plan = self.plan()
+        self.num_steps += 1
+        if not plan.entries:
+            return []
+        sampled = self.executor.execute(plan.entries)
+        now = time.perf_counter()
+        finished: list[Request] = []
+        tokens = iter(sampled)
+        for entry in plan.entries:
+            request = entry.request
+            request.num_computed_tokens = entry.start + len(entry.tokens)
+            if not entry.samples:
+                continue
+            token = int(next(tokens))
+            if request.first_token_time is None:
+                request.first_token_time = now
+            if token in self.stop_token_ids:
+                self._finish(request, "eos", now)       # the stop token is not appended
+            else:
+                request.output_token_ids.append(token)
+                if len(request.output_token_ids) >= request.max_new_tokens or request.num_tokens >= self.config.max_seq_len:
+                    self._finish(request, "length", now)
+            if request.finished:
+                finished.append(request)
+        return finished
+
+    def _finish(self, request: Request, reason: str, now: float) -> None:
+        request.status = FINISHED
+        request.finish_reason = reason
+        request.finish_time = now
+        self.running.remove(request)
+        self.executor.release(request.request_id)
+
+    def abort(self, request: Request) -> None:
+        if request.status == RUNNING:
+            self._finish(request, "abort", time.perf_counter())
+        elif request.status == WAITING:
+            self.waiting.remove(request)
+            request.status, request.finish_reason = FINISHED, "abort"
+
+    def run_to_completion(self) -> None:
+        while self.has_unfinished():
+            self.step()

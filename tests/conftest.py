@@ -48,6 +48,28 @@ def tiny_dirs(tmp_path_factory):
 
 
 @pytest.fixture(scope="session")
+def tiny_dirs_bf16(tmp_path_factory):
+    """The same configurations and seeds with the matrices stored in bfloat16."""
+    from tiny_configs import CONFIGS, SEEDS
+
+    from rapid_llm_b200.config import Qwen3Config
+    from rapid_llm_b200.weights import write_random_model
+
+    root = tmp_path_factory.mktemp("tiny_models_bf16")
+    return {
+        name: write_random_model(root / name, Qwen3Config.from_dict(raw), SEEDS[name], dtype=torch.bfloat16)
+        for name, raw in CONFIGS.items()
+    }
+
+
+@pytest.fixture(scope="session")
+def tiny_plain_bf16(tiny_dirs_bf16):
+    from plain_qwen3 import load_model_dir
+
+    return {name: load_model_dir(folder) for name, folder in tiny_dirs_bf16.items()}
+
+
+@pytest.fixture(scope="session")
 def tiny_plain(tiny_dirs):
     """``name -> (config dict, weights)`` as the plain implementation reads the folders."""
     from plain_qwen3 import load_model_dir

@@ -1,0 +1,198 @@
+"""The engine against the plain implementation, in float32 and in bfloat16.
+
+Every test replays token ids through the step function (the loop behind ``bin/trace_run``)
+and compares each wanted logits row with the plain implementation's row for the same
+request and position: whole; most in one step and the last 32 one by one; portions of
+changing size down to two tokens; mixed, up to four live requests with so few pages that
+they are used again.
+"""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+from plain_qwen3 import forward_logits
+from tiny_configs import CONFIGS, PAGE_SIZES
+from tolerances import for_dtype
+from trace_tools import collect, mixed, portions, tail_one_by_one, whole
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+DTYPES = ["float32", "bfloat16"]
+
+
+def make_runner(folder, dtype: str, max_tokens: int, page_size: int, max_live: int = 8):
+    from rapid_llm_b200.config import load_config
+    from rapid_llm_b200.engine.runner import ModelRunner
+    from rapid_llm_b200.replay import engine_config_for
+
+    config = load_config(folder)
+    return ModelRunner.from_folder(folder, engine_config_for(config, dtype, max_tokens, page_size, max_live))
+
+
+def replay(runner, records):
+    from rapid_llm_b200.replay import Replayer
+
+    replayer = Replayer(runner)
+    outputs = {}
+    for record in records:
+        out = replayer.run_step(record)
+        if out is not None:
+            outputs[record["step"]] = torch.from_numpy(out.copy())
+    runner.cache.check()
+    return outputs
+
+
+def random_tokens(vocab: int, count: int, seed: int) -> list[int]:
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (count,), generator=generator).tolist()
+
+
+def compare(rows, plain_by_request, dtype):
+    tolerance = for_dtype(dtype)
+    for request_id, by_position in rows.items():
+        want = plain_by_request[request_id]
+        for position, got in sorted(by_position.items()):
+            try:
+                torch.testing.assert_close(got, want[position], **tolerance)
+            except AssertionError as exc:
+                raise AssertionError(f"request {request_id!r}, position {position}: {exc}") from None
+
+
+@pytest.fixture(scope="module")
+def models(tiny_dirs, tiny_dirs_bf16, tiny_plain, tiny_plain_bf16):
+    return {
+        "float32": (tiny_dirs, tiny_plain),
+        "bfloat16": (tiny_dirs_bf16, tiny_plain_bf16),
+    }
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_tail_and_portions(name, dtype, models):
+    dirs, plains = models[dtype]
+    config, weights = plains[name]
+    limit = config["max_position_embeddings"]
+    lengths = [5, 17, 33, min(100, limit - 1), min(limit - 1, 200)]
+    runner = make_runner(dirs[name], dtype, max_tokens=limit, page_size=PAGE_SIZES[name])
+    for index, length in enumerate(lengths):
+        tokens = random_tokens(config["vocab_size"], length, 100 + index)
+        plain = forward_logits(config, weights, tokens)
+        cases = {
+            "whole": whole("w", tokens),
+            "tail": tail_one_by_one("t", tokens, 32),
+            "portions": portions("p", tokens, [13, 2, 7, 31, 3, 2, 16, 5]),
+        }
+        for label, records in cases.items():
+            rows = collect(records, replay(runner, records))
+            request_id = records[0]["entries"][0]["id"]
+            assert sorted(rows[request_id]) == list(range(length)), label
+            compare(rows, {request_id: plain}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_with_pages_used_again(name, dtype, models):
+    dirs, plains = models[dtype]
+    config, weights = plains[name]
+    limit = config["max_position_embeddings"]
+    page = PAGE_SIZES[name]
+    lengths = [40, 97, 23, 64, 120, 35, 77, 50, 18, 90]
+    sequences = {
+        f"r{index}": random_tokens(config["vocab_size"], min(length, limit - 1), 200 + index)
+        for index, length in enumerate(lengths)
+    }
+    records, peak = mixed(sequences, seed=7, max_live=4, page=page)
+    runner = make_runner(dirs[name], dtype, max_tokens=peak, page_size=page, max_live=4)
+    seen_pages: dict[int, set[str]] = {}
+    from rapid_llm_b200.replay import Replayer
+
+    replayer, outputs = Replayer(runner), {}
+    for record in records:
+        out = replayer.run_step(dict(record, end=[]))
+        if out is not None:
+            outputs[record["step"]] = torch.from_numpy(out.copy())
+        for entry in record["entries"]:
+            for page_id in runner.cache.pages_of(entry["id"])[0]:
+                if page_id:
+                    seen_pages.setdefault(page_id, set()).add(entry["id"])
+        for request_id in record["end"]:
+            runner.release(request_id)
+        runner.cache.check()
+    assert any(len(owners) > 1 for owners in seen_pages.values()), "no page was used again"
+    plain = {rid: forward_logits(config, weights, tokens) for rid, tokens in sequences.items()}
+    compare(collect(records, outputs), plain, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype, models):
+    """Positions 0, 1, 2 alone: a one-token prompt, then single tokens."""
+    dirs, plains = models[dtype]
+    config, weights = plains["B"]
+    tokens = random_tokens(config["vocab_size"], 4, 5)
+    runner = make_runner(dirs["B"], dtype, max_tokens=64, page_size=PAGE_SIZES["B"])
+    records = tail_one_by_one("f", tokens, tail=3)
+    rows = collect(records, replay(runner, records))
+    compare(rows, {"f": forward_logits(config, weights, tokens)}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype, models):
+    """A short prompt followed by 200 single-token steps, past several page edges and the window."""
+    dirs, plains = models[dtype]
+    config, weights = plains["C"]
+    tokens = random_tokens(config["vocab_size"], 230, 9)
+    runner = make_runner(dirs["C"], dtype, max_tokens=256, page_size=PAGE_SIZES["C"])
+    records = tail_one_by_one("d", tokens, tail=200)
+    rows = collect(records, replay(runner, records))
+    compare(rows, {"d": forward_logits(config, weights, tokens)}, dtype)
+
+
+def test_window_pages_are_given_back(models):
+    dirs, plains = models["float32"]
+    config, _ = plains["C"]
+    tokens = random_tokens(config["vocab_size"], 200, 11)
+    runner = make_runner(dirs["C"], "float32", max_tokens=256, page_size=16)
+    records = portions("w", tokens, [16])
+    from rapid_llm_b200.replay import Replayer
+
+    replayer = Replayer(runner)
+    for record in records[:-1]:
+        replayer.run_step(record)
+    groups = runner.cache.groups
+    windowed = [i for i, g in enumerate(groups) if g.window]
+    full = [i for i, g in enumerate(groups) if not g.window]
+    assert windowed and full
+    pages = runner.cache.pages_of("w")
+    live_window = [p for p in pages[windowed[0]] if p]
+    live_full = [p for p in pages[full[0]] if p]
+    assert len(live_full) == len(pages[full[0]])
+    assert len(live_window) <= config["sliding_window"] // 16 + 2 < len(live_full)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(dtype, models, tmp_path):
+    """``bin/trace_run`` as a user calls it: JSON lines in, ``done`` lines and .f32 files out."""
+    dirs, plains = models[dtype]
+    config, weights = plains["A"]
+    tokens = random_tokens(config["vocab_size"], 50, 3)
+    records = portions("a", tokens, [7, 2, 20])
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(dirs["A"]), "--dtype", dtype,
+         "--out", str(out), "--max-tokens", "128"],
+        input="".join(json.dumps(r) + "\n" for r in records), capture_output=True, text=True, timeout=600,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for r in records for w in ("done", str(r["step"]))]
+    outputs = {
+        r["step"]: torch.from_numpy(np.fromfile(out / f"{r['step']}.f32", dtype="<f4").reshape(-1, config["vocab_size"]))
+        for r in records
+    }
+    compare(collect(records, outputs), {"a": forward_logits(config, weights, tokens)}, dtype)

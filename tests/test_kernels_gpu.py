@@ -1,0 +1,320 @@
+"""Each CUDA kernel alone against a plain float32/float64 PyTorch reference of the same
+operation, at sizes other than the engine tests' (widths and vocabularies that are no power
+of two, head sizes 16 to 256, odd group counts, page sizes 1 to 64)."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+from plain_qwen3 import apply_rope, causal_attention, rms_norm, rope_angles, sample_token
+from tolerances import for_dtype
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def k():
+    from rapid_llm_b200.ops import kernels
+
+    return kernels
+
+
+def fault_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def rand(shape, dtype, scale=1.0, seed=0):
+    generator = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=generator) * scale).to(dtype)
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden", [(1000, 100), (37, 4096), (513, 72)])
+def test_embedding(dtype, vocab, hidden):
+    table = rand((vocab, hidden), dtype).to(DEV)
+    ids = torch.randint(0, vocab, (50,), dtype=torch.int32).to(DEV)
+    out = torch.empty((50, hidden), dtype=dtype, device=DEV)
+    fault = fault_word()
+    k().embedding(out, table, ids, fault)
+    assert torch.equal(out, table[ids.long()])
+    assert fault.item() == 0
+    bad = ids.clone()
+    bad[3] = vocab
+    k().embedding(out, table, bad, fault)
+    assert fault.item() == 1
+
+
+# -------------------------------------------------------------------- rmsnorm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [100, 1000, 4096, 5120])
+def test_add_rmsnorm(dtype, hidden):
+    rows, eps = 23, 3e-6
+    x = rand((rows, hidden), dtype, seed=1).to(DEV)
+    residual = rand((rows, hidden), torch.float32, seed=2).to(DEV)
+    weight = (1 + 0.1 * rand((hidden,), torch.float32, seed=3)).to(DEV)
+    out = torch.empty_like(x)
+    tol = for_dtype(dtype)
+    # first layer: residual := x
+    r0 = residual.clone()
+    k().add_rmsnorm(x, r0, weight, out, eps, mode=0, write_residual=True)
+    torch.testing.assert_close(r0, x.float(), rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), rms_norm(x.float(), weight, eps), **tol)
+    # later layers: residual += x
+    r1 = residual.clone()
+    k().add_rmsnorm(x, r1, weight, out, eps, mode=1, write_residual=True)
+    want_sum = x.float() + residual
+    torch.testing.assert_close(r1, want_sum, rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), rms_norm(want_sum, weight, eps), **tol)
+    # final norm over chosen rows, residual untouched
+    index = torch.tensor([5, 0, 22, 5], dtype=torch.int32, device=DEV)
+    picked = torch.empty((4, hidden), dtype=dtype, device=DEV)
+    r2 = residual.clone()
+    k().add_rmsnorm(x, r2, weight, picked, eps, mode=1, write_residual=False, row_index=index)
+    assert torch.equal(r2, residual)
+    torch.testing.assert_close(picked.float(), rms_norm(want_sum, weight, eps)[index.long()], **tol)
+
+
+# ------------------------------------------------------------------- silu mul
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    rows, inter = 19, 1234
+    gate_up = rand((rows, 2 * inter), dtype, scale=3.0).to(DEV)
+    out = torch.empty((rows, inter), dtype=dtype, device=DEV)
+    k().silu_mul(gate_up, out)
+    gate, up = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    torch.testing.assert_close(out.float(), gate * torch.sigmoid(gate) * up, **for_dtype(dtype))
+
+
+# -------------------------------------------------------------------- gemm f32
+@pytest.mark.parametrize("m,n,k_", [(1, 53, 71), (37, 130, 64), (128, 257, 100), (200, 64, 1027), (3, 1000, 4096)])
+def test_gemm_f32(m, n, k_):
+    a = rand((m, k_), torch.float32, seed=4).to(DEV)
+    w = rand((n, k_), torch.float32, seed=5).to(DEV)
+    out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    k().gemm_f32(a, w, out)
+    want = (a.double() @ w.double().T).float()
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5 * math.sqrt(k_))
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    a = rand((70, 300), torch.float32, seed=6).to(DEV)
+    w = rand((90, 300), torch.float32, seed=7).to(DEV)
+    full = torch.empty((70, 90), dtype=torch.float32, device=DEV)
+    k().gemm_f32(a, w, full)
+    for row in (0, 33, 69):
+        single = torch.empty((1, 90), dtype=torch.float32, device=DEV)
+        k().gemm_f32(a[row : row + 1].contiguous(), w, single)
+        assert torch.equal(single[0], full[row])
+
+
+# ---------------------------------------------------- q/k norm + rope + cache write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,rotary,page", [(4, 2, 16, 16, 4), (6, 1, 48, 48, 8), (5, 5, 128, 64, 16), (3, 3, 256, 256, 1)])
+def test_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page):
+    tokens, eps, theta, max_pos, pages = 21, 1e-5, 50000.0, 300, 40
+    qkv = rand((tokens, (hq + 2 * hkv) * d), dtype, seed=8).to(DEV)
+    qw = (1 + 0.1 * rand((d,), torch.float32, seed=9)).to(DEV)
+    kw = (1 + 0.1 * rand((d,), torch.float32, seed=10)).to(DEV)
+    positions = torch.randint(0, max_pos, (tokens,), dtype=torch.int32)
+    cos, sin = rope_angles(torch.arange(max_pos), rotary, theta)
+    dest = torch.randperm(pages * page)[:tokens].to(torch.int32)
+    cache = torch.zeros((pages, 2, hkv, page, d), dtype=dtype, device=DEV)
+    q_out = torch.empty((tokens, hq * d), dtype=dtype, device=DEV)
+    fault = fault_word()
+    k().qk_norm_rope_write(
+        qkv, q_out, num_heads=hq, num_kv_heads=hkv, head_dim=d, rotary_dim=rotary,
+        cos=cos.to(DEV).contiguous(), sin=sin.to(DEV).contiguous(), positions=positions.to(DEV), eps=eps,
+        fault=fault, q_weight=qw, k_weight=kw, kv_dest=dest.to(DEV), cache=cache, page_size=page,
+    )
+    assert fault.item() == 0
+    host = qkv.float().cpu()
+    q = host[:, : hq * d].view(tokens, hq, d)
+    key = host[:, hq * d : (hq + hkv) * d].view(tokens, hkv, d)
+    value = host[:, (hq + hkv) * d :].view(tokens, hkv, d)
+    c, s = cos[positions.long()], sin[positions.long()]
+    want_q = apply_rope(rms_norm(q, qw.cpu(), eps), c, s)
+    want_k = apply_rope(rms_norm(key, kw.cpu(), eps), c, s)
+    tol = for_dtype(dtype)
+    torch.testing.assert_close(q_out.float().cpu().view(tokens, hq, d), want_q, **tol)
+    got = cache.float().cpu()
+    page_id, offset = dest.long() // page, dest.long() % page
+    torch.testing.assert_close(got[page_id, 0, :, offset], want_k, **tol)
+    torch.testing.assert_close(got[page_id, 1, :, offset], value, rtol=0, atol=0)
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[dest.long()] = False
+    flat = got.permute(0, 3, 1, 2, 4).reshape(pages * page, -1)
+    assert flat[untouched].abs().max() == 0
+
+
+# ------------------------------------------------------------------ attention
+def paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=0, key_scale=1.0):
+    """A cache with shuffled pages holding ``lengths`` tokens per request; the last
+    ``new_counts`` of each are the step's queries."""
+    generator = torch.Generator().manual_seed(seed)
+    slots = len(lengths) + 2
+    max_pages = max(-(-n // page) for n in lengths) + 1
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = (torch.randperm(total_pages - 1, generator=generator) + 1).tolist()
+    table = torch.zeros((slots, max_pages), dtype=torch.int32)
+    cache = torch.zeros((total_pages, 2, hkv, page, d), dtype=torch.float32)
+    keys, values, queries = [], [], []
+    positions, token_slot = [], []
+    slot_ids = torch.randperm(slots, generator=generator)[: len(lengths)].tolist()
+    for slot, length, new in zip(slot_ids, lengths, new_counts):
+        key = torch.randn((length, hkv, d), generator=generator) * key_scale
+        value = torch.randn((length, hkv, d), generator=generator)
+        query = torch.randn((length, hq, d), generator=generator)
+        keys.append(key), values.append(value), queries.append(query)
+        for index in range(-(-length // page)):
+            page_id = order.pop()
+            table[slot, index] = page_id
+            chunk = slice(index * page, min(length, (index + 1) * page))
+            count = chunk.stop - chunk.start
+            cache[page_id, 0, :, :count] = key[chunk].transpose(0, 1)
+            cache[page_id, 1, :, :count] = value[chunk].transpose(0, 1)
+        positions.extend(range(length - new, length))
+        token_slot.extend([slot] * new)
+    q = torch.cat([query[length - new :] for query, length, new in zip(queries, lengths, new_counts)])
+    return {
+        "q": q.to(dtype), "cache": cache.to(dtype), "table": table,
+        "positions": torch.tensor(positions, dtype=torch.int32),
+        "token_slot": torch.tensor(token_slot, dtype=torch.int32),
+        "keys": keys, "values": values, "queries": queries,
+    }
+
+
+def plain_paged(case, dtype, lengths, new_counts, scale, window):
+    outs = []
+    for key, value, query, length, new in zip(case["keys"], case["values"], case["queries"], lengths, new_counts):
+        cast = lambda t: t.to(dtype).float()  # noqa: E731  (what the kernel reads)
+        full = causal_attention(cast(query), cast(key), cast(value), scale, window)
+        outs.append(full[length - new :])
+    return torch.cat(outs)
+
+
+def run_generic(case, hq, hkv, d, scale, window):
+    q = case["q"].to(DEV).contiguous()
+    out = torch.empty_like(q)
+    fault = fault_word()
+    k().attention_generic(
+        q, case["cache"].to(DEV), out, positions=case["positions"].to(DEV),
+        token_slot=case["token_slot"].to(DEV), block_table=case["table"].to(DEV),
+        num_heads=hq, num_kv_heads=hkv, head_dim=d, window=window, scale=scale, fault=fault,
+    )
+    assert fault.item() == 0
+    return out.float().cpu()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "hq,hkv,d,page,window",
+    [(4, 2, 16, 16, 0), (6, 1, 32, 8, 0), (7, 7, 48, 4, 0), (8, 2, 128, 16, 0), (3, 1, 256, 64, 0),
+     (6, 3, 64, 16, 40), (4, 4, 80, 1, 7), (10, 2, 96, 32, 33)],
+)
+def test_attention_generic(dtype, hq, hkv, d, page, window):
+    lengths = [1, 15, 16, 17, 129, 200, 64]
+    new_counts = [1, 15, 1, 2, 129, 1, 33]
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=d + page)
+    scale = d**-0.5
+    got = run_generic(case, hq, hkv, d, scale, window)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, window)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
+    """One key among hundreds is made to dominate: the output must be its value, unless the
+    window has just passed it."""
+    hq, hkv, d, page = 4, 2, 64, 16
+    length, far = 700, 13
+    case = paged_case(dtype, hq, hkv, d, page, [length], [1], seed=3)
+    query = case["queries"][0][-1]                       # [hq, d]
+    for head in range(hkv):
+        case["keys"][0][far, head] = 40.0 * query[head * (hq // hkv)] / query[head * (hq // hkv)].norm()
+    page_id = int(case["table"][case["token_slot"][0], far // page])
+    case["cache"][page_id, 0, :, far % page] = case["keys"][0][far].to(dtype)
+    scale = d**-0.5
+    for window, expect_far in [(0, True), (length - far, True), (length - far - 1, False)]:
+        got = run_generic(case, hq, hkv, d, scale, window)
+        want = plain_paged(case, dtype, [length], [1], scale, window)
+        torch.testing.assert_close(got, want, **for_dtype(dtype))
+        first_head = got.view(1, hq, d)[0, 0]
+        value = case["values"][0][far, 0].to(dtype).float()
+        close = (first_head - value).abs().max() < 0.15
+        assert bool(close) == expect_far
+
+
+# -------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab", [331, 8193, 151936])
+def test_greedy_is_first_maximum(dtype, vocab):
+    rows = 5
+    logits = rand((rows, vocab), dtype, seed=11).to(DEV)
+    logits[1, 7] = logits[1].max() + 1
+    logits[2, vocab - 1] = logits[2].max() + 2
+    logits[3, 100] = logits[3, 200] = logits[3].max() + 3   # a tie: the first index wins
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    k().sample(logits, out)
+    assert out.tolist() == torch.argmax(logits.float(), dim=-1).tolist()
+    assert out[3].item() == 100
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampling_matches_plain(dtype):
+    vocab, rows = 1237, 24
+    logits = rand((rows, vocab), dtype, scale=2.0, seed=12).to(DEV)
+    temperature = torch.tensor([0.0, 0.7, 1.0, 1.3] * 6, dtype=torch.float32)
+    top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 0.3, 0.95] * 4, dtype=torch.float32)
+    penalty = torch.tensor([1.0, 1.1, 1.0, 2.0] * 6, dtype=torch.float32)
+    seeds = torch.arange(rows, dtype=torch.int64) * 7919 + 5
+    counters = torch.arange(rows, dtype=torch.int32) + 3
+    generated = [torch.randint(0, vocab, (row % 5 * 9,)).tolist() for row in range(rows)]
+    offsets = torch.tensor([0] + [len(g) for g in generated], dtype=torch.int32).cumsum(0).to(torch.int32)
+    flat = torch.tensor([t for g in generated for t in g] or [0], dtype=torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    k().sample(
+        logits, out, temperature=temperature.to(DEV), top_p=top_p.to(DEV), penalty=penalty.to(DEV),
+        seeds=seeds.to(DEV), counters=counters.to(DEV), seen_tokens=flat.to(DEV), seen_offsets=offsets.to(DEV),
+    )
+    host = logits.float().cpu()
+    want = [
+        sample_token(host[row], float(temperature[row]), float(top_p[row]), float(penalty[row]),
+                     generated[row], int(seeds[row]), int(counters[row]))
+        for row in range(rows)
+    ]
+    agree = sum(int(a == b) for a, b in zip(out.tolist(), want))
+    assert agree >= rows - 1, (out.tolist(), want)   # a draw on a float32 rounding edge may differ
+
+
+def test_sampling_follows_the_distribution():
+    vocab, rows = 50, 4000
+    base = torch.linspace(-2, 2, vocab)
+    logits = base.repeat(rows, 1).to(DEV)
+    temperature = torch.full((rows,), 0.8)
+    seeds = torch.full((rows,), 1234, dtype=torch.int64)
+    counters = torch.arange(rows, dtype=torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    k().sample(logits, out, temperature=temperature.to(DEV), seeds=seeds.to(DEV), counters=counters.to(DEV))
+    counts = torch.bincount(out.long().cpu(), minlength=vocab).float() / rows
+    want = torch.softmax(base / 0.8, 0)
+    assert (counts - want).abs().max() < 0.02
+    again = torch.empty_like(out)
+    k().sample(logits, again, temperature=temperature.to(DEV), seeds=seeds.to(DEV), counters=counters.to(DEV))
+    assert torch.equal(out, again)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    kernels = k()
+    with pytest.raises(kernels.KernelError):
+        kernels.attention_generic(
+            torch.zeros((1, 24), device=DEV), torch.zeros((2, 2, 1, 4, 24), device=DEV), torch.zeros((1, 24), device=DEV),
+            positions=torch.zeros(1, dtype=torch.int32, device=DEV), token_slot=torch.zeros(1, dtype=torch.int32, device=DEV),
+            block_table=torch.zeros((1, 1), dtype=torch.int32, device=DEV), num_heads=1, num_kv_heads=1, head_dim=24,
+            window=0, scale=1.0, fault=fault_word(),
+        )
+    with pytest.raises(kernels.KernelError):
+        kernels.silu_mul(torch.zeros((2, 8)), torch.zeros((2, 4)))   # CPU tensors: no CPU path
