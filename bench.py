@@ -1,0 +1,291 @@
+"""Decode and prefill throughput of the Qwen3-8B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  ``value`` is decoded tokens per second at
+batch 8 with 1,024-token prompts (context limit 8192, pages of 16 tokens), timed on the
+device with CUDA events around exactly K steps after W warm-up steps; each step includes
+the upload of its metadata, the captured forward graph, the sampling kernel and the read
+of the sampled ids.  The weights streamed per step (15 GB) exceed L2 by two orders of
+magnitude, so no flush is needed between iterations.  ``e2e`` is the same measured by the
+wall clock through the Python entry point's scheduler (host token ids in and out).  The
+line also carries a 2,048-token prefill, decode at batch 1 and 64, the decode step's HBM
+roofline and the clocks sampled while timing.  For more than one GPU it says so and exits 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "vocab_size": 151936, "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 36,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+}
+CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
+PUBLISHED_TOK_S = 216.6   # Qwen3-8B bf16, batch 8, 1x A10: docs/benchmark_models.md:191 of the reference
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()
+                if out:
+                    self.samples.append([field.strip() for field in out.splitlines()[0].split(",")])
+            except (OSError, subprocess.SubprocessError):
+                return
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [name for i, name in enumerate(names) if any(len(s) > 2 + i and s[2 + i] == "Active" for s in self.samples)]
+        return {
+            "sm_mhz": int(statistics.median(clocks)) if clocks else None,
+            "sm_max_mhz": int(self.samples[0][1]) if self.samples and self.samples[0][1].isdigit() else None,
+            "reasons": reasons, "samples": len(self.samples),
+        }
+
+
+def weight_bytes_per_step(cfg: dict, layers: int) -> int:
+    """Every weight a decode step uses once: the layers' matrices and norms plus the head (the
+    embedding is a gather of a few rows)."""
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d, hq, hkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    per_layer = ((hq + 2 * hkv) * d * h + h * hq * d + 3 * i * h) * 2 + (2 * h + 2 * d) * 4
+    return layers * per_layer + v * h * 2 + h * 4
+
+
+def kv_bytes_per_token(cfg: dict, layers: int) -> int:
+    return layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d, hq, hkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    linear = 2.0 * tokens * ((hq + 2 * hkv) * d * h + h * hq * d + 3 * i * h)
+    attention = 4.0 * hq * d * tokens * (tokens + 1) / 2
+    return layers * (linear + attention) + 2.0 * v * h     # the head runs on the last row only
+
+
+def random_prompts(count: int, length: int, vocab: int, seed: int) -> list[list[int]]:
+    import torch
+
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (count, length), generator=generator).tolist()
+
+
+def decode_run(llm, batch: int, steps: int, warmup: int, seed: int) -> dict:
+    """Prefill ``batch`` prompts, then time ``steps`` decode steps on the device and by wall clock."""
+    import torch
+
+    from rapid_llm_b200 import SamplingParams
+    from rapid_llm_b200.ops import kernels
+
+    scheduler, runner = llm.scheduler, llm.runner
+    params = SamplingParams.greedy(max_gen_len=2 * (steps + warmup) + 8)
+    vocab = runner.model.spec.vocab_size
+    requests = [scheduler.add_request(p, params) for p in random_prompts(batch, PROMPT_LEN, vocab, seed)]
+    while any(r.num_computed_tokens < len(r.prompt_token_ids) for r in requests):
+        scheduler.step()                                   # prefill, untimed
+    for _ in range(warmup):
+        scheduler.step()
+    torch.cuda.synchronize()
+    context_start = requests[0].num_tokens
+
+    launches_before = kernels.LAUNCHES.count
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        scheduler.step()
+    end.record()
+    torch.cuda.synchronize()
+    device_ms = begin.elapsed_time(end)
+    launches = kernels.LAUNCHES.count - launches_before
+
+    started = time.perf_counter()
+    for _ in range(steps):
+        scheduler.step()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - started) * 1000.0
+    context_mean = context_start + steps / 2.0
+    for request in requests:
+        scheduler.abort(request)
+    return {
+        "device_ms": device_ms, "wall_ms": wall_ms, "launches": launches, "context_mean": context_mean,
+        "tokens": batch * steps,
+    }
+
+
+def prefill_run(llm, warmup: int, seed: int) -> float:
+    """Milliseconds of one 2,048-token prompt as a single step (best of three after warm-up)."""
+    import torch
+
+    from rapid_llm_b200.engine.runner import StepEntry
+
+    runner = llm.runner
+    vocab = runner.model.spec.vocab_size
+    times = []
+    for trial in range(max(warmup, 1) + 3):
+        tokens = random_prompts(1, PREFILL_TOKENS, vocab, seed + trial)[0]
+        runner.admit("prefill")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        runner.step([StepEntry("prefill", tokens, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        runner.release("prefill")
+        if trial >= max(warmup, 1):
+            times.append(begin.elapsed_time(end))
+    return min(times)
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from rapid_llm_b200 import LLM, EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner
+
+    peaks = measured_peaks()
+    raw = dict(QWEN3_8B)
+    layers_full = raw["num_hidden_layers"]
+    layers = args.layers or layers_full
+    raw["num_hidden_layers"] = layers
+    config = Qwen3Config.from_dict(raw)
+    batches = sorted({1, args.batch, 64})
+    pages = max(batches) * (-(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 64) // PAGE)) + PREFILL_TOKENS // PAGE + 8
+    engine = EngineConfig(
+        dtype=torch.bfloat16, max_seq_len=CONTEXT, page_size=PAGE, num_pages=pages, max_num_seqs=max(batches),
+        max_num_batched_tokens=max(PREFILL_TOKENS, 2048), max_chunk_size=2048, use_cuda_graph=True,
+    )
+    runner = ModelRunner.from_random(config, seed=0, config=engine)
+    llm = LLM.from_runner(runner)
+
+    prefill_ms = prefill_run(llm, args.warmup, seed=11)
+    results = {}
+    for batch in batches:
+        if batch == args.batch:
+            continue
+        results[batch] = decode_run(llm, batch, args.steps, args.warmup, seed=batch)
+    with ClockSampler() as clocks:
+        results[args.batch] = decode_run(llm, args.batch, args.steps, args.warmup, seed=args.batch)
+    main = results[args.batch]
+
+    ms_per_step = main["device_ms"] / args.steps
+    value = main["tokens"] / (main["device_ms"] / 1000.0)
+    step_bytes = weight_bytes_per_step(raw, layers) + args.batch * main["context_mean"] * kv_bytes_per_token(raw, layers)
+    achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
+    flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+    meta_bytes = 4 * (args.batch * (3 + 1) + 3 * args.batch + 1 + args.batch)
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 1024-token prompts)",
+        "value": round(value, 1),
+        "unit": "tok/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": round(value / PUBLISHED_TOK_S, 2),
+        "dtype": "bf16",
+        "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape, random weights", "layers": layers, "layers_full": layers_full,
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed per step)",
+            "baseline_ref": "216.6 tok/s, Qwen3-8B bf16 batch 8 on 1x A10 (reference docs/benchmark_models.md:191)",
+            "peaks": peaks["source"],
+        },
+        "e2e": {
+            "value": round(main["tokens"] / (main["wall_ms"] / 1000.0), 1), "unit": "tok/s",
+            "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1),
+        },
+        "gpu_launches": main["launches"],
+        "prefill": {
+            "value": round(PREFILL_TOKENS / (prefill_ms / 1000.0), 1), "tokens": PREFILL_TOKENS,
+            "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms / 1000.0) / (peaks["bf16_tflops"] * 1e12), 4),
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / peaks["hbm_gbs"], 4),
+        },
+        "points": {
+            f"decode_b{batch}": round(result["tokens"] / (result["device_ms"] / 1000.0), 1)
+            for batch, result in sorted(results.items()) if batch != args.batch
+        },
+        "clocks": clocks.summary(),
+    }
+
+
+def run_reference(args) -> dict:
+    return {"impl": "reference", "unavailable": "reference arm not wired yet"}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=4)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (work on several GPUs is out of scope)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -199,7 +199,11 @@ class Qwen3Config:
             unknown = sorted(set(self.layer_types) - {FULL_ATTENTION, SLIDING_ATTENTION})
             if unknown:
                 raise ValueError(f"unknown layer_types entries: {unknown}")
-        if any(self.layer_windows()) and (self.sliding_window is None or self.sliding_window < 1):
+        if self.layer_types:
+            wants_window = SLIDING_ATTENTION in self.layer_types
+        else:
+            wants_window = self.use_sliding_window and (self.max_window_layers or 0) < self.num_hidden_layers
+        if wants_window and (self.sliding_window is None or self.sliding_window < 1):
             raise ValueError(
                 "sliding-window layers are configured but sliding_window is "
                 f"{self.sliding_window!r}"

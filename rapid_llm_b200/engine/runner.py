@@ -96,7 +96,8 @@ class ModelRunner:
         self.result = torch.zeros(config.max_num_seqs + 2, dtype=torch.int32, device=self.device)
         self.fault = self.result[:1]
         self.steps_run = 0
-        self.kernel_launches = 0
+        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graph_pool = None
 
     # -- construction ---------------------------------------------------------------- #
     @classmethod
@@ -197,7 +198,7 @@ class ModelRunner:
             assert reserved
 
         g = len(cache.groups)
-        rows = sum(len(entry.want) for entry in entries)
+        rows = sum(len(entry.want) for entry in entries) + pad
         host = self._meta_host[self._meta_flip]
         self._meta_flip ^= 1
         meta = host.numpy()
@@ -240,6 +241,8 @@ class ModelRunner:
             entry_slot[i], entry_start[i] = self.pad_slot, 0
             for index in range(g):
                 kv_dest[index][at] = 0
+            logit_rows[row_at] = at
+            row_at += 1
             at += 1
             cu_seqlens[i + 1] = at
 
@@ -299,6 +302,53 @@ class ModelRunner:
             self.cache.release_passed(entry.request_id)
         self.steps_run += 1
         return logits
+
+    def decode_bucket(self, count: int) -> int:
+        """Batch size a decode-only step of ``count`` rows is padded to for graph replay."""
+        bucket = 1
+        while bucket < count:
+            bucket *= 2
+        return min(bucket, self.config.max_num_seqs) if count <= self.config.max_num_seqs else count
+
+    @torch.no_grad()
+    def step_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of single tokens, each wanting its logits, replayed from a captured graph.
+
+        The batch is padded to a bucket size with rows that point at the null page; the
+        metadata lives in a fixed device buffer that is refreshed before each replay.  The
+        first step of a bucket runs eagerly and is then captured.  The reference captures
+        decode graphs per batch size and length bucket (``rapid_llm/executor/cuda_graph.py:45-46,317``).
+        """
+        if any(len(entry.tokens) != 1 or list(entry.want) != [0] for entry in entries):
+            raise ValueError("step_decode takes single tokens that all want their logits")
+        count = len(entries)
+        bucket = self.decode_bucket(count)
+        batch = self.prepare(entries, pad_to=bucket)
+        captured = self._graphs.get(bucket)
+        if captured is None:
+            caches = self.layer_caches()
+            logits = self.model.forward(batch, caches)
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            before = kernels.LAUNCHES.count
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self.model.forward(batch, caches)
+            launches = kernels.LAUNCHES.count - before
+            kernels.LAUNCHES.count = before          # recording is not launching
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[bucket] = (graph, static_logits, launches)
+            logits = static_logits
+            graph.replay()   # the eager run above already wrote the same values; keeps one code path
+            kernels.LAUNCHES.add(launches)
+        else:
+            graph, logits, launches = captured
+            graph.replay()
+            kernels.LAUNCHES.add(launches)
+        for entry in entries:
+            self.cache.release_passed(entry.request_id)
+        self.steps_run += 1
+        return logits[:count]
 
     def check_fault(self) -> None:
         """Raise if a kernel met an index outside its tables since the last check (syncs)."""

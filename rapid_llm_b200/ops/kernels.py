@@ -69,7 +69,23 @@ def _expect(name: str, tensor: torch.Tensor | None, dtype: torch.dtype) -> None:
 _CUDA_ERRORS = {1: "invalid value (a size or argument the kernel refuses)"}
 
 
+class LaunchCounter:
+    """Counts launches of this library's kernels (library products are not counted).
+
+    A captured graph's launches are added by whoever replays it (``add``)."""
+
+    def __init__(self) -> None:
+        self.count = 0
+
+    def add(self, launches: int) -> None:
+        self.count += launches
+
+
+LAUNCHES = LaunchCounter()
+
+
 def _check(code: int, what: str) -> None:
+    LAUNCHES.count += 1
     if code != 0:
         detail = _CUDA_ERRORS.get(code, f"CUDA error {code}")
         raise KernelError(f"{what}: {detail}")

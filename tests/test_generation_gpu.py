@@ -1,0 +1,110 @@
+"""Generation through the Python entry point against the plain implementation."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+from plain_qwen3 import forward_logits, greedy_generate, sample_token
+from tiny_configs import PAGE_SIZES
+
+pytestmark = pytest.mark.gpu
+
+
+def random_prompts(vocab, lengths, seed):
+    generator = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=generator).tolist() for n in lengths]
+
+
+def make_llm(folder, dtype, name, **overrides):
+    from rapid_llm_b200 import LLM
+
+    values = dict(dtype=dtype, max_seq_len=128, max_gpu_num_blocks=64, page_size=PAGE_SIZES[name],
+                  max_num_seqs=4, max_chunk_size=13, max_num_batched_tokens=64)
+    values.update(overrides)
+    return LLM(folder, **values)
+
+
+def test_greedy_float32_equals_plain(tiny_dirs, tiny_plain):
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain["A"]
+    prompts = random_prompts(config["vocab_size"], [5, 17, 33], 1)
+    llm = make_llm(tiny_dirs["A"], "float32", "A")
+    outputs = llm.generate(prompts, SamplingParams.greedy(max_gen_len=8))
+    for prompt, output in zip(prompts, outputs):
+        assert output.token_ids == greedy_generate(config, weights, prompt, 8)
+        assert output.outputs[0].finish_reason == "length" and output.prompt_token_ids == prompt
+    llm.runner.cache.check()
+    assert llm.runner.cache.num_free_slots == 4
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_greedy_bfloat16_picks_a_maximum_of_the_plain_logits(tiny_dirs_bf16, tiny_plain_bf16, use_graph):
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain_bf16["B"]
+    prompts = random_prompts(config["vocab_size"], [1, 7, 31, 64, 100], 2)
+    llm = make_llm(tiny_dirs_bf16["B"], "bfloat16", "B", max_seq_len=160, use_cuda_graph=use_graph)
+    outputs = llm.generate(prompts, SamplingParams.greedy(max_gen_len=12))
+    for prompt, output in zip(prompts, outputs):
+        tokens = output.token_ids
+        assert len(tokens) == 12
+        logits = forward_logits(config, weights, prompt + tokens)
+        for index, token in enumerate(tokens):
+            row = logits[len(prompt) - 1 + index]
+            assert float(row.max() - row[token]) < 2e-2
+
+
+def test_graph_and_eager_decode_agree(tiny_dirs):
+    from rapid_llm_b200 import SamplingParams
+
+    prompts = random_prompts(384, [9, 30, 3], 5)
+    eager = make_llm(tiny_dirs["B"], "float32", "B", use_cuda_graph=False).generate(prompts, SamplingParams.greedy(max_gen_len=20))
+    graph = make_llm(tiny_dirs["B"], "float32", "B", use_cuda_graph=True).generate(prompts, SamplingParams.greedy(max_gen_len=20))
+    assert [o.token_ids for o in eager] == [o.token_ids for o in graph]
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_dirs, tiny_plain):
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain["B"]
+    prompts = random_prompts(config["vocab_size"], [1, 7, 31, 64, 100], 3)
+    params = [SamplingParams(temperature=0.7, top_p=0.9, repetition_penalty=1.1, max_gen_len=12, seed=50 + i) for i in range(5)]
+    llm = make_llm(tiny_dirs["B"], "float32", "B", max_seq_len=160)
+    together = llm.generate(prompts, params)
+    alone = [llm.generate([p], [sp])[0] for p, sp in zip(prompts, params)]
+    assert [o.token_ids for o in together] == [o.token_ids for o in alone]
+    # teacher-forced check of every draw against the plain sampler
+    agree = total = 0
+    for prompt, output, sp in zip(prompts, together, params):
+        tokens = output.token_ids
+        logits = forward_logits(config, weights, prompt + tokens)
+        for index, token in enumerate(tokens):
+            want = sample_token(logits[len(prompt) - 1 + index], 0.7, 0.9, 1.1, tokens[:index], sp.seed, index)
+            agree += int(want == token)
+            total += 1
+    assert agree >= total - 2, (agree, total)
+
+
+def test_eviction_under_a_small_pool_does_not_change_tokens(tiny_dirs):
+    from rapid_llm_b200 import SamplingParams
+
+    prompts = random_prompts(256, [30, 20, 25], 4)
+    roomy = make_llm(tiny_dirs["A"], "float32", "A").generate(prompts, SamplingParams.greedy(max_gen_len=30))
+    tight_llm = make_llm(tiny_dirs["A"], "float32", "A", max_gpu_num_blocks=8)
+    tight = tight_llm.generate(prompts, SamplingParams.greedy(max_gen_len=30))
+    assert [o.token_ids for o in roomy] == [o.token_ids for o in tight]
+    assert tight_llm.scheduler.num_preemptions >= 1
+    tight_llm.runner.cache.check()
+
+
+def test_stop_token_ends_a_request(tiny_dirs, tiny_plain):
+    from rapid_llm_b200 import LLM, SamplingParams
+
+    config, weights = tiny_plain["A"]
+    prompt = random_prompts(256, [12], 6)[0]
+    free = greedy_generate(config, weights, prompt, 6)
+    llm = LLM(tiny_dirs["A"], dtype="float32", max_seq_len=128, max_gpu_num_blocks=16, stop_token_ids=[free[3]])
+    output = llm.generate([prompt], SamplingParams.greedy(max_gen_len=6))[0]
+    first_stop = free.index(free[3])
+    assert output.token_ids == free[:first_stop] and output.outputs[0].finish_reason == "eos"

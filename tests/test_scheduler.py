@@ -1,0 +1,167 @@
+"""The scheduler's decisions with a scripted executor instead of a model (no GPU)."""
+
+import pytest
+
+from rapid_llm_b200.cache import CacheManager, plan_groups
+from rapid_llm_b200.config import EngineConfig
+from rapid_llm_b200.engine.scheduler import CacheExhausted, Scheduler
+from rapid_llm_b200.parts.base import CacheNeed
+from rapid_llm_b200.sampling import SamplingParams
+
+
+class ScriptedExecutor:
+    """Keeps the real cache bookkeeping, returns ``1000 + index of the generated token``."""
+
+    def __init__(self, config: EngineConfig, pages: int) -> None:
+        groups, _ = plan_groups([CacheNeed("full", 1, 16)])
+        self.cache = CacheManager(groups, page_size=config.page_size, num_pages=pages,
+                                  max_num_seqs=config.max_num_seqs, max_seq_len=config.max_seq_len)
+        self.steps: list[list[tuple]] = []
+        self.stop_after: dict = {}
+
+    def admit(self, request_id):
+        return self.cache.admit(request_id) is not None
+
+    def release(self, request_id):
+        self.cache.release(request_id)
+
+    def execute(self, entries):
+        self.steps.append([(e.request.request_id, e.start, len(e.tokens), e.samples) for e in entries])
+        sampled = []
+        for entry in entries:
+            assert entry.start == self.cache.num_tokens(entry.request.request_id), "a portion must start where the cache ends"
+            assert self.cache.reserve(entry.request.request_id, entry.start + len(entry.tokens)), "the plan overbooked the pool"
+            assert entry.tokens == entry.request.all_token_ids[entry.start : entry.start + len(entry.tokens)]
+            if entry.samples:
+                index = len(entry.request.output_token_ids)
+                stop = self.stop_after.get(entry.request.request_id)
+                sampled.append(7 if stop is not None and index >= stop else 1000 + index)
+        self.cache.check()
+        return sampled
+
+
+def make(pages=64, **overrides):
+    values = dict(max_seq_len=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=64, max_chunk_size=32)
+    values.update(overrides)
+    config = EngineConfig(**values)
+    executor = ScriptedExecutor(config, pages)
+    return Scheduler(executor, config, stop_token_ids=[7]), executor
+
+
+def greedy(n):
+    return SamplingParams.greedy(max_gen_len=n)
+
+
+def test_prompt_is_cut_into_portions_under_the_chunk_size():
+    scheduler, executor = make()
+    request = scheduler.add_request(list(range(70)), greedy(3), "a")
+    scheduler.run_to_completion()
+    assert [step[0][1:] for step in executor.steps] == [(0, 32, False), (32, 32, False), (64, 6, True), (70, 1, True), (71, 1, True)]
+    assert request.output_token_ids == [1000, 1001, 1002] and request.finish_reason == "length"
+    assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
+
+
+def test_token_budget_decodes_first_then_resumed_then_new():
+    scheduler, executor = make(max_num_batched_tokens=40)
+    scheduler.add_request(list(range(10)), greedy(8), "a")
+    scheduler.step()                                   # a: whole prompt, samples
+    scheduler.add_request(list(range(50)), greedy(2), "b")
+    scheduler.add_request(list(range(30)), greedy(2), "c")
+    scheduler.step()
+    assert executor.steps[-1] == [("a", 10, 1, True), ("b", 0, 32, False), ("c", 0, 7, False)]   # 1 + 32 + 7 = 40
+    scheduler.step()
+    assert executor.steps[-1] == [("a", 11, 1, True), ("b", 32, 18, True), ("c", 7, 21, False)]
+    assert sum(n for _, _, n, _ in executor.steps[-1]) == 40
+
+
+def test_first_token_comes_from_the_last_portion_and_eos_is_not_appended():
+    scheduler, executor = make()
+    executor.stop_after["a"] = 2
+    request = scheduler.add_request(list(range(5)), greedy(10), "a")
+    scheduler.run_to_completion()
+    assert request.output_token_ids == [1000, 1001] and request.finish_reason == "eos"
+    assert request.first_token_time is not None
+
+
+def test_admission_is_fcfs_and_bounded_by_slots():
+    scheduler, executor = make(max_num_seqs=2, max_num_batched_tokens=256)
+    requests = [scheduler.add_request(list(range(4)), greedy(2), name) for name in "abc"]
+    scheduler.step()
+    assert [e[0] for e in executor.steps[-1]] == ["a", "b"]
+    scheduler.step()
+    assert [e[0] for e in executor.steps[-1]] == ["a", "b"]      # both finish here
+    scheduler.step()
+    assert [e[0] for e in executor.steps[-1]] == ["c"]
+    scheduler.run_to_completion()
+    assert all(r.finish_reason == "length" for r in requests)
+
+
+def test_waiting_request_waits_for_pages():
+    scheduler, executor = make(pages=4, max_num_batched_tokens=256, max_chunk_size=256)
+    first = scheduler.add_request(list(range(40)), greedy(3), "a")      # 3 pages
+    second = scheduler.add_request(list(range(30)), greedy(3), "b")     # 2 pages: must wait
+    scheduler.step()
+    assert [e[0] for e in executor.steps[-1]] == ["a"] and second.status == "waiting"
+    scheduler.run_to_completion()
+    assert first.finish_reason == second.finish_reason == "length"
+    assert scheduler.num_preemptions == 0
+
+
+def test_growth_evicts_the_youngest_which_recomputes_with_its_tokens_folded_in():
+    scheduler, executor = make(pages=4, max_num_batched_tokens=256, max_chunk_size=256)
+    old = scheduler.add_request(list(range(30)), greedy(20), "old")      # 49 tokens = 4 pages alone
+    young = scheduler.add_request(list(range(20)), greedy(30), "young")  # 49 tokens = 4 pages alone
+    scheduler.step()                                                      # both prefill: 2 + 2 pages
+    assert executor.cache.num_free_pages() == 0
+    for _ in range(3):
+        scheduler.step()                                                  # old reaches 33 tokens: needs a third page
+    assert scheduler.num_preemptions >= 1 and young.num_preemptions >= 1 and old.num_preemptions == 0
+    kept = list(young.output_token_ids)
+    assert kept, "the evicted request keeps what it generated"
+    scheduler.run_to_completion()
+    assert old.finish_reason == young.finish_reason == "length"
+    assert len(old.output_token_ids) == 20 and len(young.output_token_ids) == 30
+    assert young.output_token_ids[: len(kept)] == kept
+    assert young.output_token_ids == [1000 + i for i in range(30)]
+    recompute = [e for step in executor.steps for e in step if e[0] == "young" and e[1] == 0]
+    assert len(recompute) >= 2 and recompute[-1][2] > 20, "the recomputed prompt holds the generated tokens"
+    assert executor.cache.num_free_pages() == 4
+
+
+def test_without_eviction_a_stuck_pool_is_an_error_not_a_spin():
+    scheduler, executor = make(pages=4, max_num_batched_tokens=256, max_chunk_size=256, enable_preemption=False)
+    scheduler.add_request(list(range(30)), greedy(20), "a")
+    scheduler.add_request(list(range(30)), greedy(20), "b")
+    with pytest.raises(CacheExhausted):
+        scheduler.run_to_completion()
+
+
+def test_submission_checks():
+    scheduler, _ = make(pages=4)
+    with pytest.raises(ValueError, match="empty"):
+        scheduler.add_request([], greedy(1))
+    with pytest.raises(ValueError, match="max_seq_len"):
+        scheduler.add_request(list(range(256)), greedy(1))
+    with pytest.raises(ValueError, match="pages"):
+        scheduler.add_request(list(range(100)), greedy(1))           # 7 pages > 4
+    roomy, _ = make(pages=64)
+    request = roomy.add_request(list(range(10)), SamplingParams(temperature=0.0, max_gen_len=None))
+    assert request.max_new_tokens == 246                                 # None fills the context
+
+
+def test_whole_prompts_only_when_chunking_is_off():
+    scheduler, executor = make(enable_chunked_prefill=False, max_num_batched_tokens=64)
+    scheduler.add_request(list(range(50)), greedy(1), "a")
+    scheduler.add_request(list(range(40)), greedy(1), "b")
+    scheduler.step()
+    assert executor.steps[-1] == [("a", 0, 50, True)]                 # b does not fit the budget whole
+    scheduler.step()
+    assert executor.steps[-1] == [("b", 0, 40, True)]
+
+
+def test_sampling_params_are_validated():
+    for bad in (dict(temperature=-1), dict(top_p=0), dict(top_p=1.5), dict(max_gen_len=0), dict(repetition_penalty=0)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+    assert SamplingParams().temperature == 0.6 and SamplingParams().top_p == 0.9 and SamplingParams().repetition_penalty == 1.1
+    assert SamplingParams(temperature=0).is_greedy
