@@ -1,0 +1,563 @@
+// bfloat16 matrix product of the linear layers on the sm_100a tensor cores:
+//   out[T, N] = x[T, K] . w[N, K]^T                      (plain)
+//   out[T, I] = silu(x . w[0:I]^T) * (x . w[I:2I]^T)     (fused SwiGLU over a [2I, K] weight)
+// float32 accumulation in tensor memory, one rounding at the store.
+//
+// The weight is the M side of the instruction: one tcgen05.mma covers 128 weight rows by
+// BN tokens (BN = 16 .. 256), so a decode step of a few tokens still fills the 128 lanes of
+// the tensor core and the kernel is a pure stream of the weight matrix.  Operands reach
+// shared memory through TMA in 128-byte-swizzled tiles of 64 k-elements (rows beyond T or N
+// and columns beyond K read as zeros), a ring of stages decouples the copy engine from the
+// tensor core, and the accumulator of a tile sits in one of two tensor-memory buffers so its
+// epilogue overlaps the next tile's products.  Roles: warp 0 issues TMA, warp 1 issues
+// tcgen05.mma (one elected thread each), warps 2..5 read the accumulators back
+// (tcgen05.ld), apply the epilogue and store.
+//
+// Few tokens mean few tiles (N / 128), too few to keep 148 SMs streaming.  The k-range of a
+// tile is then split over the CTAs of a thread-block cluster: each accumulates its slice in
+// tensor memory, parks the float32 partial tile in its own shared memory, and after a
+// cluster barrier every CTA sums a share of the tile's token columns over all ranks through
+// distributed shared memory, in rank order (so the sum does not depend on timing), and
+// stores it.  No global scratch, no atomics.  With many tokens the k-range is not split and a
+// CTA walks several tiles, the epilogue of one overlapping the products of the next.
+//
+// Launched with programmatic stream serialization, the kernel starts while its predecessor
+// in the stream drains: barriers, tensor memory and the first weight tiles (which no kernel
+// writes) are set up and in flight before griddepcontrol.wait lets it read the activations.
+//
+// The reference calls a library product here (rapid_llm/kernels/ops/gemm/linear.py:17-40)
+// and a separate SwiGLU kernel (rapid_llm/kernels/ops/activation/swiglu.py:91-121).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace rl {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int kTileN = 128;           // weight rows per tile = M of one tcgen05.mma
+constexpr int kTileK = 64;            // bf16 elements in one 128-byte swizzle row
+constexpr int kUmmaK = 16;            // k-elements of one tcgen05.mma of kind::f16
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct GemmArgs {
+  bf16* out;               // [T, N]
+  int* fault;
+  int T, N, K;
+  int up_offset;           // first "up" row of the weight (SwiGLU), else unused
+  int n_tiles, t_tiles, k_blocks;
+  int k_split;             // CTAs (= cluster size) that share one tile's k-range
+  int pdl;                 // launched with programmatic stream serialization
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t gemm_smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Waits for the phase of the given parity to complete; gives up after a bounded number of
+// tries, records that in the fault word and in the CTA's abort flag, and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* aborted,
+                                          int* fault) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && *aborted) return false;
+  }
+  *aborted = 1;
+  atomicOr(fault, kFaultWaitLimit);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t result_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem),
+               "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier once every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// 16 consecutive accumulator columns of this thread's lane.
+__device__ __forceinline__ void tmem_load16(uint32_t address, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(address));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Every thread of every CTA of the cluster arrives, then waits: shared-memory writes made
+// before are visible to the other CTAs after.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float load_cluster_f32(uint32_t local_address, uint32_t cta_rank) {
+  uint32_t remote;
+  float value;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+  return value;
+}
+// Programmatic dependent launch: let the next kernel of the stream start its prologue, and
+// wait for the previous kernel's results before touching them.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
+// eight rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_address) {
+  return static_cast<uint64_t>((smem_address & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+  return gate / (1.0f + __expf(-gate)) * up;
+}
+
+template <bool kSwiglu, int BN>
+struct GemmShape {
+  static constexpr int kHalves = kSwiglu ? 2 : 1;
+  static constexpr int kStageBytes = kHalves * kTileN * kTileK * 2 + BN * kTileK * 2;
+  // Small token tiles stream weights: three or more stages within 110 KB let two CTAs (or this
+  // kernel's and the next one's) share an SM.  Large token tiles get the whole SM.
+  static constexpr bool kShareSm = BN <= 64 && 3 * kStageBytes <= 110 * 1024;
+  static constexpr int kBudget = kShareSm ? 110 * 1024 : 200 * 1024;
+  static constexpr int kStagesFit = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int kAccColumns = kHalves * BN;          // per accumulator buffer
+  static constexpr int kTmemColumns = 2 * kAccColumns < 32 ? 32 : 2 * kAccColumns;
+  static constexpr int kPartialBytes = kHalves * BN * kTileN * 4;
+  static constexpr bool kCanSplit = BN <= 64 && kPartialBytes <= kStages * kStageBytes;
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+  static_assert(kTmemColumns <= 512 && (kTmemColumns & (kTmemColumns - 1)) == 0, "tensor memory");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "token tile");
+  static_assert(kStages >= 2, "pipeline depth");
+};
+
+// grid = (k_split, tile CTAs); with k_split > 1 the x dimension is one cluster and every CTA
+// has exactly one tile; otherwise a CTA walks the tiles blockIdx.y, blockIdx.y + gridDim.y, ...
+template <bool kSwiglu, int BN>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 const GemmArgs args) {
+  using Shape = GemmShape<kSwiglu, BN>;
+  constexpr int kStages = Shape::kStages, kHalves = Shape::kHalves;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                              (static_cast<uint32_t>(BN >> 3) << 17) |
+                              (static_cast<uint32_t>(kTileN >> 4) << 24);
+  extern __shared__ unsigned char gemm_smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full_bar[2], acc_empty_bar[2], drain_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int aborted_flag;
+  volatile int* aborted = &aborted_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (gemm_smem_u32(gemm_smem_raw) + 1023u) & ~1023u;
+  auto stage_a = [&](int s, int half) { return smem_base + s * Shape::kStageBytes + half * kTileN * kTileK * 2; };
+  auto stage_b = [&](int s) { return smem_base + s * Shape::kStageBytes + kHalves * kTileN * kTileK * 2; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(gemm_smem_u32(&full_bar[s]), 1);
+      mbar_init(gemm_smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(gemm_smem_u32(&acc_full_bar[b]), 1);
+      mbar_init(gemm_smem_u32(&acc_empty_bar[b]), 4);
+    }
+    mbar_init(gemm_smem_u32(&drain_bar), 1);
+    aborted_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(gemm_smem_u32(&tmem_base_slot), Shape::kTmemColumns);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  if (args.pdl && threadIdx.x == 0) pdl_launch_dependents();
+
+  // this CTA's slice of the k-blocks and its tiles
+  const int rank = blockIdx.x;
+  const int k_base = args.k_blocks / args.k_split, k_rem = args.k_blocks - k_base * args.k_split;
+  const int kb_begin = rank * k_base + min(rank, k_rem);
+  const int kb_count = k_base + (rank < k_rem ? 1 : 0);
+  const int tiles = args.n_tiles * args.t_tiles;
+  const int my_tiles = (tiles - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) /
+                       static_cast<int>(gridDim.y);
+  const long long total_iters = static_cast<long long>(my_tiles) * kb_count;
+  auto tile_of = [&](int index) { return static_cast<int>(blockIdx.y) + index * static_cast<int>(gridDim.y); };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      auto load_a = [&](long long it, int stage) {
+        const int tile = tile_of(static_cast<int>(it / kb_count));
+        const int kb = kb_begin + static_cast<int>(it % kb_count);
+        const int n_tile = tile / args.t_tiles;
+        const uint32_t bar = gemm_smem_u32(&full_bar[stage]);
+        mbar_expect_tx(bar, Shape::kStageBytes);
+        tma_load_2d(stage_a(stage, 0), &map_w, bar, kb * kTileK, n_tile * kTileN);
+        if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, kb * kTileK, args.up_offset + n_tile * kTileN);
+      };
+      auto load_b = [&](long long it, int stage) {
+        const int tile = tile_of(static_cast<int>(it / kb_count));
+        const int kb = kb_begin + static_cast<int>(it % kb_count);
+        const int t_tile = tile % args.t_tiles;
+        tma_load_2d(stage_b(stage), &map_x, gemm_smem_u32(&full_bar[stage]), kb * kTileK, t_tile * BN);
+      };
+      // weights first: nothing in the stream writes them, so they may fly before the
+      // previous kernel has finished; the activations only after
+      const int prefetch = static_cast<int>(min(static_cast<long long>(kStages), total_iters));
+      for (int it = 0; it < prefetch; ++it) load_a(it, it);
+      if (args.pdl) pdl_wait();
+      for (int it = 0; it < prefetch; ++it) load_b(it, it);
+      int stage = prefetch % kStages;
+      uint32_t phase = prefetch == kStages ? 1u : 0u;
+      bool ok = true;
+      long long filled = prefetch;                     // iterations whose copies were issued
+      for (long long it = prefetch; it < total_iters; ++it) {
+        ok = mbar_wait(gemm_smem_u32(&empty_bar[stage]), phase ^ 1u, aborted, args.fault);
+        if (!ok) break;
+        load_a(it, stage);
+        load_b(it, stage);
+        ++filled;
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok || *aborted) {
+        // copies still in flight must land before the CTA may exit: wait (bounded, like every
+        // wait here) for the last fill of every stage
+        for (int s = 0; s < kStages; ++s) {
+          const long long fills = (filled - s + kStages - 1) / kStages;   // fills of stage s so far
+          if (fills > 0)
+            mbar_wait(gemm_smem_u32(&full_bar[s]), static_cast<uint32_t>((fills - 1) & 1), aborted, args.fault);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ tensor-core issuer
+    if (lane == 0) {
+      int stage = 0, buf = 0;
+      uint32_t phase = 0, acc_phase[2] = {0, 0};
+      bool ok = kb_count > 0;
+      for (int index = 0; index < my_tiles && ok; ++index) {
+        ok = mbar_wait(gemm_smem_u32(&acc_empty_bar[buf]), acc_phase[buf] ^ 1u, aborted, args.fault);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * Shape::kAccColumns;
+        for (int kb = 0; kb < kb_count; ++kb) {
+          ok = mbar_wait(gemm_smem_u32(&full_bar[stage]), phase, aborted, args.fault);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t b_desc = operand_desc(stage_b(stage));
+#pragma unroll
+          for (int half = 0; half < kHalves; ++half) {
+            const uint64_t a_desc = operand_desc(stage_a(stage, half));
+#pragma unroll
+            for (int k = 0; k < kTileK / kUmmaK; ++k) {
+              // 32 bytes further along the swizzled row = +2 in the descriptor's address field
+              umma_bf16(d_tmem + half * BN, a_desc + 2 * k, b_desc + 2 * k, kIdesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(gemm_smem_u32(&empty_bar[stage]));   // the stage is free once these products retire
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(gemm_smem_u32(&acc_full_bar[buf]));
+        acc_phase[buf] ^= 1u;
+        buf ^= 1;
+      }
+      // nothing of this CTA may still be running on the tensor core when its memory is freed
+      umma_commit(gemm_smem_u32(&drain_bar));
+      mbar_wait(gemm_smem_u32(&drain_bar), 0, aborted, args.fault);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                       // the 32 tensor-memory lanes this warp may read
+    const int n_local = quarter * 32 + lane;
+    int buf = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    bool ok = kb_count > 0;
+    if (args.pdl) pdl_wait();                           // the output buffer may still be read upstream
+    for (int index = 0; index < my_tiles && ok; ++index) {
+      const int tile = tile_of(index);
+      const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
+      const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
+      ok = mbar_wait(gemm_smem_u32(&acc_full_bar[buf]), acc_phase[buf], aborted, args.fault);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * Shape::kAccColumns + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (args.k_split == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (t0 + c >= args.T) break;
+          float v[16];
+          tmem_load16(acc + c, v);
+          if (kSwiglu) {
+            float u[16];
+            tmem_load16(acc + BN + c, u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], u[j]);
+          }
+          if (n < args.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (t0 + c + j < args.T)
+                args.out[static_cast<size_t>(t0 + c + j) * args.N + n] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      } else if (Shape::kCanSplit) {
+        // park the partial tile in this CTA's shared memory: [halves * BN columns][128 rows]
+        float* mine = reinterpret_cast<float*>(gemm_smem_raw + (smem_base - gemm_smem_u32(gemm_smem_raw))) + n_local;
+#pragma unroll 1
+        for (int c = 0; c < kHalves * BN; c += 16) {
+          float v[16];
+          tmem_load16(acc + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(c + j) * kTileN] = v[j];
+        }
+      }
+      // the accumulator buffer may be overwritten from here on
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(gemm_smem_u32(&acc_empty_bar[buf]));
+      acc_phase[buf] ^= 1u;
+      buf ^= 1;
+    }
+  }
+
+  if (args.k_split > 1) {
+    // sum the partial tiles of the cluster's CTAs: rank r takes the token columns r, r + k_split, ...
+    __syncwarp();
+    cluster_sync();
+    if (warp >= 2 && Shape::kCanSplit && !*aborted) {
+      const int n_local = (warp & 3) * 32 + lane;
+      const int tile = static_cast<int>(blockIdx.y);
+      const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
+      const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
+      for (int j = rank; j < BN && t0 + j < args.T; j += args.k_split) {
+        float gate = 0.0f, up = 0.0f;
+        for (int q = 0; q < args.k_split; ++q) {
+          gate += load_cluster_f32(smem_base + (j * kTileN + n_local) * 4, q);
+          if (kSwiglu) up += load_cluster_f32(smem_base + ((BN + j) * kTileN + n_local) * 4, q);
+        }
+        if (n < args.N)
+          args.out[static_cast<size_t>(t0 + j) * args.N + n] =
+              __float2bfloat16_rn(kSwiglu ? silu_mul(gate, up) : gate);
+      }
+    }
+    __syncwarp();
+    cluster_sync();   // nobody leaves while its shared memory may still be read
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Shape::kTmemColumns);
+  }
+}
+
+// ----------------------------------------------------------------------------- host
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  }
+  return fn;
+}
+
+// A [rows, cols] row-major bf16 matrix read in boxes of box_rows x 64 with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
+}
+
+static int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+static bool g_gemm_configured[2][9] = {};   // [swiglu][BN / 32]; file-local on purpose
+
+template <bool kSwiglu, int BN>
+static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, GemmArgs args, int forced_split,
+                       cudaStream_t stream) {
+  using Shape = GemmShape<kSwiglu, BN>;
+  auto kernel = gemm_bf16_kernel<kSwiglu, BN>;
+  bool& configured = g_gemm_configured[kSwiglu ? 1 : 0][BN / 32];
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Shape::kSmemBytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  // how many CTAs the GPU holds at once, and how finely to split k so that they all stream
+  const int resident = sm_count() * (Shape::kShareSm ? 2 : 1);
+  const int tiles = args.n_tiles * args.t_tiles;
+  int split = 1;
+  if (Shape::kCanSplit) {
+    if (forced_split > 0) {
+      split = forced_split;
+    } else {
+      // the largest power of two (clusters of other sizes schedule poorly) that still lets
+      // every CTA be resident at once; 8 is the portable cluster limit
+      while (split < 8 && 2 * split * tiles <= resident) split *= 2;
+    }
+    if (split > args.k_blocks / 2) split = args.k_blocks / 2;   // at least two k-blocks per CTA
+    if (split < 1) split = 1;
+  }
+  args.k_split = split;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(split, split > 1 ? tiles : (tiles < resident ? tiles : resident));
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = Shape::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (split > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = split;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (args.pdl) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, args));
+}
+
+static int token_tile(int tokens, bool swiglu) {
+  if (tokens <= 16) return 16;
+  if (tokens <= 32) return 32;
+  if (tokens <= 64) return 64;
+  if (tokens <= 128 || swiglu) return 128;
+  return 256;
+}
+
+}  // namespace rl
+
+extern "C" {
+
+// x: [tokens, k], w: [n_out, k] (swiglu: [2 * n_out, k], gate rows first), out: [tokens, n_out];
+// all bfloat16, contiguous, 16-byte aligned, k a multiple of 8.  `pdl` launches with
+// programmatic stream serialization (the previous kernel of the stream must then be one that
+// tolerates an early successor; every kernel of this library does).  `k_split` forces the
+// number of CTAs per tile (0 = choose).
+int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
+                 int k_split, int* fault, cudaStream_t stream) {
+  if (tokens == 0 || n_out == 0) return 0;
+  if (tokens < 0 || n_out < 0 || k <= 0 || k % 8 != 0 || k_split < 0 || k_split > 8 ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int bn = rl::token_tile(tokens, swiglu != 0);
+  CUtensorMap map_w, map_x;
+  int status = rl::make_map(&map_w, w, static_cast<long long>(n_out) * (swiglu ? 2 : 1), k, rl::kTileN);
+  if (status != 0) return status;
+  status = rl::make_map(&map_x, x, tokens, k, bn);
+  if (status != 0) return status;
+  rl::GemmArgs args;
+  args.out = static_cast<rl::bf16*>(out);
+  args.fault = fault;
+  args.T = tokens; args.N = n_out; args.K = k;
+  args.up_offset = n_out;
+  args.n_tiles = (n_out + rl::kTileN - 1) / rl::kTileN;
+  args.t_tiles = (tokens + bn - 1) / bn;
+  args.k_blocks = (k + rl::kTileK - 1) / rl::kTileK;
+  args.k_split = 1;
+  args.pdl = pdl;
+#define RL_GEMM_CASE(SW, BNV) \
+  if ((swiglu != 0) == SW && bn == BNV) return rl::launch_gemm<SW, BNV>(map_w, map_x, args, k_split, stream);
+  RL_GEMM_CASE(false, 16) RL_GEMM_CASE(false, 32) RL_GEMM_CASE(false, 64) RL_GEMM_CASE(false, 128)
+  RL_GEMM_CASE(false, 256) RL_GEMM_CASE(true, 16) RL_GEMM_CASE(true, 32) RL_GEMM_CASE(true, 64)
+  RL_GEMM_CASE(true, 128)
+#undef RL_GEMM_CASE
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+}  // extern "C"

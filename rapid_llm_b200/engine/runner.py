@@ -24,6 +24,7 @@ from ..cache import CacheManager, CacheStorage, plan_groups
 from ..config import EngineConfig, load_config
 from ..models.causal_lm import CausalLM
 from ..ops import kernels
+from ..parts.base import StepShape
 from ..weights import fill_random_on_device, load_weights
 from .batch import GroupView, LayerCache, StepBatch, Workspace
 
@@ -86,7 +87,10 @@ class ModelRunner:
         self.workspace = Workspace(config.max_num_batched_tokens, self.device)
 
         t_max, n_max, g = config.max_num_batched_tokens, config.max_num_seqs + 1, len(groups)
-        self._meta_capacity = t_max * (4 + g) + 3 * n_max + 8
+        self._planners = model.step_planners()
+        self._meta_capacity = t_max * (4 + g) + 3 * n_max + 8 + sum(
+            planner.capacity(t_max, n_max) + 8 for planner in self._planners
+        )
         self._meta_host = [
             torch.empty(self._meta_capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)
         ]
@@ -216,6 +220,19 @@ class ModelRunner:
         cu_seqlens, entry_slot, entry_start = carve("cu_seqlens", n + 1), carve("entry_slot", n), carve("entry_start", n)
         kv_dest = [carve(f"kv_dest{i}", t) for i in range(g)]
         logit_rows = carve("logit_rows", rows)
+        shape = StepShape(
+            lengths=np.asarray(lengths + [1] * pad, dtype=np.int32),
+            starts=np.asarray(starts + [0] * pad, dtype=np.int32),
+            decode_only=max(lengths) == 1,
+        )
+        planned: dict[tuple, dict[str, Any]] = {}
+        for planner in self._planners:
+            plan = planner.plan(shape)
+            for name, value in plan.items():
+                if isinstance(value, np.ndarray):
+                    cursor = -(-cursor // 4) * 4          # 16-byte aligned arrays
+                    carve(f"plan:{planner.key}:{name}", value.size)[:] = value.reshape(-1)
+            planned[planner.key] = plan
         if cursor > self._meta_capacity:
             raise ValueError("the step's metadata does not fit its buffer")
 
@@ -253,6 +270,13 @@ class ModelRunner:
             begin, count = offsets[name]
             return self._meta_device[begin : begin + count]
 
+        extras = {
+            key: {
+                name: dev(f"plan:{key}:{name}").view(value.shape) if isinstance(value, np.ndarray) else value
+                for name, value in plan.items()
+            }
+            for key, plan in planned.items()
+        }
         ends = [start + length for start, length in zip(starts, lengths)]
         views = [
             GroupView(
@@ -283,6 +307,7 @@ class ModelRunner:
             fault=self.fault,
             dtype=self.dtype,
             decode_only=max(lengths) == 1,
+            extras=extras,
         )
 
     def layer_caches(self) -> list[LayerCache]:

@@ -74,6 +74,14 @@ class CausalLM:
     def state_needs(self) -> list[StateNeed | None]:
         return [self.layers[entry.layer].state_need() for entry in self.spec.schedule]
 
+    def step_planners(self) -> list:
+        """The distinct host-side planners of the layers (one per key)."""
+        planners: dict[tuple, object] = {}
+        for layer in self.layers:
+            for planner in layer.step_planners():
+                planners.setdefault(planner.key, planner)
+        return list(planners.values())
+
     # -- forward ------------------------------------------------------------------- #
     def forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""

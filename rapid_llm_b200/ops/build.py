@@ -36,7 +36,7 @@ COMMON_FLAGS = [
     "-fPIC",
 ]
 
-# library name -> its sources (relative to csrc/)
+# library name -> its sources (relative to csrc/); per-library flags in LIBRARY_FLAGS
 LIBRARIES: dict[str, list[str]] = {
     "core": [
         "elementwise.cu",
@@ -45,7 +45,25 @@ LIBRARIES: dict[str, list[str]] = {
         "gemm_f32.cu",
         "sampling.cu",
     ],
+    "gemm": ["gemm_bf16.cu"],
 }
+LIBRARY_FLAGS: dict[str, list[str]] = {}
+
+# head sizes whose attention library `build_all` compiles ahead of time; any other multiple
+# of 16 up to 256 is compiled when a model with that head size is first built
+DEFAULT_HEAD_DIMS = (64, 128)
+
+
+def attention_library(head_dim: int) -> str:
+    """Name of the tensor-core attention library specialised for one head size."""
+    head_dim = int(head_dim)
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise BuildError(f"the attention kernels take head sizes in steps of 16 up to 256, got {head_dim}")
+    name = f"attention_d{head_dim}"
+    if name not in LIBRARIES:
+        LIBRARIES[name] = ["attention_mma.cu"]
+        LIBRARY_FLAGS[name] = [f"-DRL_HEAD_DIM={head_dim}"]
+    return name
 
 _LOCK = threading.Lock()
 _LOADED: dict[str, ctypes.CDLL] = {}
@@ -144,7 +162,7 @@ def build_library(name: str, extra_flags: list[str] | None = None) -> Path:
     missing = [str(p) for p in sources if not p.is_file()]
     if missing:
         raise BuildError(f"kernel sources missing: {missing}")
-    flags = COMMON_FLAGS + list(extra_flags or [])
+    flags = COMMON_FLAGS + LIBRARY_FLAGS.get(name, []) + list(extra_flags or [])
     digest = _digest(sources, flags)
     ready = _existing(name, digest)
     if ready is not None:
@@ -189,4 +207,6 @@ def load_library(name: str) -> ctypes.CDLL:
 
 def build_all() -> list[Path]:
     """Compile every library (what ``__graft_entry__.build`` calls)."""
-    return [build_library(name) for name in LIBRARIES]
+    for head_dim in DEFAULT_HEAD_DIMS:
+        attention_library(head_dim)
+    return [build_library(name) for name in list(LIBRARIES)]

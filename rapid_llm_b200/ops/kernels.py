@@ -12,7 +12,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from .build import load_library
+from .build import attention_library, load_library
 
 F32, BF16 = 0, 1
 
@@ -296,6 +296,96 @@ def attention_generic(
     return out
 
 
+_ATTENTION_LIBS: dict[int, ctypes.CDLL] = {}
+
+CHUNK_TILE_ROWS = 64    # packed rows (token, head of the group) of a chunk tile
+DECODE_TILE_ROWS = 16   # ... of a decode tile
+
+
+def attention_lib(head_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention library of one head size, built at its first use."""
+    lib = _ATTENTION_LIBS.get(head_dim)
+    if lib is None:
+        lib = load_library(attention_library(head_dim))
+        lib.rl_attention_mma.argtypes = [
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+        ]
+        lib.rl_attention_mma.restype = c_int
+        if lib.rl_attention_head_dim() != head_dim:
+            raise KernelError(f"the attention library for head size {head_dim} was built for another size")
+        if lib.rl_attention_chunk_rows() != CHUNK_TILE_ROWS or lib.rl_attention_decode_rows() != DECODE_TILE_ROWS:
+            raise KernelError("the attention library's tile sizes differ from the host's")
+        _ATTENTION_LIBS[head_dim] = lib
+    return lib
+
+
+def attention_mma(
+    q: torch.Tensor,
+    cache: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    chunk_items: torch.Tensor | None,
+    decode_items: torch.Tensor | None,
+    splits: int,
+    part_out: torch.Tensor | None,
+    part_lse: torch.Tensor | None,
+    cu_seqlens: torch.Tensor,
+    entry_start: torch.Tensor,
+    entry_slot: torch.Tensor,
+    block_table: torch.Tensor,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    window: int,
+    scale: float,
+    fault: torch.Tensor,
+) -> torch.Tensor:
+    """bfloat16 paged causal attention over work items the host cut the step into.
+
+    ``chunk_items`` / ``decode_items`` are int32 ``[n, 4]`` rows ``(entry, first packed row,
+    split, 0)`` for tiles of :data:`CHUNK_TILE_ROWS` / :data:`DECODE_TILE_ROWS` packed rows
+    (row ``p`` of an entry is token ``p // group``, head ``p % group`` of each kv head).
+    With ``splits > 1`` every item exists once per split and ``part_out`` ``[T * Hq * splits,
+    D]`` / ``part_lse`` ``[T * Hq * splits]`` (float32) are scratch.
+    """
+    _need_cuda(q, cache, out, chunk_items, decode_items, part_out, part_lse, cu_seqlens, entry_start,
+               entry_slot, block_table, fault)
+    for name, tensor in (("q", q), ("cache", cache), ("out", out)):
+        _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
+    for name, tensor in (("chunk_items", chunk_items), ("decode_items", decode_items), ("cu_seqlens", cu_seqlens),
+                         ("entry_start", entry_start), ("entry_slot", entry_slot), ("block_table", block_table)):
+        _expect(name, tensor, torch.int32), _contig(name, tensor)
+    _expect("part_out", part_out, torch.float32), _expect("part_lse", part_lse, torch.float32)
+    width = num_heads * head_dim
+    if q.dim() != 2 or q.shape[1] != width or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [tokens, heads * head_dim]")
+    tokens = q.shape[0]
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    if num_heads % num_kv_heads:
+        raise KernelError("attention: heads must be a multiple of kv heads")
+    n_chunk = 0 if chunk_items is None else chunk_items.shape[0]
+    n_decode = 0 if decode_items is None else decode_items.shape[0]
+    if splits > 1:
+        need = tokens * num_heads * splits
+        if part_out is None or part_lse is None or part_out.numel() < need * head_dim or part_lse.numel() < need:
+            raise KernelError("attention: scratch for the split key ranges is missing or too small")
+    _check(
+        attention_lib(head_dim).rl_attention_mma(
+            _ptr(q), _ptr(cache), _ptr(out), _ptr(part_out), _ptr(part_lse), _ptr(chunk_items), n_chunk,
+            _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
+            _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
+            block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
+            _ptr(fault), _stream(),
+        ),
+        f"attention_mma(head_dim={head_dim})",
+    )
+    LAUNCHES.count += (1 if n_chunk and n_decode else 0) + (1 if splits > 1 else 0)
+    return out
+
+
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ w[N, K]^T`` in true float32."""
     _need_cuda(a, w, out, bias)
@@ -310,6 +400,53 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Te
         core().rl_gemm_f32(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), a.shape[0], w.shape[0], a.shape[1],
                            a.stride(0), out.stride(0), _stream()),
         "gemm_f32",
+    )
+    return out
+
+
+_GEMM_LIB: ctypes.CDLL | None = None
+PDL = False   # launch with programmatic stream serialization (set by the engine for its steps)
+
+
+def gemm_lib() -> ctypes.CDLL:
+    global _GEMM_LIB
+    if _GEMM_LIB is None:
+        lib = load_library("gemm")
+        lib.rl_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_void_p]
+        lib.rl_gemm_bf16.restype = c_int
+        _GEMM_LIB = lib
+    return _GEMM_LIB
+
+
+def gemm_bf16_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core product takes these operands (TMA wants 16-byte rows)."""
+    return x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor, *, swiglu: bool = False,
+              k_split: int = 0) -> torch.Tensor:
+    """``out[T, N] = x[T, K] @ w[N, K]^T`` in bfloat16 on the tcgen05 tensor cores.
+
+    With ``swiglu``, ``w`` is ``[2 N, K]`` (gate rows, then up rows) and
+    ``out = silu(x @ gate^T) * (x @ up^T)`` without the ``[T, 2 N]`` intermediate.
+    ``k_split`` forces how many CTAs share a tile's inner range (0 = the kernel chooses).
+    """
+    _need_cuda(x, w, out, fault)
+    for name, tensor in (("x", x), ("w", w), ("out", out)):
+        _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
+    tokens, k = x.shape
+    n_out = out.shape[1]
+    if w.shape != ((2 if swiglu else 1) * n_out, k) or out.shape[0] != tokens:
+        raise KernelError(f"gemm_bf16: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+    if not gemm_bf16_supports(x, w):
+        raise KernelError("gemm_bf16: the inner size must be a multiple of 8 and the operands 16-byte aligned")
+    if tokens == 0:
+        return out
+    _check(
+        gemm_lib().rl_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL),
+                                int(k_split), _ptr(fault), _stream()),
+        f"gemm_bf16({tokens}x{k} by {n_out})",
     )
     return out
 

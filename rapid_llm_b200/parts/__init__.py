@@ -17,11 +17,13 @@ from .base import (
     Part,
     PositionEncoding,
     StateNeed,
+    StepPlanner,
+    StepShape,
     TensorSpec,
 )
 
 __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS",
     "Block", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
-    "StateNeed", "TensorSpec",
+    "StateNeed", "StepPlanner", "StepShape", "TensorSpec",
 ]

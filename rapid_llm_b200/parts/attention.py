@@ -14,11 +14,68 @@ cache (``cache.writes`` false) projects queries only.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..config.model_spec import PartSpec
 from ..ops import gemm, kernels
-from .base import MATRIX, MIXERS, POSITION_ENCODINGS, VECTOR, CacheNeed, Mixer, TensorSpec
+from .base import (
+    MATRIX, MIXERS, POSITION_ENCODINGS, VECTOR, CacheNeed, Mixer, StepPlanner, StepShape, TensorSpec,
+)
+
+TARGET_CTAS = 2 * 148     # work items the attention kernels want in flight on a B200
+MAX_SPLITS = 16
+MIN_KEYS_PER_SPLIT = 256
+
+
+class AttentionItems(StepPlanner):
+    """Cuts a step into the work items of the tensor-core attention kernels.
+
+    Every entry's packed rows (token, head of the group) are tiled: entries of one token, or
+    of at most 16 packed rows, into decode tiles of 16 rows; the others into chunk tiles of
+    64.  When the tiles are too few to fill the GPU, each tile's key range is split into
+    ``splits`` parts (the same number for the whole step): a function of the number of
+    entries alone in a decode-only step, so that a captured decode graph replays the same
+    item list at every context length; bounded by the longest context otherwise.
+    The reference picks its split size per launch in the same spirit
+    (``rapid_llm/kernels/ops/attention/flashdecoding.py:43-112``).
+    """
+
+    def __init__(self, group: int, num_kv_heads: int) -> None:
+        self.group, self.num_kv_heads = int(group), int(num_kv_heads)
+        self.key = ("attention_items", self.group, self.num_kv_heads)
+
+    def capacity(self, max_tokens: int, max_entries: int) -> int:
+        chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
+        decode_tiles = max_entries * -(-self.group // kernels.DECODE_TILE_ROWS)
+        return 4 * (chunk_tiles + decode_tiles + 2 * TARGET_CTAS)
+
+    def plan(self, shape: StepShape) -> dict:
+        lengths = np.asarray(shape.lengths, dtype=np.int64)
+        rows = lengths * self.group
+        is_decode = (lengths == 1) | (rows <= kernels.DECODE_TILE_ROWS)
+        tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, kernels.CHUNK_TILE_ROWS)
+        tiles = -(-rows // tile_rows)
+        ctas = int(tiles.sum()) * self.num_kv_heads
+        splits = max(1, min(MAX_SPLITS, TARGET_CTAS // max(ctas, 1)))
+        if not shape.decode_only:
+            longest = int((np.asarray(shape.starts, dtype=np.int64) + lengths).max())
+            splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
+        entry = np.repeat(np.arange(len(lengths), dtype=np.int64), tiles)
+        first = np.concatenate(([0], np.cumsum(tiles)[:-1]))
+        tile_index = np.arange(int(tiles.sum()), dtype=np.int64) - np.repeat(first, tiles)
+        row0 = tile_index * np.repeat(tile_rows, tiles)
+        decode_tile = np.repeat(is_decode, tiles)
+
+        def items(mask: np.ndarray) -> np.ndarray:
+            count = int(mask.sum())
+            out = np.zeros((count * splits, 4), dtype=np.int32)
+            out[:, 0] = np.repeat(entry[mask], splits)
+            out[:, 1] = np.repeat(row0[mask], splits)
+            out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), count)
+            return out
+
+        return {"chunk_items": items(~decode_tile), "decode_items": items(decode_tile), "splits": splits}
 
 
 @MIXERS.register("gqa_attention")
@@ -50,6 +107,7 @@ class GQAAttention(Mixer):
         self.window = int(window)
         self.scale = float(scale) if scale is not None else self.d**-0.5
         self.shares_cache = bool(shares_cache)
+        self._items = AttentionItems(self.hq // self.hkv, self.hkv)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", self.d))
 
@@ -63,6 +121,11 @@ class GQAAttention(Mixer):
     def cache_need(self) -> CacheNeed | None:
         kind = "window" if self.window > 0 else "full"
         return CacheNeed(kind, self.hkv, self.d, self.window)
+
+    def step_planner(self) -> StepPlanner | None:
+        if self.dtype != torch.bfloat16:
+            return None      # the float32 path runs the one-warp-per-row kernel: no work list
+        return self._items
 
     # -- weights --------------------------------------------------------------- #
     def tensor_specs(self) -> dict[str, TensorSpec]:
@@ -112,7 +175,7 @@ class GQAAttention(Mixer):
         group = batch.groups[cache.group]
         rows = x.shape[0]
         qkv = batch.workspace.get("attn_qkv", rows, self.qkv.shape[0], x.dtype)
-        gemm.linear(x, self.qkv, qkv)
+        gemm.linear(x, self.qkv, qkv, batch.fault)
         q = batch.workspace.get("attn_q", rows, self.hq * self.d, x.dtype)
         cos, sin = self.position.tables()
         kernels.qk_norm_rope_write(
@@ -127,9 +190,26 @@ class GQAAttention(Mixer):
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
-        return gemm.linear(attended, self.o, out)
+        return gemm.linear(attended, self.o, out, batch.fault)
 
     def attend(self, q, pages, out, batch, group) -> None:
+        if q.dtype == torch.bfloat16:
+            plan = batch.extras[self._items.key]
+            splits = plan["splits"]
+            part_out = part_lse = None
+            if splits > 1:
+                rows = q.shape[0] * self.hq * splits
+                part_out = batch.workspace.get("attn_part_out", rows, self.d, torch.float32, min_rows=rows)
+                part_lse = batch.workspace.get("attn_part_lse", rows, 1, torch.float32, min_rows=rows)
+            kernels.attention_mma(
+                q, pages, out,
+                chunk_items=plan["chunk_items"], decode_items=plan["decode_items"], splits=splits,
+                part_out=part_out, part_lse=part_lse,
+                cu_seqlens=batch.cu_seqlens, entry_start=batch.entry_start, entry_slot=batch.entry_slot,
+                block_table=group.block_table, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
+                window=self.window, scale=self.scale, fault=batch.fault,
+            )
+            return
         kernels.attention_generic(
             q, pages, out,
             positions=batch.positions, token_slot=batch.token_slot, block_table=group.block_table,

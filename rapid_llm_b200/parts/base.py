@@ -10,8 +10,9 @@ seam through factory methods and class flags on the model skeleton
 Roles and what each must provide:
 
 * **Mixer** — ``forward(x, batch, cache) -> y`` over the packed tokens of a step;
-  ``cache_need()`` says which pages it wants (all keys, a window of them, none) and
-  ``state_need()`` which per-request state of fixed size.
+  ``cache_need()`` says which pages it wants (all keys, a window of them, none),
+  ``state_need()`` which per-request state of fixed size, and ``step_planner()`` may name
+  host-side planning it wants done once per step (work lists for its kernels).
 * **FeedForward** — ``forward(x, batch) -> y``.
 * **Norm** — ``forward(x, residual, batch, mode, ...) -> normed``; the residual stream is a
   float32 buffer the norm adds into.
@@ -73,6 +74,37 @@ class StateNeed:
     dtype: torch.dtype
 
 
+@dataclass(frozen=True)
+class StepShape:
+    """What the host knows about a step before it runs, for parts that plan work on the host.
+
+    ``lengths[i]`` tokens of entry ``i`` start at position ``starts[i]`` of its request;
+    padding rows of a captured decode batch are entries of one token at position 0.
+    """
+
+    lengths: Any          # numpy int32 [entries]
+    starts: Any           # numpy int32 [entries]
+    decode_only: bool
+
+
+class StepPlanner:
+    """Host-side work planning a part wants done once per step, before the metadata upload.
+
+    Parts that return planners with equal ``key`` share one plan.  ``plan`` returns int32
+    arrays (uploaded with the step's metadata and handed to the part as device tensors in
+    ``batch.extras[key]``) and plain Python values (handed over as they are).
+    """
+
+    key: tuple = ()
+
+    def capacity(self, max_tokens: int, max_entries: int) -> int:
+        """Most int32 words the arrays of one step can take."""
+        return 0
+
+    def plan(self, shape: StepShape) -> dict[str, Any]:
+        return {}
+
+
 class Part:
     """Base of every part: construction parameters and weights by checkpoint name."""
 
@@ -116,6 +148,9 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
+    def step_planner(self) -> StepPlanner | None:
+        return None
+
     def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
         raise NotImplementedError
 
@@ -141,6 +176,9 @@ class Block(Part):
 
     def state_need(self) -> StateNeed | None:
         return None
+
+    def step_planners(self) -> list[StepPlanner]:
+        return []
 
     def forward(self, x, residual, batch, cache):
         raise NotImplementedError

@@ -49,6 +49,10 @@ class PreNormBlock(Block):
     def state_need(self):
         return self.mixer.state_need()
 
+    def step_planners(self):
+        planner = self.mixer.step_planner()
+        return [] if planner is None else [planner]
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         specs = {}
         for prefix, part in self._children():

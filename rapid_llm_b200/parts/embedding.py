@@ -72,4 +72,4 @@ class LMHead(Part):
 
     def forward(self, hidden_rows: torch.Tensor, batch) -> torch.Tensor:
         out = batch.workspace.get("logits", hidden_rows.shape[0], self.vocab, hidden_rows.dtype, min_rows=64)
-        return gemm.linear(hidden_rows, self.weight, out)
+        return gemm.linear(hidden_rows, self.weight, out, batch.fault)

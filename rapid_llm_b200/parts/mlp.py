@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import gemm, kernels
+from ..ops import gemm
 from .base import FEED_FORWARDS, MATRIX, FeedForward, TensorSpec
 
 
@@ -48,9 +48,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
         rows = x.shape[0]
-        gate_up = batch.workspace.get("ffn_gate_up", rows, 2 * self.inter, x.dtype)
-        gemm.linear(x, self.gate_up, gate_up)
         act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)
-        kernels.silu_mul(gate_up, act)
+        gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault)
         out = batch.workspace.get("ffn_out", rows, self.hidden, x.dtype)
-        return gemm.linear(act, self.down, out)
+        return gemm.linear(act, self.down, out, batch.fault)

@@ -1,0 +1,63 @@
+"""The host-side cut of a step into attention work items: every packed row of every entry is
+covered exactly once per split, by a tile of the right kind."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from rapid_llm_b200.ops import kernels
+from rapid_llm_b200.parts.attention import MAX_SPLITS, TARGET_CTAS, AttentionItems
+from rapid_llm_b200.parts.base import StepShape
+
+
+def covered(items: np.ndarray, tile_rows: int, rows_of_entry: np.ndarray, splits: int) -> dict:
+    seen: dict[tuple[int, int, int], int] = {}
+    for entry, row0, split, _ in items.tolist():
+        assert 0 <= split < splits and row0 % tile_rows == 0 and row0 < rows_of_entry[entry]
+        for row in range(row0, min(row0 + tile_rows, int(rows_of_entry[entry]))):
+            seen[(entry, row, split)] = seen.get((entry, row, split), 0) + 1
+    return seen
+
+
+@pytest.mark.parametrize("group,kv_heads", [(1, 4), (2, 2), (4, 8), (6, 1), (20, 2)])
+@pytest.mark.parametrize("seed", range(5))
+def test_every_row_is_covered_once_per_split(group, kv_heads, seed):
+    rng = np.random.default_rng(seed)
+    entries = int(rng.integers(1, 9))
+    lengths = rng.choice([1, 1, 1, 2, 3, 16, 17, 100, 700], size=entries).astype(np.int32)
+    starts = rng.integers(0, 3000, size=entries).astype(np.int32)
+    planner = AttentionItems(group, kv_heads)
+    plan = planner.plan(StepShape(lengths, starts, decode_only=bool(lengths.max() == 1)))
+    splits = plan["splits"]
+    assert 1 <= splits <= MAX_SPLITS
+    rows = lengths.astype(np.int64) * group
+    seen = covered(plan["chunk_items"], kernels.CHUNK_TILE_ROWS, rows, splits)
+    for key, count in covered(plan["decode_items"], kernels.DECODE_TILE_ROWS, rows, splits).items():
+        seen[key] = seen.get(key, 0) + count
+    assert all(count == 1 for count in seen.values())
+    assert len(seen) == int(rows.sum()) * splits
+    words = 4 * (len(plan["chunk_items"]) + len(plan["decode_items"]))
+    assert words <= planner.capacity(int(lengths.sum()), entries)
+    for entry in plan["decode_items"][:, 0]:
+        assert lengths[entry] == 1 or rows[entry] <= kernels.DECODE_TILE_ROWS
+    for entry in plan["chunk_items"][:, 0]:
+        assert lengths[entry] > 1 and rows[entry] > kernels.DECODE_TILE_ROWS
+
+
+def test_a_decode_only_step_splits_by_the_number_of_entries_alone():
+    planner = AttentionItems(4, 8)
+    short = planner.plan(StepShape(np.ones(4, np.int32), np.full(4, 3, np.int32), decode_only=True))
+    long = planner.plan(StepShape(np.ones(4, np.int32), np.full(4, 7000, np.int32), decode_only=True))
+    assert short["splits"] == long["splits"] == min(MAX_SPLITS, TARGET_CTAS // (4 * 8))
+    assert np.array_equal(short["decode_items"], long["decode_items"])
+    full = planner.plan(StepShape(np.ones(64, np.int32), np.full(64, 1000, np.int32), decode_only=True))
+    assert full["splits"] == 1
+
+
+def test_short_contexts_are_not_split_in_a_mixed_step():
+    planner = AttentionItems(4, 8)
+    plan = planner.plan(StepShape(np.array([30, 1], np.int32), np.array([0, 100], np.int32), decode_only=False))
+    assert plan["splits"] == 1
+    plan = planner.plan(StepShape(np.array([30, 1], np.int32), np.array([4000, 100], np.int32), decode_only=False))
+    assert plan["splits"] > 1

@@ -111,6 +111,91 @@ def test_gemm_f32_rows_do_not_depend_on_the_batch():
         assert torch.equal(single[0], full[row])
 
 
+# ------------------------------------------------------------------- gemm bf16
+def bf16_product(x, w, n, swiglu):
+    ref = x.float() @ w.float().T
+    if swiglu:
+        ref = torch.nn.functional.silu(ref[:, :n]) * ref[:, n:]
+    return ref
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize(
+    "t,n,k_",
+    [(1, 128, 64), (5, 100, 72), (8, 384, 96), (16, 256, 4096), (3, 1000, 1000), (33, 160, 208), (64, 777, 136),
+     (100, 300, 200), (130, 256, 128), (300, 500, 264), (513, 130, 1024)],
+)
+def test_gemm_bf16(t, n, k_, swiglu):
+    """The tcgen05 product at sizes that are no multiple of any tile, plain and with the fused SwiGLU."""
+    x = rand((t, k_), torch.bfloat16, seed=20).to(DEV)
+    w = rand(((2 if swiglu else 1) * n, k_), torch.bfloat16, scale=0.05, seed=21).to(DEV)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16(x, w, out, fault, swiglu=swiglu)
+    assert fault.item() == 0
+    want = bf16_product(x, w, n, swiglu)
+    torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
+
+
+@pytest.mark.parametrize("split", [2, 4, 8])
+@pytest.mark.parametrize("t,n,k_,swiglu", [(8, 256, 4096, False), (33, 384, 1024, False), (64, 130, 12288, False),
+                                           (7, 160, 1000, True), (60, 256, 2048, True)])
+def test_gemm_bf16_inner_range_split_over_a_cluster(t, n, k_, swiglu, split):
+    """Partial tiles summed through distributed shared memory equal the unsplit product's
+    float32 sum up to the order of additions, and do not change from call to call."""
+    x = rand((t, k_), torch.bfloat16, seed=22).to(DEV)
+    w = rand(((2 if swiglu else 1) * n, k_), torch.bfloat16, scale=0.05, seed=23).to(DEV)
+    fault = fault_word()
+    outs = []
+    for _ in range(2):
+        out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        k().gemm_bf16(x, w, out, fault, swiglu=swiglu, k_split=split)
+        outs.append(out)
+    assert fault.item() == 0 and torch.equal(outs[0], outs[1])
+    want = bf16_product(x, w, n, swiglu)
+    torch.testing.assert_close(outs[0].float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
+
+
+def test_gemm_bf16_rows_do_not_depend_on_the_batch_beyond_rounding():
+    x = rand((40, 512), torch.bfloat16, seed=24).to(DEV)
+    w = rand((300, 512), torch.bfloat16, scale=0.05, seed=25).to(DEV)
+    fault = fault_word()
+    full = torch.empty((40, 300), dtype=torch.bfloat16, device=DEV)
+    k().gemm_bf16(x, w, full, fault)
+    single = torch.empty((1, 300), dtype=torch.bfloat16, device=DEV)
+    k().gemm_bf16(x[17:18].contiguous(), w, single, fault)
+    torch.testing.assert_close(single[0].float(), full[17].float(), rtol=1e-2, atol=2e-2)
+
+
+def test_gemm_bf16_under_programmatic_dependent_launch():
+    """With the early-start attribute set, a chain of products still sees its predecessor's output."""
+    kernels = k()
+    x = rand((8, 1024), torch.bfloat16, seed=26).to(DEV)
+    w1 = rand((1024, 1024), torch.bfloat16, scale=0.03, seed=27).to(DEV)
+    w2 = rand((512, 1024), torch.bfloat16, scale=0.03, seed=28).to(DEV)
+    fault = fault_word()
+    mid, out = torch.empty((8, 1024), dtype=torch.bfloat16, device=DEV), torch.empty((8, 512), dtype=torch.bfloat16, device=DEV)
+    kernels.PDL = True
+    try:
+        for _ in range(20):
+            kernels.gemm_bf16(x, w1, mid, fault)
+            kernels.gemm_bf16(mid, w2, out, fault)
+    finally:
+        kernels.PDL = False
+    assert fault.item() == 0
+    want_mid = (x.float() @ w1.float().T).to(torch.bfloat16)
+    want = want_mid.float() @ w2.float().T
+    torch.testing.assert_close(mid.float(), want_mid.float(), rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=3e-2)
+
+
+def test_gemm_bf16_refuses_rows_that_are_no_multiple_of_16_bytes():
+    kernels = k()
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_bf16(torch.zeros((4, 100), dtype=torch.bfloat16, device=DEV), torch.zeros((8, 100), dtype=torch.bfloat16, device=DEV),
+                          torch.zeros((4, 8), dtype=torch.bfloat16, device=DEV), fault_word())
+
+
 # ---------------------------------------------------- q/k norm + rope + cache write
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hkv,d,rotary,page", [(4, 2, 16, 16, 4), (6, 1, 48, 48, 8), (5, 5, 128, 64, 16), (3, 3, 256, 256, 1)])
@@ -183,7 +268,7 @@ def paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=0, key_scale=1
         "q": q.to(dtype), "cache": cache.to(dtype), "table": table,
         "positions": torch.tensor(positions, dtype=torch.int32),
         "token_slot": torch.tensor(token_slot, dtype=torch.int32),
-        "keys": keys, "values": values, "queries": queries,
+        "keys": keys, "values": values, "queries": queries, "slots": slot_ids,
     }
 
 
@@ -246,6 +331,96 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
         value = case["values"][0][far, 0].to(dtype).float()
         close = (first_head - value).abs().max() < 0.15
         assert bool(close) == expect_far
+
+
+def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None):
+    """The tensor-core kernels over the same paged case, items cut by the part's own planner."""
+    import numpy as np
+
+    from rapid_llm_b200.parts.attention import AttentionItems
+    from rapid_llm_b200.parts.base import StepShape
+
+    starts = [length - new for length, new in zip(lengths, new_counts)]
+    planner = AttentionItems(hq // hkv, hkv)
+    shape = StepShape(np.asarray(new_counts, dtype=np.int32), np.asarray(starts, dtype=np.int32),
+                      decode_only=max(new_counts) == 1)
+    plan = planner.plan(shape)
+    if splits is not None and splits != plan["splits"]:
+        def respread(items):
+            base = items[items[:, 2] == 0]
+            out = np.repeat(base, splits, axis=0)
+            out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), len(base))
+            return out
+        plan = {"chunk_items": respread(plan["chunk_items"]), "decode_items": respread(plan["decode_items"]), "splits": splits}
+    q = case["q"].to(DEV).reshape(-1, hq * d).contiguous()
+    out = torch.full_like(q, float("nan"))
+    tokens = q.shape[0]
+    count = plan["splits"]
+    part_out = part_lse = None
+    if count > 1:
+        part_out = torch.full((tokens * hq * count, d), float("nan"), dtype=torch.float32, device=DEV)
+        part_lse = torch.full((tokens * hq * count,), float("nan"), dtype=torch.float32, device=DEV)
+    cu = torch.tensor([0] + list(np.cumsum(new_counts)), dtype=torch.int32, device=DEV)
+    fault = fault_word()
+    k().attention_mma(
+        q, case["cache"].to(DEV), out,
+        chunk_items=torch.from_numpy(plan["chunk_items"]).to(DEV), decode_items=torch.from_numpy(plan["decode_items"]).to(DEV),
+        splits=count, part_out=part_out, part_lse=part_lse, cu_seqlens=cu,
+        entry_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
+        entry_slot=torch.tensor(case["slots"], dtype=torch.int32, device=DEV),
+        block_table=case["table"].to(DEV), num_heads=hq, num_kv_heads=hkv, head_dim=d,
+        window=window, scale=scale, fault=fault,
+    )
+    assert fault.item() == 0
+    return out.float().cpu().view(tokens, hq, d)
+
+
+@pytest.mark.parametrize(
+    "hq,hkv,d,page,window,splits",
+    [(8, 2, 128, 16, 0, None), (8, 2, 128, 16, 0, 3), (6, 1, 32, 8, 0, None), (7, 7, 48, 4, 0, 2),
+     (4, 2, 16, 16, 0, None), (3, 1, 256, 64, 0, None), (6, 3, 64, 16, 40, None), (6, 3, 64, 16, 40, 4),
+     (4, 4, 80, 1, 7, None), (10, 2, 96, 32, 33, 5), (40, 2, 64, 16, 0, None), (32, 8, 128, 16, 300, 2)],
+)
+def test_attention_mma(hq, hkv, d, page, window, splits):
+    """Chunk tiles and decode tiles in one launch, whole and with split key ranges."""
+    dtype = torch.bfloat16
+    lengths = [1, 15, 16, 17, 129, 200, 64, 700, 333]
+    new_counts = [1, 15, 1, 2, 129, 1, 33, 1, 70]
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=d + page)
+    scale = d**-0.5
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, window)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+def test_attention_mma_decode_only_step_splits_by_entry_count():
+    dtype, hq, hkv, d, page = torch.bfloat16, 8, 2, 128, 16
+    lengths, new_counts = [5, 1000, 64, 257], [1, 1, 1, 1]
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=1)
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, d**-0.5, 0)      # planner: 16 splits, most of them empty
+    want = plain_paged(case, dtype, lengths, new_counts, d**-0.5, 0)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+def test_attention_mma_finds_a_far_key_and_respects_the_window_edge():
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 2, 64, 16
+    length, far = 700, 13
+    for new in (1, 40):
+        case = paged_case(dtype, hq, hkv, d, page, [length], [new], seed=3)
+        query = case["queries"][0][-1]
+        for head in range(hkv):
+            case["keys"][0][far, head] = 40.0 * query[head * (hq // hkv)] / query[head * (hq // hkv)].norm()
+        page_id = int(case["table"][case["slots"][0], far // page])
+        case["cache"][page_id, 0, :, far % page] = case["keys"][0][far].to(dtype)
+        scale = d**-0.5
+        for window, expect_far in [(0, True), (length - far, True), (length - far - 1, False)]:
+            for splits in (None, 4):
+                got = run_mma(case, [length], [new], hq, hkv, d, scale, window, splits)
+                want = plain_paged(case, dtype, [length], [new], scale, window)
+                torch.testing.assert_close(got, want, **for_dtype(dtype))
+                value = case["values"][0][far, 0].to(dtype).float()
+                close = (got[-1, 0] - value).abs().max() < 0.15
+                assert bool(close) == expect_far
 
 
 # -------------------------------------------------------------------- sampling
