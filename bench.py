@@ -125,7 +125,10 @@ def decode_run(llm, batch: int, steps: int, warmup: int, seed: int) -> dict:
     from rapid_llm_b200.ops import kernels
 
     scheduler, runner = llm.scheduler, llm.runner
-    params = SamplingParams.greedy(max_gen_len=2 * (steps + warmup) + 8)
+    # every request must still be decoding when the last timed step runs: the prompts are
+    # prefilled two per step while the earlier requests already decode
+    prefill_steps = -(-batch * PROMPT_LEN // PREFILL_TOKENS)
+    params = SamplingParams.greedy(max_gen_len=2 * (steps + warmup) + prefill_steps + 8)
     vocab = runner.model.spec.vocab_size
     requests = [scheduler.add_request(p, params) for p in random_prompts(batch, PROMPT_LEN, vocab, seed)]
     while any(r.num_computed_tokens < len(r.prompt_token_ids) for r in requests):
@@ -196,7 +199,8 @@ def run_ours(args) -> dict:
     raw["num_hidden_layers"] = layers
     config = Qwen3Config.from_dict(raw)
     batches = sorted({1, args.batch, 64})
-    pages = max(batches) * (-(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 64) // PAGE)) + PREFILL_TOKENS // PAGE + 8
+    longest = PROMPT_LEN + 2 * (args.steps + args.warmup) + max(batches) * PROMPT_LEN // PREFILL_TOKENS + 64
+    pages = max(batches) * (-(-longest // PAGE)) + PREFILL_TOKENS // PAGE + 8
     engine = EngineConfig(
         dtype=torch.bfloat16, max_seq_len=CONTEXT, page_size=PAGE, num_pages=pages, max_num_seqs=max(batches),
         max_num_batched_tokens=max(PREFILL_TOKENS, 2048), max_chunk_size=2048, use_cuda_graph=True,
@@ -265,7 +269,64 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
-    return {"impl": "reference", "unavailable": "reference arm not wired yet"}
+    """The unmodified reference engine on the same workload, in a child process of its own.
+
+    The child (``baseline/reference_arm.py``) imports nothing of this package.  Any failure
+    (no offline install, a kernel of the reference that does not build or run on this GPU,
+    the time limit) yields the ``unavailable`` line instead of a number.
+    """
+    arm = ROOT / "baseline" / "reference_arm.py"
+    if not (ROOT / "baseline" / "_ref" / "rapid_llm").is_dir():
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+    command = [sys.executable, str(arm), "--steps", str(args.steps), "--warmup", str(args.warmup),
+               "--batch", str(args.batch)]
+    if args.layers:
+        command += ["--layers", str(args.layers)]
+    try:
+        with ClockSampler() as clocks:
+            done = subprocess.run(command, capture_output=True, text=True, timeout=args.reference_timeout)
+    except subprocess.TimeoutExpired:
+        return {"impl": "reference", "unavailable": f"the reference did not finish within {args.reference_timeout} s"}
+    lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+    if done.returncode != 0 or not lines:
+        tail = " | ".join((done.stderr or done.stdout).strip().splitlines()[-3:])[:400]
+        return {"impl": "reference", "unavailable": f"the reference engine failed here (exit {done.returncode}): {tail}"}
+    got = json.loads(lines[-1])
+    peaks = measured_peaks()
+    raw = dict(QWEN3_8B)
+    layers = got["layers"]
+    ms_per_step = got["device_ms"] / args.steps
+    value = got["tokens"] / (got["device_ms"] / 1000.0)
+    context_mean = PROMPT_LEN + args.warmup + args.steps / 2.0
+    step_bytes = weight_bytes_per_step(raw, layers) + args.batch * context_mean * kv_bytes_per_token(raw, layers)
+    achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
+    flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 1024-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / PUBLISHED_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": {
+            "model": "Qwen3-8B shape, random weights", "layers": layers, "layers_full": got["layers_full"],
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed per step)",
+            "engine": "rapid_llm.engine.Scheduler (stock path, CUDA graphs on)", "peaks": peaks["source"],
+            "finished_early": got["finished_early"],
+        },
+        "e2e": {"value": round(got["wall_tokens"] / (got["wall_ms"] / 1000.0), 1), "unit": "tok/s",
+                "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+        "prefill": {
+            "value": round(PREFILL_TOKENS / (got["prefill_ms"] / 1000.0), 1), "tokens": PREFILL_TOKENS,
+            "ms": round(got["prefill_ms"], 3),
+            "frac": round(flops / (got["prefill_ms"] / 1000.0) / (peaks["bf16_tflops"] * 1e12), 4),
+        },
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "clocks": clocks.summary(),
+    }
 
 
 def main() -> int:
@@ -276,6 +337,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (work on several GPUs is out of scope)")
