@@ -22,6 +22,9 @@
 // sum and the output accumulator are float32; the exponent is taken in base 2 with log2(e)
 // folded into the scale; P is rounded to bfloat16 before the P.V product, as the
 // reference's tensor-core kernels do (flashattention2_nopad.py:162).
+#include <mutex>
+
+#include "attention_static_scratch.h"
 #include "common.cuh"
 
 #ifndef RL_HEAD_DIM
@@ -504,6 +507,96 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
     status = static_cast<int>(cudaGetLastError());
   }
   return status;
+}
+
+}  // extern "C"
+
+// ----------------------------------------------------------------------------------------
+// Allocation-free variant (declared and explained in attention_static_scratch.h; the
+// reference has nothing like it).  The scratch of the split key ranges lives in the library
+// image instead of in memory the caller allocates.
+namespace rl {
+namespace RL_ATTENTION_NS {
+
+constexpr long long kStaticScratchFloats = 1ll << 20;   // 4 MiB per GPU that loads this library
+constexpr int kStaticScratchMaxDevices = 64;
+
+// Device memory.  In host code this name is only a handle for cudaGetSymbolAddress: it is
+// not a device address and must never be handed to a kernel as one.
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+static std::mutex g_static_scratch_mutex;
+static float* g_static_scratch_address[kStaticScratchMaxDevices] = {};   // per device, looked up once
+
+// The array's address on the current device; the first call on a device asks the runtime.
+static int static_scratch_address(float** address) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device < 0 || device >= kStaticScratchMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+  std::lock_guard<std::mutex> guard(g_static_scratch_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* found = nullptr;
+    e = cudaGetSymbolAddress(&found, g_static_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (found == nullptr) return static_cast<int>(cudaErrorInvalidSymbol);
+    g_static_scratch_address[device] = static_cast<float*>(found);
+  }
+  *address = g_static_scratch_address[device];
+  return 0;
+}
+
+// lse[i] = -inf: a (row, split) slot that no work item of this call writes then weighs
+// nothing in the merge, whatever an earlier call left there.
+__global__ void static_scratch_reset_kernel(float* __restrict__ lse, long long count) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < count) lse[i] = -INFINITY;
+}
+
+}  // namespace RL_ATTENTION_NS
+}  // namespace rl
+
+extern "C" {
+
+long long rl_attention_static_scratch_bytes(void) {
+  return attn::kStaticScratchFloats * static_cast<long long>(sizeof(float));
+}
+
+const char* rl_attention_static_scratch_strerror(int code) {
+  if (code == 0) return "success";
+  if (code == RL_ATTENTION_STATIC_SCRATCH_TOO_LARGE)
+    return "tokens * hq * splits * (head_dim + 1) floats exceed the library's built-in scratch array "
+           "(rl_attention_static_scratch_bytes); use fewer splits or tokens per call, or rl_attention_mma "
+           "with buffers of your own";
+  return cudaGetErrorString(static_cast<cudaError_t>(code));
+}
+
+int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out, const int* chunk_items,
+                                    int n_chunk_items, const int* decode_items, int n_decode_items,
+                                    const int* cu_seqlens, const int* entry_start, const int* entry_slot,
+                                    const int* block_table, int tokens, int hq, int hkv, int head_dim,
+                                    int page_size, int num_pages, int max_pages, int slots, int window,
+                                    int splits, float scale, int* fault, cudaStream_t stream) {
+  if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
+  if (tokens < 0 || hq <= 0 || splits < 1 || head_dim != attn::kD)
+    return static_cast<int>(cudaErrorInvalidValue);
+  float* part_out = nullptr;
+  float* part_lse = nullptr;
+  if (splits > 1) {
+    const long long rows = static_cast<long long>(tokens) * hq * splits;
+    if (rows > attn::kStaticScratchFloats / (attn::kD + 1)) return RL_ATTENTION_STATIC_SCRATCH_TOO_LARGE;
+    float* scratch = nullptr;
+    const int status = attn::static_scratch_address(&scratch);
+    if (status != 0) return status;
+    part_out = scratch;                        // [rows, D]
+    part_lse = scratch + rows * attn::kD;      // [rows]
+    attn::static_scratch_reset_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, stream>>>(part_lse, rows);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
+                          n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, stream);
 }
 
 }  // extern "C"
