@@ -50,6 +50,8 @@ class EngineConfig:
         memory_fraction: Share of the device's memory the cache may claim when
             ``num_pages`` is ``None``.
         use_cuda_graph: Replay decode-only steps from captured graphs.
+        use_dependent_launch: Launch the step's kernels as programmatic dependents of one
+            another, so that each starts (and fetches its weights) while its predecessor drains.
     """
 
     dtype: torch.dtype = torch.bfloat16
@@ -63,6 +65,7 @@ class EngineConfig:
     enable_preemption: bool = True
     memory_fraction: float = 0.9
     use_cuda_graph: bool = True
+    use_dependent_launch: bool = True
 
     def __post_init__(self) -> None:
         parse_dtype(self.dtype)

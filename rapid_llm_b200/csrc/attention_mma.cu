@@ -115,6 +115,7 @@ attention_mma_kernel(const AttentionArgs args) {
   bf16* k_smem = q_smem + kTileM * kStride;                            // [kStages][64][kStride]
   bf16* v_smem = k_smem + kStages * kBlockN * kStride;                 // [kStages][64][kStride]
 
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp % kWarpsM, wn = warp / kWarpsM;
   const int* item = args.items + static_cast<size_t>(blockIdx.x) * 4;
@@ -198,6 +199,7 @@ attention_mma_kernel(const AttentionArgs args) {
     }
   };
 
+  pdl_wait();   // queries and this step's keys come from the kernels before
   load_q();
 #pragma unroll
   for (int s = 0; s < kStages - 1; ++s) {
@@ -407,6 +409,8 @@ attention_mma_kernel(const AttentionArgs args) {
 __global__ void attention_merge_kernel(const float* __restrict__ part_out,
                                        const float* __restrict__ part_lse, bf16* __restrict__ out,
                                        long long rows, int splits) {
+  pdl_trigger();
+  pdl_wait();
   const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -433,7 +437,7 @@ constexpr size_t attention_smem_bytes() {
 static bool g_configured[2] = {false, false};   // [chunk tiles, decode tiles]; file-local on purpose
 
 template <int kWarpsM, int kWarpsN, int kStages>
-int launch_attention(const AttentionArgs& args, int n_items, cudaStream_t stream) {
+int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStream_t stream) {
   auto kernel = attention_mma_kernel<kWarpsM, kWarpsN, kStages>;
   constexpr size_t smem = attention_smem_bytes<kWarpsM, kWarpsN, kStages>();
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
@@ -444,8 +448,7 @@ int launch_attention(const AttentionArgs& args, int n_items, cudaStream_t stream
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  kernel<<<dim3(n_items, args.hkv), kThreads, smem, stream>>>(args);
-  return static_cast<int>(cudaGetLastError());
+  return launch_kernel(kernel, dim3(n_items, args.hkv), dim3(kThreads), smem, stream, pdl, args);
 }
 
 }  // namespace RL_ATTENTION_NS
@@ -469,7 +472,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      int n_decode_items, const int* cu_seqlens, const int* entry_start,
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
-                     int window, int splits, float scale, int* fault, cudaStream_t stream) {
+                     int window, int splits, float scale, int* fault, int pdl, cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
@@ -492,19 +495,18 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   int status = 0;
   if (n_chunk_items > 0) {
     args.items = chunk_items;
-    status = attn::launch_attention<4, 1, 2>(args, n_chunk_items, stream);
+    status = attn::launch_attention<4, 1, 2>(args, n_chunk_items, pdl != 0, stream);
     if (status != 0) return status;
   }
   if (n_decode_items > 0) {
     args.items = decode_items;
-    status = attn::launch_attention<1, 4, 3>(args, n_decode_items, stream);
+    status = attn::launch_attention<1, 4, 3>(args, n_decode_items, pdl != 0, stream);
     if (status != 0) return status;
   }
   if (splits > 1) {
     const long long rows = static_cast<long long>(tokens) * hq;
-    attn::attention_merge_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, 0, stream>>>(
-        part_out, part_lse, static_cast<attn::bf16*>(out), rows, splits);
-    status = static_cast<int>(cudaGetLastError());
+    status = rl::launch_kernel(attn::attention_merge_kernel, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0,
+                               stream, pdl != 0, part_out, part_lse, static_cast<attn::bf16*>(out), rows, splits);
   }
   return status;
 }
@@ -596,7 +598,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, stream);
 }
 
 }  // extern "C"

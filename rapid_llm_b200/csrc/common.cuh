@@ -93,6 +93,35 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&out)[8]) {
 
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// A kernel launched with `pdl` may start while the kernel before it in the stream is still
+// running.  Every kernel of this library therefore follows one discipline: it lets its own
+// successor start early (pdl_trigger, first thing), touches before pdl_wait() only memory
+// that no kernel of a step writes (weights, tables, the step's uploaded metadata), and calls
+// pdl_wait() — which returns once the preceding kernel has finished and its writes are
+// visible — before it reads an activation or writes anything at all.  Because every kernel
+// waits before it finishes, "the kernel before me is done" implies that all earlier ones
+// are.  Both instructions do nothing in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launches `kernel`; with `pdl` as a programmatic dependent of the stream's previous kernel.
+template <typename... Params, typename... Args>
+inline int launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = pdl ? 1 : 0;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...));
+}
+
 }  // namespace rl
 
 // Calls `fn<float>` or `fn<__nv_bfloat16>` by a DType tag; returns cudaErrorInvalidValue otherwise.

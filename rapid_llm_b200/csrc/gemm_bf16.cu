@@ -150,12 +150,6 @@ __device__ __forceinline__ float load_cluster_f32(uint32_t local_address, uint32
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
   return value;
 }
-// Programmatic dependent launch: let the next kernel of the stream start its prologue, and
-// wait for the previous kernel's results before touching them.
-__device__ __forceinline__ void pdl_launch_dependents() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
 // eight rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
@@ -231,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  if (args.pdl && threadIdx.x == 0) pdl_launch_dependents();
+  if (args.pdl && threadIdx.x == 0) pdl_trigger();
 
   // this CTA's slice of the k-blocks and its tiles
   const int rank = blockIdx.x;

@@ -16,85 +16,168 @@ namespace rl {
 constexpr int kRopeWarps = 4;
 constexpr int kMaxHeadDim = 256;
 
-template <typename T>
-__global__ void qk_norm_rope_write_kernel(
-    const T* __restrict__ qkv,          // [tokens, row_width]: q heads, then k heads, then v heads
-    const float* __restrict__ bias,     // [(hq + 2 hkv) * d] or null
-    const float* __restrict__ q_weight, // [d] or null (no q/k norm)
-    const float* __restrict__ k_weight, // [d] or null
-    const float* __restrict__ cos_table,  // [max_pos, rotary/2]
-    const float* __restrict__ sin_table,
-    const int* __restrict__ positions,  // [tokens]
-    const int* __restrict__ kv_dest,    // [tokens] page * page_size + offset, or null (q only)
-    T* __restrict__ q_out,              // [tokens, hq, d]
-    T* __restrict__ cache,              // layer cache or null
-    int tokens, int row_width, int hq, int hkv, int d, int rotary, int max_pos, int page_size,
-    int num_pages, float eps, int* __restrict__ fault) {
-  __shared__ float staged[kRopeWarps][kMaxHeadDim];
+struct RopeArgs {
+  const void* qkv;          // [tokens, row_width]: q heads, then k heads, then v heads
+  const float* bias;        // [(hq + 2 hkv) * d] or null
+  const float* q_weight;    // [d] or null (no q/k norm)
+  const float* k_weight;    // [d] or null
+  const float* cos_table;   // [max_pos, rotary/2]
+  const float* sin_table;
+  const int* positions;     // [tokens]
+  const int* kv_dest;       // [tokens] page * page_size + offset, or null (q only)
+  void* q_out;              // [tokens, hq, d]
+  void* cache;              // layer cache or null
+  int tokens, row_width, hq, hkv, d, rotary, max_pos, page_size, num_pages;
+  float eps;
+  int* fault;
+};
+
+// One warp per (token, head).  kVec > 0: the head size is 32 * kVec, the whole head rotates
+// (rotary == d), and lane l holds the kVec consecutive elements from l * kVec in registers;
+// its rotation partner (element + d/2) sits in lane l ^ 16.  kVec == 0: any head size up to
+// 256 and any even rotary width, element by element through shared memory.
+template <typename T, int kVec>
+__global__ void qk_norm_rope_write_kernel(const RopeArgs a) {
+  __shared__ float staged[kVec == 0 ? kRopeWarps : 1][kVec == 0 ? kMaxHeadDim : 1];
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads_per_token = kv_dest ? hq + 2 * hkv : hq;
+  const int heads_per_token = a.kv_dest ? a.hq + 2 * a.hkv : a.hq;
   const long long item = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
-  if (item >= static_cast<long long>(tokens) * heads_per_token) return;
-  const int t = static_cast<int>(item / heads_per_token);
-  const int head = static_cast<int>(item - static_cast<long long>(t) * heads_per_token);
-  const T* src = qkv + static_cast<size_t>(t) * row_width + static_cast<size_t>(head) * d;
-  const float* b = bias ? bias + static_cast<size_t>(head) * d : nullptr;
-
-  // 0 = q, 1 = k, 2 = v
-  const int kind = head < hq ? 0 : (head < hq + hkv ? 1 : 2);
-  T* dst = nullptr;
-  if (kind == 0) {
-    dst = q_out + (static_cast<size_t>(t) * hq + head) * d;
-  } else {
-    const int kv_head = kind == 1 ? head - hq : head - hq - hkv;
-    const int dest = kv_dest[t];
-    const int page = dest / page_size, offset = dest - page * page_size;
-    if (dest < 0 || page >= num_pages) {
-      if (lane == 0) atomicOr(fault, kFaultPageId);
-      return;
-    }
-    dst = cache +
-          ((((static_cast<size_t>(page) * 2 + (kind - 1)) * hkv + kv_head) * page_size) + offset) * d;
-  }
-
-  float* mine = staged[warp];
-  float sum_sq = 0.0f;
-  for (int i = lane; i < d; i += 32) {
-    float v = to_float(src[i]);
-    if (b) v += b[i];
-    mine[i] = v;
-    sum_sq += v * v;
-  }
-  if (kind == 2) {
-    __syncwarp();
-    for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(mine[i]);
+  if (item >= static_cast<long long>(a.tokens) * heads_per_token) {
+    pdl_wait();
     return;
   }
-  const float* w = kind == 0 ? q_weight : k_weight;
-  if (w) {
-    sum_sq = warp_sum(sum_sq);
-    const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + eps);
-    for (int i = lane; i < d; i += 32) mine[i] = mine[i] * inv_rms * w[i];
+  const int d = a.d;
+  const int t = static_cast<int>(item / heads_per_token);
+  const int head = static_cast<int>(item - static_cast<long long>(t) * heads_per_token);
+  const T* src = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
+  const float* b = a.bias ? a.bias + static_cast<size_t>(head) * d : nullptr;
+
+  // 0 = q, 1 = k, 2 = v
+  const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);
+  T* dst = nullptr;
+  bool bad_page = false;
+  if (kind == 0) {
+    dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
+  } else {
+    const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+    const int dest = a.kv_dest[t];
+    const int page = dest / a.page_size, offset = dest - page * a.page_size;
+    if (dest < 0 || page >= a.num_pages) {
+      if (lane == 0) atomicOr(a.fault, kFaultPageId);
+      bad_page = true;
+    } else {
+      dst = static_cast<T*>(a.cache) +
+            ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
+    }
   }
-  __syncwarp();
-  int pos = positions[t];
-  if (pos < 0 || pos >= max_pos) {
-    if (lane == 0) atomicOr(fault, kFaultPosition);
+  int pos = a.positions[t];
+  if (kind != 2 && (pos < 0 || pos >= a.max_pos)) {
+    if (lane == 0) atomicOr(a.fault, kFaultPosition);
     pos = 0;
   }
-  const int half = rotary >> 1;
-  const float* c = cos_table + static_cast<size_t>(pos) * half;
-  const float* s = sin_table + static_cast<size_t>(pos) * half;
-  for (int i = lane; i < d; i += 32) {
-    float v;
-    if (i < half) {
-      v = mine[i] * c[i] - mine[i + half] * s[i];
-    } else if (i < rotary) {
-      v = mine[i] * c[i - half] + mine[i - half] * s[i - half];
-    } else {
-      v = mine[i];
+  const float* w = kind == 0 ? a.q_weight : (kind == 1 ? a.k_weight : nullptr);
+  const int half = a.rotary >> 1;
+
+  if constexpr (kVec > 0) {
+    const int at = lane * kVec;
+    float v[kVec], wv[kVec], c[kVec], s[kVec];
+    const int angle = at < half ? at : at - half;      // kVec divides d / 2, so a lane never straddles
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      wv[i] = w ? w[at + i] : 1.0f;
+      c[i] = kind == 2 ? 1.0f : a.cos_table[static_cast<size_t>(pos) * half + angle + i];
+      s[i] = kind == 2 ? 0.0f : a.sin_table[static_cast<size_t>(pos) * half + angle + i];
     }
-    dst[i] = from_float<T>(v);
+    pdl_wait();
+    if (bad_page) return;
+    if constexpr (kVec == 8) {
+      load8(src + at, v);
+    } else if constexpr (sizeof(T) == 2 && kVec == 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src + at);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+      v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) v[i] = to_float(src[at + i]);
+    }
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      if (b) v[i] += b[at + i];
+      sum_sq += v[i] * v[i];
+    }
+    if (kind != 2) {
+      if (w) {
+        sum_sq = warp_sum(sum_sq);
+        const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) v[i] = v[i] * inv_rms * wv[i];
+      }
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        // first half: x1 * c - x2 * s; second half: x2 * c + x1 * s
+        v[i] = lane < 16 ? v[i] * c[i] - other * s[i] : v[i] * c[i] + other * s[i];
+      }
+    }
+    if constexpr (kVec == 8) {
+      if constexpr (sizeof(T) == 2) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst + at) = raw;
+      } else {
+        *reinterpret_cast<float4*>(dst + at) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(dst + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else if constexpr (sizeof(T) == 2 && kVec == 4) {
+      uint2 raw;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+      h[0] = __floats2bfloat162_rn(v[0], v[1]);
+      h[1] = __floats2bfloat162_rn(v[2], v[3]);
+      *reinterpret_cast<uint2*>(dst + at) = raw;
+    } else {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) dst[at + i] = from_float<T>(v[i]);
+    }
+  } else {
+    pdl_wait();
+    if (bad_page) return;
+    float* mine = staged[warp];
+    float sum_sq = 0.0f;
+    for (int i = lane; i < d; i += 32) {
+      float v = to_float(src[i]);
+      if (b) v += b[i];
+      mine[i] = v;
+      sum_sq += v * v;
+    }
+    if (kind == 2) {
+      __syncwarp();
+      for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(mine[i]);
+      return;
+    }
+    if (w) {
+      sum_sq = warp_sum(sum_sq);
+      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+      for (int i = lane; i < d; i += 32) mine[i] = mine[i] * inv_rms * w[i];
+    }
+    __syncwarp();
+    const float* c = a.cos_table + static_cast<size_t>(pos) * half;
+    const float* s = a.sin_table + static_cast<size_t>(pos) * half;
+    for (int i = lane; i < d; i += 32) {
+      float v;
+      if (i < half) {
+        v = mine[i] * c[i] - mine[i + half] * s[i];
+      } else if (i < a.rotary) {
+        v = mine[i] * c[i - half] + mine[i - half] * s[i - half];
+      } else {
+        v = mine[i];
+      }
+      dst[i] = from_float<T>(v);
+    }
   }
 }
 
@@ -106,7 +189,7 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
                                      const int* positions, const int* kv_dest, void* q_out,
                                      void* cache, int tokens, int hq, int hkv, int d, int rotary,
                                      int max_pos, int page_size, int num_pages, float eps,
-                                     int* fault, cudaStream_t stream) {
+                                     int* fault, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (d > rl::kMaxHeadDim || d <= 0 || rotary < 0 || rotary > d || (rotary & 1) ||
       (kv_dest != nullptr && cache == nullptr))
@@ -114,11 +197,23 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
   const long long items =
       static_cast<long long>(tokens) * (kv_dest ? hq + 2 * hkv : hq);
   const unsigned blocks = static_cast<unsigned>((items + rl::kRopeWarps - 1) / rl::kRopeWarps);
+  rl::RopeArgs a;
+  a.qkv = qkv; a.bias = bias; a.q_weight = q_weight; a.k_weight = k_weight;
+  a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.kv_dest = kv_dest;
+  a.q_out = q_out; a.cache = cache; a.tokens = tokens; a.row_width = row_width; a.hq = hq; a.hkv = hkv;
+  a.d = d; a.rotary = rotary; a.max_pos = max_pos; a.page_size = page_size; a.num_pages = num_pages;
+  a.eps = eps; a.fault = fault;
+  // registers when the whole head rotates, a lane's elements are whole vectors and everything is aligned
+  const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                         reinterpret_cast<uintptr_t>(cache)) & 15) == 0 && row_width % 8 == 0;
+  const int vec = (rotary == d && d % 32 == 0 && aligned) ? d / 32 : 0;
+  const dim3 grid(blocks), block(rl::kRopeWarps * 32);
   RL_DISPATCH_DTYPE(dtype, {
-    rl::qk_norm_rope_write_kernel<scalar_t><<<blocks, rl::kRopeWarps * 32, 0, stream>>>(
-        static_cast<const scalar_t*>(qkv), bias, q_weight, k_weight, cos_table, sin_table,
-        positions, kv_dest, static_cast<scalar_t*>(q_out), static_cast<scalar_t*>(cache), tokens,
-        row_width, hq, hkv, d, rotary, max_pos, page_size, num_pages, eps, fault);
+    if (vec == 8) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 8>, grid, block, 0, stream, pdl != 0, a);
+    if (vec == 4) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 4>, grid, block, 0, stream, pdl != 0, a);
+    if (vec == 2) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 2>, grid, block, 0, stream, pdl != 0, a);
+    if (vec == 1) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 1>, grid, block, 0, stream, pdl != 0, a);
+    return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 0>, grid, block, 0, stream, pdl != 0, a);
   });
-  return rl::launch_status();
+  return 0;
 }

@@ -92,8 +92,10 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
   __shared__ float fscratch[32];
   __shared__ int iscratch[32];
   __shared__ float warp_totals[32];
+  pdl_trigger();
   const int row = blockIdx.x;
   const T* x = logits + static_cast<size_t>(row) * row_stride;
+  pdl_wait();
   const float temp = temperature ? temperature[row] : 0.0f;
   const float pen = penalty ? penalty[row] : 1.0f;
   const int seen_begin = seen_offsets ? seen_offsets[row] : 0;
@@ -117,7 +119,24 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
 
   // Greedy pick: needed for greedy rows and as the fallback of the draw.
   MaxIndex best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  // rows that start on a 16-byte boundary are read eight elements at a time; a thread still
+  // meets its indices in rising order, so its strict comparison keeps the first maximum
+  const bool vector = (reinterpret_cast<uintptr_t>(x) & (sizeof(T) == 2 ? 15 : 31)) == 0;
+  const int vector_end = vector ? (vocab & ~7) : 0;
+  for (int c = threadIdx.x * 8; c < vector_end; c += blockDim.x * 8) {
+    float v[8];
+    load8(x + c, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float e = v[j];
+      if (has_pen && ((seen_bits[(c + j) >> 5] >> ((c + j) & 31)) & 1u)) e = e < 0.0f ? e * pen : e / pen;
+      if (e > best.value) {
+        best.value = e;
+        best.index = c + j;
+      }
+    }
+  }
+  for (int i = vector_end + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = value(i);
     if (v > best.value) {
       best.value = v;
@@ -220,7 +239,7 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
 extern "C" int rl_sample(int dtype, const void* logits, int rows, int vocab, long long row_stride,
                          const float* temperature, const float* top_p, const float* penalty,
                          const unsigned long long* seeds, const int* counters,
-                         const int* seen_tokens, const int* seen_offsets, int* out,
+                         const int* seen_tokens, const int* seen_offsets, int* out, int pdl,
                          cudaStream_t stream) {
   if (rows == 0) return 0;
   if (vocab <= 0 || (temperature != nullptr && (seeds == nullptr || counters == nullptr)))
@@ -235,9 +254,9 @@ extern "C" int rl_sample(int dtype, const void* logits, int rows, int vocab, lon
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
     }
-    kernel<<<rows, threads, smem, stream>>>(static_cast<const scalar_t*>(logits), vocab,
-                                            row_stride, temperature, top_p, penalty, seeds,
-                                            counters, seen_tokens, seen_offsets, out);
+    return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, pdl != 0,
+                             static_cast<const scalar_t*>(logits), vocab, row_stride, temperature, top_p,
+                             penalty, seeds, counters, seen_tokens, seen_offsets, out);
   });
-  return rl::launch_status();
+  return 0;
 }

@@ -322,11 +322,20 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries as one batch; logits ``[wanted, vocab]`` in entry and ``want`` order."""
         batch = self.prepare(entries)
-        logits = self.model.forward(batch, self.layer_caches())
+        logits = self._forward(batch, self.layer_caches())
         for entry in entries:
             self.cache.release_passed(entry.request_id)
         self.steps_run += 1
         return logits
+
+    def _forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
+        """The model over one batch, its kernels chained by programmatic dependent launch if configured."""
+        previous = kernels.PDL
+        kernels.PDL = self.config.use_dependent_launch
+        try:
+            return self.model.forward(batch, caches)
+        finally:
+            kernels.PDL = previous
 
     def decode_bucket(self, count: int) -> int:
         """Batch size a decode-only step of ``count`` rows is padded to for graph replay."""
@@ -352,12 +361,12 @@ class ModelRunner:
         captured = self._graphs.get(bucket)
         if captured is None:
             caches = self.layer_caches()
-            logits = self.model.forward(batch, caches)
+            logits = self._forward(batch, caches)
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
             before = kernels.LAUNCHES.count
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_logits = self.model.forward(batch, caches)
+                static_logits = self._forward(batch, caches)
             launches = kernels.LAUNCHES.count - before
             kernels.LAUNCHES.count = before          # recording is not launching
             if self._graph_pool is None:

@@ -16,6 +16,11 @@ from .build import attention_library, load_library
 
 F32, BF16 = 0, 1
 
+# Launch every kernel of this library as a programmatic dependent of the stream's previous
+# kernel: it may then start while that kernel drains, and waits inside for its results.  The
+# engine switches it on for its steps; direct callers get ordinary launches.
+PDL = False
+
 FAULT_BITS = {
     1: "a token id outside the vocabulary",
     2: "a page id outside the cache pool",
@@ -99,14 +104,14 @@ def core() -> ctypes.CDLL:
     global _SIGNATURES_SET
     lib = load_library("core")
     if not _SIGNATURES_SET:
-        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
-        lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p]
-        lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
-        lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_void_p]
+        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]
+        lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_qk_norm_rope_write.argtypes = [
             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_float, c_void_p, c_void_p,
+            c_float, c_void_p, c_int, c_void_p,
         ]
         lib.rl_attention_generic.argtypes = [
             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -115,7 +120,7 @@ def core() -> ctypes.CDLL:
         lib.rl_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_sample.argtypes = [
             c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
         ]
         for name in (
             "rl_embedding", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
@@ -136,7 +141,7 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: 
         raise KernelError(f"embedding: out {tuple(out.shape)} {out.dtype} does not fit table {tuple(table.shape)} {table.dtype}")
     _check(
         core().rl_embedding(dtype_tag(table.dtype), _ptr(out), _ptr(table), _ptr(ids), ids.numel(),
-                            table.shape[1], table.shape[0], _ptr(fault), _stream()),
+                            table.shape[1], table.shape[0], _ptr(fault), 0, _stream()),   # first kernel of a step: an ordinary launch
         "embedding",
     )
     return out
@@ -171,7 +176,7 @@ def add_rmsnorm(
         raise KernelError("add_rmsnorm: residual must have the shape of x")
     _check(
         core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out),
-                              _ptr(row_index), rows, hidden, float(eps), mode, int(write_residual), _stream()),
+                              _ptr(row_index), rows, hidden, float(eps), mode, int(write_residual), int(PDL), _stream()),
         f"add_rmsnorm(hidden={hidden})",
     )
     return out
@@ -184,7 +189,7 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     rows, width = gate_up.shape
     if width % 2 or out.shape != (rows, width // 2) or out.dtype != gate_up.dtype:
         raise KernelError("silu_mul: out must be [rows, width / 2] of the input's dtype")
-    _check(core().rl_silu_mul(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), rows, width // 2, _stream()), "silu_mul")
+    _check(core().rl_silu_mul(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), rows, width // 2, int(PDL), _stream()), "silu_mul")
     return out
 
 
@@ -194,7 +199,7 @@ def to_float(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _expect("out", out, torch.float32)
     if out.numel() != src.numel():
         raise KernelError("to_float: sizes differ")
-    _check(core().rl_to_float(dtype_tag(src.dtype), _ptr(src), _ptr(out), src.numel(), _stream()), "to_float")
+    _check(core().rl_to_float(dtype_tag(src.dtype), _ptr(src), _ptr(out), src.numel(), int(PDL), _stream()), "to_float")
     return out
 
 
@@ -248,7 +253,7 @@ def qk_norm_rope_write(
             dtype_tag(qkv.dtype), _ptr(qkv), row_width, _ptr(bias), _ptr(q_weight), _ptr(k_weight),
             _ptr(cos), _ptr(sin), _ptr(positions), _ptr(kv_dest), _ptr(q_out), _ptr(cache), tokens,
             num_heads, num_kv_heads, head_dim, rotary_dim, cos.shape[0], page_size, num_pages,
-            float(eps), _ptr(fault), _stream(),
+            float(eps), _ptr(fault), int(PDL), _stream(),
         ),
         f"qk_norm_rope_write(head_dim={head_dim})",
     )
@@ -310,7 +315,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         if lib.rl_attention_head_dim() != head_dim:
@@ -378,7 +383,7 @@ def attention_mma(
             _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
-            _ptr(fault), _stream(),
+            _ptr(fault), int(PDL), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )
@@ -405,7 +410,6 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Te
 
 
 _GEMM_LIB: ctypes.CDLL | None = None
-PDL = False   # launch with programmatic stream serialization (set by the engine for its steps)
 
 
 def gemm_lib() -> ctypes.CDLL:
@@ -476,7 +480,7 @@ def sample(
         core().rl_sample(
             dtype_tag(logits.dtype), _ptr(logits), logits.shape[0], logits.shape[1], logits.stride(0),
             _ptr(temperature), _ptr(top_p), _ptr(penalty), _ptr(seeds), _ptr(counters),
-            _ptr(seen_tokens), _ptr(seen_offsets), _ptr(out), _stream(),
+            _ptr(seen_tokens), _ptr(seen_offsets), _ptr(out), int(PDL), _stream(),
         ),
         f"sample(vocab={logits.shape[1]})",
     )
