@@ -208,10 +208,10 @@ def run_ours(args) -> dict:
     runner = ModelRunner.from_random(config, seed=0, config=engine)
     llm = LLM.from_runner(runner)
 
-    prefill_ms = prefill_run(llm, args.warmup, seed=11)
+    prefill_ms = prefill_run(llm, args.warmup, seed=11) if "prefill" in args.parts else float("nan")
     results = {}
     for batch in batches:
-        if batch == args.batch:
+        if batch == args.batch or "points" not in args.parts:
             continue
         results[batch] = decode_run(llm, batch, args.steps, args.warmup, seed=batch)
     with ClockSampler() as clocks:
@@ -337,6 +337,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--parts", default="prefill,points", help="extra measurements beside the main decode run "
+                        "(comma-separated: prefill, points); an empty string leaves only the main run, for profiling")
     parser.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = parser.parse_args()
     if args.gpus != 1:
@@ -344,6 +346,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    args.parts = {part for part in args.parts.split(",") if part}
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

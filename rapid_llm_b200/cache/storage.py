@@ -2,7 +2,7 @@
 
 Per group one tensor ``[entries, pages + 1, 2, kv_heads, page_size, head_dim]`` (page 0
 is the null page that padding and released table entries point at), one int32 block table
-``[slots, max_pages]`` mirrored from the host bookkeeping row by row as rows change, and
+``[slots, max_pages]`` mirrored from the host bookkeeping (the step function uploads the rows that changed with its metadata), and
 per run-order entry that asks for it one state tensor ``[slots, *shape]``, zeroed when a
 slot is handed to a new request.  The reference stores one row per token,
 ``[max_tokens, 2 * kv_heads, head_dim]`` per layer (``rapid_llm/executor/kv_cache_manager.py:230-249``).
@@ -40,7 +40,6 @@ class CacheStorage:
         self.block_tables = [
             torch.zeros(table.shape, dtype=torch.int32, device=device) for table in manager.block_tables
         ]
-        self._host_tables = [torch.from_numpy(table) for table in manager.block_tables]
         self.states: list[torch.Tensor | None] = [
             None if need is None
             else torch.zeros((self.num_rows, *need.shape), dtype=need.dtype, device=device)
@@ -57,12 +56,6 @@ class CacheStorage:
             return None, None
         local = self.manager.groups[group].entries.index(owner)
         return group, self.pages[group][local]
-
-    def sync_block_tables(self) -> None:
-        """Copy the rows that changed since the last step to the device."""
-        for index, table in enumerate(self.block_tables):
-            for slot in self.manager.take_dirty(index):
-                table[slot].copy_(self._host_tables[index][slot], non_blocking=False)
 
     def reset_state(self, slot: int) -> None:
         for state in self.states:

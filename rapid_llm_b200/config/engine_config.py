@@ -50,6 +50,8 @@ class EngineConfig:
         memory_fraction: Share of the device's memory the cache may claim when
             ``num_pages`` is ``None``.
         use_cuda_graph: Replay decode-only steps from captured graphs.
+        run_ahead: Enqueue a step before the host has read the previous step's tokens (they
+            are fed back on the device); off = read every step's tokens before planning the next.
         use_dependent_launch: Launch the step's kernels as programmatic dependents of one
             another, so that each starts (and fetches its weights) while its predecessor drains.
     """
@@ -66,6 +68,7 @@ class EngineConfig:
     memory_fraction: float = 0.9
     use_cuda_graph: bool = True
     use_dependent_launch: bool = True
+    run_ahead: bool = True
 
     def __post_init__(self) -> None:
         parse_dtype(self.dtype)

@@ -50,6 +50,7 @@ constexpr int kStride = kD + 8;             // row stride in shared memory (elem
 constexpr int kChunksPerRow = kD / 8;       // 16-byte chunks in a row
 constexpr int kThreads = 128;
 constexpr bool kQInRegisters = kD <= 128;
+constexpr int kStagedPages = 1024;          // page ids of an item's key range kept in shared memory
 
 struct AttentionArgs {
   const bf16* q;            // [tokens, hq, D]
@@ -160,6 +161,25 @@ attention_mma_kernel(const AttentionArgs args) {
   const int* table = args.block_table + static_cast<size_t>(bad ? 0 : slot) * args.max_pages;
   const size_t v_plane = static_cast<size_t>(args.hkv) * args.page_size * kD;
 
+  // The page ids of this item's key range, fetched once and side by side (a lookup per
+  // 16-byte copy would put a dependent global load in front of every copy).  The block table
+  // is uploaded before the step's first kernel, so this may run before the wait below.
+  __shared__ int staged_pages[kStagedPages];
+  const int first_page = k_begin / args.page_size;
+  const int page_count = n_blocks > 0 ? (k_end - 1) / args.page_size - first_page + 1 : 0;
+  const bool staged = page_count <= kStagedPages;
+  if (staged) {
+    for (int i = tid; i < page_count; i += kThreads) {
+      int page = table[first_page + i];
+      if (page < 0 || page >= args.num_pages) {
+        atomicOr(args.fault, kFaultPageId);
+        page = -1;
+      }
+      staged_pages[i] = page;
+    }
+    __syncthreads();
+  }
+
   // ---- loads -------------------------------------------------------------------------
   auto load_q = [&]() {
     for (int idx = tid; idx < kTileM * kChunksPerRow; idx += kThreads) {
@@ -174,9 +194,43 @@ attention_mma_kernel(const AttentionArgs args) {
       cp_async16(smem_u32(q_smem + r * kStride + c * 8), src, valid);
     }
   };
+  // Where each of this thread's 16-byte copies of a block comes from.  When a block of 64 keys
+  // is a whole number of pages (or lies inside one page), the page a row belongs to and its
+  // place in the page do not change from block to block, so they are worked out once.
+  constexpr int kLoadIters = kBlockN * kChunksPerRow / kThreads;
+  static_assert(kBlockN * kChunksPerRow % kThreads == 0, "copies divide evenly over the threads");
+  const bool regular = staged && (kBlockN % args.page_size == 0 || args.page_size % kBlockN == 0);
+  int copy_row[kLoadIters], copy_page[kLoadIters], copy_src[kLoadIters], copy_dst[kLoadIters];
+#pragma unroll
+  for (int i = 0; i < kLoadIters; ++i) {
+    const int idx = tid + i * kThreads;
+    const int r = idx / kChunksPerRow, c = idx - r * kChunksPerRow;
+    copy_row[i] = r;
+    copy_dst[i] = r * kStride + c * 8;
+    const bool small_pages = args.page_size <= kBlockN;
+    copy_page[i] = regular && small_pages ? r / args.page_size : 0;
+    copy_src[i] = (regular && small_pages ? r % args.page_size : r) * kD + c * 8;
+  }
+  const size_t page_stride = static_cast<size_t>(2) * args.hkv * args.page_size * kD;
+  const bf16* head_base = args.cache + static_cast<size_t>(kv_head) * args.page_size * kD;
+
   auto load_block = [&](int stage, int kb) {
     bf16* ks = k_smem + stage * kBlockN * kStride;
     bf16* vs = v_smem + stage * kBlockN * kStride;
+    if (regular) {
+      const int block_page = kb / args.page_size - first_page;
+      const int block_offset = (kb % args.page_size) * kD;      // 0 unless pages are larger than a block
+#pragma unroll
+      for (int i = 0; i < kLoadIters; ++i) {
+        bool valid = kb + copy_row[i] < k_end;
+        const int page = valid ? staged_pages[block_page + copy_page[i]] : -1;
+        valid = page >= 0;
+        const bf16* src = valid ? head_base + page * page_stride + block_offset + copy_src[i] : args.cache;
+        cp_async16(smem_u32(ks + copy_dst[i]), src, valid);
+        cp_async16(smem_u32(vs + copy_dst[i]), valid ? src + v_plane : src, valid);
+      }
+      return;
+    }
     for (int idx = tid; idx < kBlockN * kChunksPerRow; idx += kThreads) {
       const int r = idx / kChunksPerRow, c = idx - r * kChunksPerRow;
       const int j = kb + r;
@@ -184,14 +238,20 @@ attention_mma_kernel(const AttentionArgs args) {
       const bf16* src = args.cache;
       if (valid) {
         const int page_index = j / args.page_size;
-        const int page = table[page_index];
-        if (page < 0 || page >= args.num_pages) {
-          atomicOr(args.fault, kFaultPageId);
+        int page;
+        if (staged) {
+          page = staged_pages[page_index - first_page];
+        } else {
+          page = table[page_index];
+          if (page < 0 || page >= args.num_pages) {
+            atomicOr(args.fault, kFaultPageId);
+            page = -1;
+          }
+        }
+        if (page < 0) {
           valid = false;
         } else {
-          src = args.cache +
-                ((static_cast<size_t>(page) * 2 * args.hkv + kv_head) * args.page_size +
-                 (j - page_index * args.page_size)) * kD + c * 8;
+          src = head_base + page * page_stride + static_cast<size_t>(j - page_index * args.page_size) * kD + c * 8;
         }
       }
       cp_async16(smem_u32(ks + r * kStride + c * 8), src, valid);

@@ -27,13 +27,16 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 }
 
 // ---------------------------------------------------------------- embedding
+// An id -(r + 1) stands for "the token in feedback[r]": the id the previous step sampled into
+// row r of its result, which the host may not have read yet.
 template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int hidden, int vocab,
-                                 int* __restrict__ fault) {
+                                 const int* __restrict__ ids, const int* __restrict__ feedback,
+                                 int feedback_rows, int hidden, int vocab, int* __restrict__ fault) {
   pdl_trigger();
   const int row = blockIdx.x;
   int id = ids[row];
+  if (id < 0 && feedback != nullptr && -(id + 1) < feedback_rows) id = feedback[-(id + 1)];
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) atomicOr(fault, kFaultTokenId);
     id = 0;
@@ -160,20 +163,35 @@ __global__ void to_float_kernel(const TIn* __restrict__ in, float* __restrict__ 
     out[idx] = to_float(in[idx]);
 }
 
+// ------------------------------------------------------------ block-table rows
+// table[slots[i], :] = rows[i, :]: the block-table rows that changed on the host, brought over
+// with the step's metadata instead of one copy per row.
+__global__ void scatter_rows_kernel(int* __restrict__ table, int row_len, int table_rows,
+                                    const int* __restrict__ slots, const int* __restrict__ rows,
+                                    int* __restrict__ fault) {
+  const int slot = slots[blockIdx.x];
+  if (slot < 0 || slot >= table_rows) {
+    if (threadIdx.x == 0) atomicOr(fault, kFaultSlot);
+    return;
+  }
+  for (int c = threadIdx.x; c < row_len; c += blockDim.x)
+    table[static_cast<size_t>(slot) * row_len + c] = rows[static_cast<size_t>(blockIdx.x) * row_len + c];
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace rl
 
 extern "C" {
 
-int rl_embedding(int dtype, void* out, const void* table, const int* ids, int rows, int hidden,
-                 int vocab, int* fault, int pdl, cudaStream_t stream) {
+int rl_embedding(int dtype, void* out, const void* table, const int* ids, const int* feedback,
+                 int feedback_rows, int rows, int hidden, int vocab, int* fault, int pdl, cudaStream_t stream) {
   if (rows == 0) return 0;
   RL_DISPATCH_DTYPE(dtype, {
     const int threads = hidden >= 2048 ? 256 : 128;
     return rl::launch_kernel(rl::embedding_kernel<scalar_t>, dim3(rows), dim3(threads), 0, stream, pdl != 0,
-                             static_cast<scalar_t*>(out), static_cast<const scalar_t*>(table), ids, hidden,
-                             vocab, fault);
+                             static_cast<scalar_t*>(out), static_cast<const scalar_t*>(table), ids, feedback,
+                             feedback_rows, hidden, vocab, fault);
   });
   return 0;
 }
@@ -226,6 +244,14 @@ int rl_silu_mul(int dtype, const void* gate_up, void* out, int rows, int inter, 
                              static_cast<const scalar_t*>(gate_up), static_cast<scalar_t*>(out), rows, inter);
   });
   return 0;
+}
+
+int rl_scatter_rows(int* table, int row_len, int table_rows, const int* slots, const int* rows, int count,
+                    int* fault, cudaStream_t stream) {
+  if (count == 0 || row_len == 0) return 0;
+  if (count < 0 || row_len < 0 || table_rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  rl::scatter_rows_kernel<<<count, 128, 0, stream>>>(table, row_len, table_rows, slots, rows, fault);
+  return rl::launch_status();
 }
 
 int rl_to_float(int dtype, const void* in, float* out, long long n, int pdl, cudaStream_t stream) {

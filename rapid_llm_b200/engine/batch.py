@@ -111,6 +111,7 @@ class StepBatch:
     dtype: torch.dtype
     decode_only: bool = False
     extras: dict[str, Any] = field(default_factory=dict)
+    feedback: torch.Tensor | None = None     # ids the previous step sampled, for token ids -(row + 1)
 
     @property
     def num_logit_rows(self) -> int:

@@ -26,7 +26,11 @@ class DeviceExecutor:
     def release(self, request_id: Hashable) -> None:
         self.runner.release(request_id)
 
-    def execute(self, entries: Sequence) -> list[int]:
+    def launch(self, entries: Sequence):
+        """Enqueue the batch, its sampling and the read of the sampled ids; returns a ticket.
+
+        A token id ``-(row + 1)`` among the entries' tokens is taken on the device from row
+        ``row`` of the ids the previously launched batch sampled."""
         step_entries = [
             StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
             for e in entries
@@ -38,7 +42,7 @@ class DeviceExecutor:
         else:
             logits = self.runner.step(step_entries)
         if not sampling:
-            return []
+            return None
         self.sampler.launch(
             logits,
             [r.params for r in sampling],
@@ -46,4 +50,10 @@ class DeviceExecutor:
             [len(r.output_token_ids) for r in sampling],
             [r.output_token_ids for r in sampling],
         )
-        return self.sampler.read(len(sampling))
+        return self.sampler.read_later(len(sampling))
+
+    def collect(self, ticket) -> list[int]:
+        return [] if ticket is None else self.sampler.collect(ticket)
+
+    def execute(self, entries: Sequence) -> list[int]:
+        return self.collect(self.launch(entries))

@@ -90,7 +90,7 @@ class ModelRunner:
         self._planners = model.step_planners()
         self._meta_capacity = t_max * (4 + g) + 3 * n_max + 8 + sum(
             planner.capacity(t_max, n_max) + 8 for planner in self._planners
-        )
+        ) + g * (n_max * (config.max_pages_per_seq + 1) + 8)      # block-table rows that changed
         self._meta_host = [
             torch.empty(self._meta_capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)
         ]
@@ -263,12 +263,27 @@ class ModelRunner:
             at += 1
             cu_seqlens[i + 1] = at
 
-        self.storage.sync_block_tables()
+        # block-table rows that changed on the host ride along and are put in place by a kernel
+        changed: list[tuple[int, str, str]] = []
+        for index in range(g):
+            slots = cache.take_dirty(index)
+            if not slots:
+                continue
+            table = cache.block_tables[index]
+            cursor = -(-cursor // 4) * 4
+            carve(f"table_slots{index}", len(slots))[:] = slots
+            carve(f"table_rows{index}", len(slots) * table.shape[1])[:] = table[slots].reshape(-1)
+            changed.append((index, f"table_slots{index}", f"table_rows{index}"))
+        if cursor > self._meta_capacity:
+            raise ValueError("the step's metadata does not fit its buffer")
         self._meta_device[:cursor].copy_(host[:cursor], non_blocking=True)
 
         def dev(name: str) -> torch.Tensor:
             begin, count = offsets[name]
             return self._meta_device[begin : begin + count]
+
+        for index, slots_name, rows_name in changed:
+            kernels.scatter_rows(self.storage.block_tables[index], dev(slots_name), dev(rows_name), self.fault)
 
         extras = {
             key: {
@@ -308,6 +323,7 @@ class ModelRunner:
             dtype=self.dtype,
             decode_only=max(lengths) == 1,
             extras=extras,
+            feedback=self.result[1:],
         )
 
     def layer_caches(self) -> list[LayerCache]:

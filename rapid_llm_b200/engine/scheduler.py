@@ -17,6 +17,18 @@ When pages run out:
 * with eviction off, it waits for others to finish; if every running request is stuck,
   :class:`CacheExhausted` is raised rather than spinning;
 * a request that could never fit the pool even alone is refused when it is submitted.
+
+Running ahead.  A step's sampled tokens stay on the device, where the next step's embedding
+can pick them up, so the next step can be planned and enqueued before the host has seen them:
+everything else a step needs (positions, pages, which rows to sample) follows from counts.
+With ``run_ahead`` the scheduler therefore enqueues step N+1 and only then reads step N's
+tokens, while the GPU is already busy; a token that is known only on the device stands in
+the request's list as the negative number ``-(row + 1)`` of its row in the previous step's
+result.  What the host learns one step late is a stop token: the token that the request's
+extra step produced is dropped.  The reference runs the same launch/harvest pipeline with
+device-side token feedback (``rapid_llm/engine/scheduler.py:817-933``).  Requests with a
+repetition penalty need their tokens on the host for the next step and are stepped in
+lockstep instead.
 """
 
 from __future__ import annotations
@@ -53,6 +65,7 @@ class Request:
     num_computed_tokens: int = 0
     finish_reason: str | None = None
     num_preemptions: int = 0
+    exhausted: bool = False        # its last token is sampled (perhaps still on the device): nothing more to feed
     arrival_time: float = 0.0
     first_scheduled_time: float | None = None
     first_token_time: float | None = None
@@ -83,6 +96,15 @@ class PlannedEntry:
 
 
 @dataclass
+class Inflight:
+    """A step that is enqueued but whose sampled tokens the host has not read yet."""
+
+    entries: list[PlannedEntry]
+    handle: object
+    slots: list[tuple[Request, int]]    # per sampled row: the request and the index of its stand-in token
+
+
+@dataclass
 class StepPlan:
     entries: list[PlannedEntry] = field(default_factory=list)
     preempted: list[Request] = field(default_factory=list)
@@ -102,7 +124,11 @@ class Executor(Protocol):
     def release(self, request_id: Hashable) -> None: ...
 
     def execute(self, entries: Sequence[PlannedEntry]) -> list[int]:
-        """Run the entries as one batch; one sampled token per entry with ``samples`` set, in order."""
+        """Run the entries as one batch; one sampled token per entry with ``samples`` set, in order.
+
+        An executor that can run ahead also has ``launch(entries) -> handle`` (enqueue only) and
+        ``collect(handle) -> list[int]`` (wait for that step's tokens); a token id ``-(row + 1)``
+        among the entries' tokens then means row ``row`` of the previously launched step's result."""
 
 
 class Scheduler:
@@ -116,6 +142,8 @@ class Scheduler:
         self._ids = itertools.count()
         self.num_steps = 0
         self.num_preemptions = 0
+        self._inflight: Inflight | None = None
+        self._can_launch = hasattr(executor, "launch") and hasattr(executor, "collect")
 
     # -- submission ------------------------------------------------------------------ #
     def add_request(
@@ -151,7 +179,7 @@ class Scheduler:
         return request
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._inflight is not None)
 
     # -- planning -------------------------------------------------------------------- #
     def _chunk(self, request: Request, budget: int) -> int:
@@ -191,8 +219,8 @@ class Scheduler:
         planned: set[Hashable] = set()
 
         # running requests, oldest first: single decoded tokens and resumed portions
-        decoding = [r for r in self.running if r.num_tokens - r.num_computed_tokens == 1]
-        resumed = [r for r in self.running if r.num_tokens - r.num_computed_tokens > 1]
+        decoding = [r for r in self.running if not r.exhausted and r.num_tokens - r.num_computed_tokens == 1]
+        resumed = [r for r in self.running if not r.exhausted and r.num_tokens - r.num_computed_tokens > 1]
         for request in decoding + resumed:
             if request not in self.running:        # evicted while planning an older one
                 continue
@@ -238,9 +266,10 @@ class Scheduler:
             self._take(plan, request, size, needed, free, planned)
             budget -= size
 
-        if not plan.entries and self.running and not plan.preempted:
+        stuck = [r for r in self.running if not r.exhausted]
+        if not plan.entries and stuck and not plan.preempted and self._inflight is None:
             raise CacheExhausted(
-                f"{len(self.running)} running requests, none can grow: the cache pool "
+                f"{len(stuck)} running requests, none can grow: the cache pool "
                 f"({[pool.num_pages for pool in self.cache.pools]} pages) is exhausted and eviction is off"
             )
         return plan
@@ -254,47 +283,92 @@ class Scheduler:
         planned.add(request.request_id)
 
     # -- one step -------------------------------------------------------------------- #
-    def step(self) -> list[Request]:
-        """Plan, run and harvest one batch; returns the requests that finished in it."""
-        plan = self.plan()
-        self.num_steps += 1
-        if not plan.entries:
-            return []
-        sampled = self.executor.execute(plan.entries)
-        now = time.perf_counter()
-        finished: list[Request] = []
-        tokens = iter(sampled)
+    def _runs_ahead(self) -> bool:
+        if not (self.config.run_ahead and self._can_launch):
+            return False
+        return all(r.params.repetition_penalty == 1.0 for r in itertools.chain(self.running, self.waiting))
+
+    def _launch(self, plan: StepPlan) -> Inflight:
+        """Enqueue the planned batch; every sampled row leaves a stand-in token in its request."""
+        if self._can_launch:
+            handle = self.executor.launch(plan.entries)
+        else:
+            handle = self.executor.execute(plan.entries)
+        slots: list[tuple[Request, int]] = []
         for entry in plan.entries:
             request = entry.request
             request.num_computed_tokens = entry.start + len(entry.tokens)
             if not entry.samples:
                 continue
-            token = int(next(tokens))
+            request.output_token_ids.append(-(len(slots) + 1))
+            slots.append((request, len(request.output_token_ids) - 1))
+            if len(request.output_token_ids) >= request.max_new_tokens or request.num_tokens >= self.config.max_seq_len:
+                request.exhausted = True
+        return Inflight(plan.entries, handle, slots)
+
+    def _harvest(self, inflight: Inflight) -> list[Request]:
+        """Read a launched step's tokens; put them in place of their stand-ins, finish and free."""
+        sampled = self.executor.collect(inflight.handle) if self._can_launch else inflight.handle
+        now = time.perf_counter()
+        finished: list[Request] = []
+        for (request, index), token in zip(inflight.slots, sampled):
+            if request.finished:
+                continue                                  # a step it ran ahead into: the token is dropped
+            token = int(token)
             if request.first_token_time is None:
                 request.first_token_time = now
             if token in self.stop_token_ids:
-                self._finish(request, "eos", now)       # the stop token is not appended
+                del request.output_token_ids[index:]      # the stop token is not appended
+                self._finish(request, "eos", now)
             else:
-                request.output_token_ids.append(token)
-                if len(request.output_token_ids) >= request.max_new_tokens or request.num_tokens >= self.config.max_seq_len:
+                request.output_token_ids[index] = token
+                if request.exhausted and index == len(request.output_token_ids) - 1:
                     self._finish(request, "length", now)
             if request.finished:
                 finished.append(request)
         return finished
 
+    def step(self) -> list[Request]:
+        """Plan and enqueue one batch and harvest one; returns the requests that finished.
+
+        Running ahead, the batch harvested is the one enqueued by the previous call (so the
+        GPU works on the new batch while the host reads the old one's tokens); otherwise it is
+        the batch this call enqueued."""
+        finished: list[Request] = []
+        previous, self._inflight = self._inflight, None
+        ahead = self._runs_ahead()
+        if previous is not None and not ahead:
+            finished += self._harvest(previous)
+            previous = None
+        self._inflight = previous          # planning may ask whether anything is still in flight
+        plan = self.plan()
+        self._inflight = None
+        self.num_steps += 1
+        current = self._launch(plan) if plan.entries else None
+        if previous is not None:
+            finished += self._harvest(previous)
+        if current is not None and not ahead:
+            finished += self._harvest(current)
+            current = None
+        self._inflight = current
+        return finished
+
     def _finish(self, request: Request, reason: str, now: float) -> None:
+        was_running = request.status == RUNNING
         request.status = FINISHED
         request.finish_reason = reason
         request.finish_time = now
-        self.running.remove(request)
-        self.executor.release(request.request_id)
+        while request.output_token_ids and request.output_token_ids[-1] < 0:
+            request.output_token_ids.pop()               # stand-ins of steps it ran ahead into
+        if was_running:
+            self.running.remove(request)
+            self.executor.release(request.request_id)
+        elif request in self.waiting:                    # evicted while its last token was in flight
+            self.waiting.remove(request)
 
     def abort(self, request: Request) -> None:
-        if request.status == RUNNING:
+        if request.status in (RUNNING, WAITING):
             self._finish(request, "abort", time.perf_counter())
-        elif request.status == WAITING:
-            self.waiting.remove(request)
-            request.status, request.finish_reason = FINISHED, "abort"
 
     def run_to_completion(self) -> None:
         while self.has_unfinished():

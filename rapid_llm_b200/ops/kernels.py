@@ -104,9 +104,10 @@ def core() -> ctypes.CDLL:
     global _SIGNATURES_SET
     lib = load_library("core")
     if not _SIGNATURES_SET:
-        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]
         lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rl_scatter_rows.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         lib.rl_to_float.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_qk_norm_rope_write.argtypes = [
             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -123,7 +124,7 @@ def core() -> ctypes.CDLL:
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
         ]
         for name in (
-            "rl_embedding", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
+            "rl_embedding", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
             "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
             getattr(lib, name).restype = c_int
@@ -132,19 +133,38 @@ def core() -> ctypes.CDLL:
 
 
 # --------------------------------------------------------------------------- ops
-def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: torch.Tensor) -> torch.Tensor:
-    """``out[t] = table[ids[t]]``; ``ids`` int32 ``[T]``; bad ids set the fault word."""
-    _need_cuda(out, table, ids, fault)
-    _expect("ids", ids, torch.int32)
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: torch.Tensor,
+              feedback: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]``; ``ids`` int32 ``[T]``; bad ids set the fault word.
+
+    With ``feedback`` (int32, on the device) an id ``-(r + 1)`` is replaced by ``feedback[r]``."""
+    _need_cuda(out, table, ids, fault, feedback)
+    _expect("ids", ids, torch.int32), _expect("feedback", feedback, torch.int32)
     _contig("out", out), _contig("table", table), _contig("ids", ids)
     if out.dtype != table.dtype or out.shape != (ids.numel(), table.shape[1]):
         raise KernelError(f"embedding: out {tuple(out.shape)} {out.dtype} does not fit table {tuple(table.shape)} {table.dtype}")
     _check(
-        core().rl_embedding(dtype_tag(table.dtype), _ptr(out), _ptr(table), _ptr(ids), ids.numel(),
+        core().rl_embedding(dtype_tag(table.dtype), _ptr(out), _ptr(table), _ptr(ids), _ptr(feedback),
+                            0 if feedback is None else feedback.numel(), ids.numel(),
                             table.shape[1], table.shape[0], _ptr(fault), 0, _stream()),   # first kernel of a step: an ordinary launch
         "embedding",
     )
     return out
+
+
+def scatter_rows(table: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor, fault: torch.Tensor) -> torch.Tensor:
+    """``table[slots[i]] = rows[i]`` for int32 tables; a slot outside the table sets the fault word."""
+    _need_cuda(table, slots, rows, fault)
+    for name, tensor in (("table", table), ("slots", slots), ("rows", rows)):
+        _expect(name, tensor, torch.int32), _contig(name, tensor)
+    if table.dim() != 2 or rows.numel() != slots.numel() * table.shape[1]:
+        raise KernelError("scatter_rows: rows must hold one table row per slot")
+    _check(
+        core().rl_scatter_rows(_ptr(table), table.shape[1], table.shape[0], _ptr(slots), _ptr(rows), slots.numel(),
+                               _ptr(fault), _stream()),
+        "scatter_rows",
+    )
+    return table
 
 
 def add_rmsnorm(

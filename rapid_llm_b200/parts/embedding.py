@@ -35,7 +35,7 @@ class TokenEmbedding(Part):
 
     def forward(self, batch) -> torch.Tensor:
         out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
-        return kernels.embedding(out, self.weight, batch.token_ids, batch.fault)
+        return kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback)
 
 
 @HEADS.register("lm_head")

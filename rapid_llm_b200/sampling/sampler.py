@@ -24,6 +24,10 @@ class Sampler:
         self.device = result.device
         self.max_rows = result.numel() - 1
         self._host = torch.zeros(result.numel(), dtype=torch.int32, pin_memory=True)
+        # reads that are enqueued but not waited for yet: a few pinned buffers in rotation
+        self._ring = [torch.zeros(result.numel(), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._events = [torch.cuda.Event() for _ in range(4)]
+        self._turn = 0
 
     def launch(
         self,
@@ -69,6 +73,23 @@ class Sampler:
         """The step's one device-to-host read: fault word and ``rows`` sampled ids."""
         self._host[: rows + 1].copy_(self.result[: rows + 1], non_blocking=False)
         values = self._host[: rows + 1].tolist()
+        if values[0]:
+            self.result[:1].zero_()
+            raise RuntimeError(f"a kernel reported a fault: {kernels.describe_fault(values[0])}")
+        return values[1:]
+
+    def read_later(self, rows: int) -> tuple[int, int]:
+        """Enqueue the read of the fault word and ``rows`` ids; :meth:`collect` waits for it."""
+        turn = self._turn
+        self._turn = (turn + 1) % len(self._ring)
+        self._ring[turn][: rows + 1].copy_(self.result[: rows + 1], non_blocking=True)
+        self._events[turn].record()
+        return turn, rows
+
+    def collect(self, ticket: tuple[int, int]) -> list[int]:
+        turn, rows = ticket
+        self._events[turn].synchronize()
+        values = self._ring[turn][: rows + 1].tolist()
         if values[0]:
             self.result[:1].zero_()
             raise RuntimeError(f"a kernel reported a fault: {kernels.describe_fault(values[0])}")

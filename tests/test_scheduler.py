@@ -165,3 +165,128 @@ def test_sampling_params_are_validated():
             SamplingParams(**bad)
     assert SamplingParams().temperature == 0.6 and SamplingParams().top_p == 0.9 and SamplingParams().repetition_penalty == 1.1
     assert SamplingParams(temperature=0).is_greedy
+
+
+# ------------------------------------------------------------------ running ahead
+class RunAheadExecutor(ScriptedExecutor):
+    """Adds ``launch``/``collect``: a launched step's tokens are computed when it is collected,
+    as on the device, where a token id ``-(row + 1)`` reads row ``row`` of the previous result."""
+
+    def __init__(self, config, pages):
+        super().__init__(config, pages)
+        self.previous_result: list[int] = []
+        self.fed: list[list[int]] = []          # per step, the token ids the model actually saw
+        self.collected = 0
+        self.launched = 0
+
+    def launch(self, entries):
+        self.launched += 1
+        self.steps.append([(e.request.request_id, e.start, len(e.tokens), e.samples) for e in entries])
+        sampled, fed = [], []
+        for entry in entries:
+            assert entry.start == self.cache.num_tokens(entry.request.request_id)
+            assert self.cache.reserve(entry.request.request_id, entry.start + len(entry.tokens))
+            for token in entry.tokens:
+                fed.append(self.previous_result[-token - 1] if token < 0 else token)
+            if entry.samples:
+                index = sum(1 for t in entry.request.output_token_ids)          # stand-ins count
+                stop = self.stop_after.get(entry.request.request_id)
+                sampled.append(7 if stop is not None and index >= stop else 1000 + index)
+        self.cache.check()
+        self.fed.append(fed)
+        self.previous_result = sampled
+        return (self.launched, sampled)
+
+    def collect(self, ticket):
+        number, sampled = ticket
+        assert number == self.collected + 1, "steps are collected in the order they were launched"
+        self.collected = number
+        return sampled
+
+    def execute(self, entries):
+        return self.collect(self.launch(entries))
+
+
+def make_ahead(pages=64, **overrides):
+    values = dict(max_seq_len=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=64, max_chunk_size=32)
+    values.update(overrides)
+    config = EngineConfig(**values)
+    executor = RunAheadExecutor(config, pages)
+    return Scheduler(executor, config, stop_token_ids=[7]), executor
+
+
+def test_running_ahead_launches_the_next_step_before_it_reads_the_previous_one():
+    scheduler, executor = make_ahead()
+    request = scheduler.add_request(list(range(5)), greedy(4), "a")
+    scheduler.step()
+    assert executor.launched == 1 and executor.collected == 0
+    assert request.output_token_ids == [-1]                  # a stand-in: row 0 of the step in flight
+    scheduler.step()
+    assert executor.launched == 2 and executor.collected == 1
+    assert request.output_token_ids == [1000, -1]
+    scheduler.run_to_completion()
+    assert request.output_token_ids == [1000, 1001, 1002, 1003] and request.finish_reason == "length"
+    assert executor.launched == 4 and executor.collected == 4       # no step beyond the last token
+    assert executor.fed[1:] == [[1000], [1001], [1002]]              # each step saw the token before it
+    assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
+
+
+def test_running_ahead_gives_the_same_tokens_and_steps_as_lockstep():
+    def run(ahead):
+        scheduler, executor = make_ahead(run_ahead=ahead, max_num_batched_tokens=48)
+        requests = [scheduler.add_request(list(range(n)), greedy(g), name)
+                    for name, n, g in (("a", 40, 6), ("b", 9, 3), ("c", 70, 5), ("d", 3, 9))]
+        scheduler.run_to_completion()
+        return [r.output_token_ids for r in requests], executor.steps, executor
+    tokens_ahead, steps_ahead, executor = run(True)
+    tokens_lock, steps_lock, _ = run(False)
+    assert tokens_ahead == tokens_lock
+    assert steps_ahead == steps_lock
+    assert all(t >= 0 for fed in executor.fed for t in fed)
+    assert executor.cache.num_free_pages() == 64
+
+
+def test_running_ahead_drops_the_token_of_the_step_past_a_stop_token():
+    scheduler, executor = make_ahead()
+    executor.stop_after["a"] = 2
+    a = scheduler.add_request(list(range(5)), greedy(10), "a")
+    b = scheduler.add_request(list(range(6)), greedy(5), "b")
+    scheduler.run_to_completion()
+    assert a.output_token_ids == [1000, 1001] and a.finish_reason == "eos"
+    assert b.output_token_ids == [1000, 1001, 1002, 1003, 1004] and b.finish_reason == "length"
+    # a ran one step past its stop token (the host learnt of it a step late), never two
+    assert sum(1 for step in executor.steps for entry in step if entry[0] == "a") == 4
+    assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
+
+
+def test_running_ahead_with_eviction_keeps_every_token():
+    scheduler, executor = make_ahead(pages=5, max_seq_len=64)
+    a = scheduler.add_request(list(range(30)), greedy(20), "a")
+    b = scheduler.add_request(list(range(30)), greedy(20), "b")
+    scheduler.run_to_completion()
+    assert scheduler.num_preemptions >= 1
+    for request in (a, b):
+        assert request.output_token_ids == [1000 + i for i in range(20)], request.output_token_ids
+    assert all(t >= 0 for fed in executor.fed for t in fed)
+    assert executor.cache.num_free_pages() == 5
+
+
+def test_a_repetition_penalty_keeps_the_steps_in_lockstep():
+    scheduler, executor = make_ahead()
+    request = scheduler.add_request(list(range(5)), SamplingParams(temperature=0.0, repetition_penalty=1.3, max_gen_len=3), "a")
+    scheduler.step()
+    assert executor.launched == 1 and executor.collected == 1 and request.output_token_ids == [1000]
+    scheduler.run_to_completion()
+    assert request.output_token_ids == [1000, 1001, 1002]
+
+
+def test_abort_while_a_step_is_in_flight():
+    scheduler, executor = make_ahead()
+    a = scheduler.add_request(list(range(5)), greedy(10), "a")
+    b = scheduler.add_request(list(range(5)), greedy(3), "b")
+    scheduler.step(), scheduler.step()
+    scheduler.abort(a)
+    assert a.finish_reason == "abort" and all(t >= 0 for t in a.output_token_ids)
+    scheduler.run_to_completion()
+    assert b.output_token_ids == [1000, 1001, 1002]
+    assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
