@@ -514,6 +514,77 @@ int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStrea
 }  // namespace RL_ATTENTION_NS
 }  // namespace rl
 
+#include "attention_decode_tc.cuh"
+
+namespace rl {
+namespace RL_ATTENTION_NS {
+
+// Whether the tcgen05 decode kernel takes this geometry (everything else: the mma.sync tiles).
+static bool decode_tc_supported(int page_size) {
+  return kD == kTcD && page_size % 8 == 0 && (kTcKeys % page_size == 0 || page_size % kTcKeys == 0);
+}
+
+static bool g_decode_tc_configured[5] = {};   // per row-count instantiation; file-local on purpose
+
+template <int kRows>
+static int launch_decode_tc_rows(const CUtensorMap& map, const DecodeTcArgs& t, int n_items, bool pdl,
+                                 cudaStream_t stream, bool* configured) {
+  auto kernel = attention_decode_tc_kernel<kRows>;
+  if (!*configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    *configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(n_items, t.hkv);
+  config.blockDim = dim3(kTcThreads);
+  config.dynamicSmemBytes = kTcSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (t.cluster_merge) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = t.splits;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (pdl) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map, t));
+}
+
+// cluster_merge: the `splits` items of a tile are consecutive in the grid and launched as one
+// thread-block cluster, whose CTAs merge their partial results among themselves.  max_rows: the
+// most packed rows any of the items has (0 = not known).
+static int launch_decode_tc(const AttentionArgs& a, int n_items, int max_rows, bool cluster_merge, bool pdl,
+                            cudaStream_t stream) {
+  CUtensorMap map;
+  const long long rows = static_cast<long long>(a.num_pages) * 2 * a.hkv * a.page_size;
+  int status = make_map(&map, a.cache, rows, kD, a.page_size < kTcKeys ? a.page_size : kTcKeys);
+  if (status != 0) return status;
+  DecodeTcArgs t;
+  t.q = a.q; t.out = a.out; t.part_out = a.part_out; t.part_lse = a.part_lse; t.items = a.items;
+  t.cu_seqlens = a.cu_seqlens; t.entry_start = a.entry_start; t.entry_slot = a.entry_slot;
+  t.block_table = a.block_table; t.hq = a.hq; t.hkv = a.hkv; t.page_size = a.page_size;
+  t.num_pages = a.num_pages; t.max_pages = a.max_pages; t.slots = a.slots; t.window = a.window;
+  t.splits = a.splits; t.cluster_merge = cluster_merge ? 1 : 0; t.scale_log2 = a.scale_log2; t.fault = a.fault;
+  if (max_rows <= 0 || max_rows > kTcRows) max_rows = kTcRows;
+  if (max_rows <= 1) return launch_decode_tc_rows<1>(map, t, n_items, pdl, stream, &g_decode_tc_configured[0]);
+  if (max_rows <= 2) return launch_decode_tc_rows<2>(map, t, n_items, pdl, stream, &g_decode_tc_configured[1]);
+  if (max_rows <= 4) return launch_decode_tc_rows<4>(map, t, n_items, pdl, stream, &g_decode_tc_configured[2]);
+  if (max_rows <= 8) return launch_decode_tc_rows<8>(map, t, n_items, pdl, stream, &g_decode_tc_configured[3]);
+  return launch_decode_tc_rows<16>(map, t, n_items, pdl, stream, &g_decode_tc_configured[4]);
+}
+
+}  // namespace RL_ATTENTION_NS
+}  // namespace rl
+
 namespace attn = rl::RL_ATTENTION_NS;
 
 extern "C" {
@@ -524,6 +595,8 @@ int rl_attention_head_dim() { return attn::kD; }
 int rl_attention_chunk_rows() { return 64; }
 int rl_attention_decode_rows() { return 16; }
 
+// decode_kernel: 0 = the tcgen05 kernel for decode tiles where it applies, 1 = always the
+// mma.sync tiles.  decode_rows: the most packed rows any decode tile has (0 = not known).
 // chunk_items / decode_items: [n, 4] int32 (entry, first packed row, split, 0).  With
 // splits > 1, part_out [tokens, hq, splits, D] and part_lse [tokens, hq, splits] are scratch
 // and every (row, split) pair must be covered by exactly one item.
@@ -532,7 +605,8 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      int n_decode_items, const int* cu_seqlens, const int* entry_start,
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
-                     int window, int splits, float scale, int* fault, int pdl, cudaStream_t stream) {
+                     int window, int splits, float scale, int* fault, int pdl, int decode_kernel, int decode_rows,
+                     cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
@@ -553,6 +627,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   args.scale_log2 = scale * 1.4426950408889634f;
   args.fault = fault;
   int status = 0;
+  bool merged_in_cluster = false;
   if (n_chunk_items > 0) {
     args.items = chunk_items;
     status = attn::launch_attention<4, 1, 2>(args, n_chunk_items, pdl != 0, stream);
@@ -560,10 +635,14 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   }
   if (n_decode_items > 0) {
     args.items = decode_items;
-    status = attn::launch_attention<1, 4, 3>(args, n_decode_items, pdl != 0, stream);
+    if (decode_kernel != 1 && attn::decode_tc_supported(page_size)) {
+      merged_in_cluster = n_chunk_items == 0 && splits > 1 && splits <= 8 && n_decode_items % splits == 0;
+      status = attn::launch_decode_tc(args, n_decode_items, decode_rows, merged_in_cluster, pdl != 0, stream);
+    } else
+      status = attn::launch_attention<1, 4, 3>(args, n_decode_items, pdl != 0, stream);
     if (status != 0) return status;
   }
-  if (splits > 1) {
+  if (splits > 1 && !merged_in_cluster) {
     const long long rows = static_cast<long long>(tokens) * hq;
     status = rl::launch_kernel(attn::attention_merge_kernel, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0,
                                stream, pdl != 0, part_out, part_lse, static_cast<attn::bf16*>(out), rows, splits);
@@ -658,7 +737,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, stream);
 }
 
 }  // extern "C"

@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace rl {
 
@@ -39,7 +40,6 @@ constexpr int kTileN = 128;           // weight rows per tile = M of one tcgen05
 constexpr int kTileK = 64;            // bf16 elements in one 128-byte swizzle row
 constexpr int kUmmaK = 16;            // k-elements of one tcgen05.mma of kind::f16
 constexpr int kGemmThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct GemmArgs {
   bf16* out;               // [T, N]
@@ -50,113 +50,6 @@ struct GemmArgs {
   int k_split;             // CTAs (= cluster size) that share one tile's k-range
   int pdl;                 // launched with programmatic stream serialization
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t gemm_smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Waits for the phase of the given parity to complete; gives up after a bounded number of
-// tries, records that in the fault word and in the CTA's abort flag, and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* aborted,
-                                          int* fault) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 1023u && *aborted) return false;
-  }
-  *aborted = 1;
-  atomicOr(fault, kFaultWaitLimit);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
-                                            int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t result_smem, uint32_t columns) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem),
-               "r"(columns)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrives on the barrier once every tcgen05.mma issued so far by this thread has finished.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-// 16 consecutive accumulator columns of this thread's lane.
-__device__ __forceinline__ void tmem_load16(uint32_t address, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15])
-      : "r"(address));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-// Every thread of every CTA of the cluster arrives, then waits: shared-memory writes made
-// before are visible to the other CTAs after.
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release;\n barrier.cluster.wait.acquire;" ::: "memory");
-}
-__device__ __forceinline__ float load_cluster_f32(uint32_t local_address, uint32_t cta_rank) {
-  uint32_t remote;
-  float value;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
-  return value;
-}
-
-// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
-// eight rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_address) {
-  return static_cast<uint64_t>((smem_address & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) |
-         (1ull << 46) | (2ull << 61);
-}
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
   return gate / (1.0f + __expf(-gate)) * up;
@@ -200,25 +93,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   volatile int* aborted = &aborted_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t smem_base = (gemm_smem_u32(gemm_smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_base = (smem_addr(gemm_smem_raw) + 1023u) & ~1023u;
   auto stage_a = [&](int s, int half) { return smem_base + s * Shape::kStageBytes + half * kTileN * kTileK * 2; };
   auto stage_b = [&](int s) { return smem_base + s * Shape::kStageBytes + kHalves * kTileN * kTileK * 2; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(gemm_smem_u32(&full_bar[s]), 1);
-      mbar_init(gemm_smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_addr(&full_bar[s]), 1);
+      mbar_init(smem_addr(&empty_bar[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(gemm_smem_u32(&acc_full_bar[b]), 1);
-      mbar_init(gemm_smem_u32(&acc_empty_bar[b]), 4);
+      mbar_init(smem_addr(&acc_full_bar[b]), 1);
+      mbar_init(smem_addr(&acc_empty_bar[b]), 4);
     }
-    mbar_init(gemm_smem_u32(&drain_bar), 1);
+    mbar_init(smem_addr(&drain_bar), 1);
     aborted_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(gemm_smem_u32(&tmem_base_slot), Shape::kTmemColumns);
+    tmem_alloc(smem_addr(&tmem_base_slot), Shape::kTmemColumns);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -245,7 +138,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const int tile = tile_of(static_cast<int>(it / kb_count));
         const int kb = kb_begin + static_cast<int>(it % kb_count);
         const int n_tile = tile / args.t_tiles;
-        const uint32_t bar = gemm_smem_u32(&full_bar[stage]);
+        const uint32_t bar = smem_addr(&full_bar[stage]);
         mbar_expect_tx(bar, Shape::kStageBytes);
         tma_load_2d(stage_a(stage, 0), &map_w, bar, kb * kTileK, n_tile * kTileN);
         if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, kb * kTileK, args.up_offset + n_tile * kTileN);
@@ -254,7 +147,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         const int tile = tile_of(static_cast<int>(it / kb_count));
         const int kb = kb_begin + static_cast<int>(it % kb_count);
         const int t_tile = tile % args.t_tiles;
-        tma_load_2d(stage_b(stage), &map_x, gemm_smem_u32(&full_bar[stage]), kb * kTileK, t_tile * BN);
+        tma_load_2d(stage_b(stage), &map_x, smem_addr(&full_bar[stage]), kb * kTileK, t_tile * BN);
       };
       // weights first: nothing in the stream writes them, so they may fly before the
       // previous kernel has finished; the activations only after
@@ -267,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       bool ok = true;
       long long filled = prefetch;                     // iterations whose copies were issued
       for (long long it = prefetch; it < total_iters; ++it) {
-        ok = mbar_wait(gemm_smem_u32(&empty_bar[stage]), phase ^ 1u, aborted, args.fault);
+        ok = mbar_wait(smem_addr(&empty_bar[stage]), phase ^ 1u, aborted, args.fault);
         if (!ok) break;
         load_a(it, stage);
         load_b(it, stage);
@@ -280,7 +173,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int s = 0; s < kStages; ++s) {
           const long long fills = (filled - s + kStages - 1) / kStages;   // fills of stage s so far
           if (fills > 0)
-            mbar_wait(gemm_smem_u32(&full_bar[s]), static_cast<uint32_t>((fills - 1) & 1), aborted, args.fault);
+            mbar_wait(smem_addr(&full_bar[s]), static_cast<uint32_t>((fills - 1) & 1), aborted, args.fault);
         }
       }
     }
@@ -291,12 +184,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       uint32_t phase = 0, acc_phase[2] = {0, 0};
       bool ok = kb_count > 0;
       for (int index = 0; index < my_tiles && ok; ++index) {
-        ok = mbar_wait(gemm_smem_u32(&acc_empty_bar[buf]), acc_phase[buf] ^ 1u, aborted, args.fault);
+        ok = mbar_wait(smem_addr(&acc_empty_bar[buf]), acc_phase[buf] ^ 1u, aborted, args.fault);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * Shape::kAccColumns;
         for (int kb = 0; kb < kb_count; ++kb) {
-          ok = mbar_wait(gemm_smem_u32(&full_bar[stage]), phase, aborted, args.fault);
+          ok = mbar_wait(smem_addr(&full_bar[stage]), phase, aborted, args.fault);
           if (!ok) break;
           tc_fence_after();
           const uint64_t b_desc = operand_desc(stage_b(stage));
@@ -310,17 +203,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                         (kb > 0 || k > 0) ? 1u : 0u);
             }
           }
-          umma_commit(gemm_smem_u32(&empty_bar[stage]));   // the stage is free once these products retire
+          umma_commit(smem_addr(&empty_bar[stage]));   // the stage is free once these products retire
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(gemm_smem_u32(&acc_full_bar[buf]));
+        umma_commit(smem_addr(&acc_full_bar[buf]));
         acc_phase[buf] ^= 1u;
         buf ^= 1;
       }
       // nothing of this CTA may still be running on the tensor core when its memory is freed
-      umma_commit(gemm_smem_u32(&drain_bar));
-      mbar_wait(gemm_smem_u32(&drain_bar), 0, aborted, args.fault);
+      umma_commit(smem_addr(&drain_bar));
+      mbar_wait(smem_addr(&drain_bar), 0, aborted, args.fault);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -334,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int tile = tile_of(index);
       const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
       const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
-      ok = mbar_wait(gemm_smem_u32(&acc_full_bar[buf]), acc_phase[buf], aborted, args.fault);
+      ok = mbar_wait(smem_addr(&acc_full_bar[buf]), acc_phase[buf], aborted, args.fault);
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * Shape::kAccColumns + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -359,7 +252,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
       } else if (Shape::kCanSplit) {
         // park the partial tile in this CTA's shared memory: [halves * BN columns][128 rows]
-        float* mine = reinterpret_cast<float*>(gemm_smem_raw + (smem_base - gemm_smem_u32(gemm_smem_raw))) + n_local;
+        float* mine = reinterpret_cast<float*>(gemm_smem_raw + (smem_base - smem_addr(gemm_smem_raw))) + n_local;
 #pragma unroll 1
         for (int c = 0; c < kHalves * BN; c += 16) {
           float v[16];
@@ -371,7 +264,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       // the accumulator buffer may be overwritten from here on
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(gemm_smem_u32(&acc_empty_bar[buf]));
+      if (lane == 0) mbar_arrive(smem_addr(&acc_empty_bar[buf]));
       acc_phase[buf] ^= 1u;
       buf ^= 1;
     }
@@ -410,37 +303,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 }
 
 // ----------------------------------------------------------------------------- host
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                 CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_tiled() {
-  static EncodeTiled fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(ptr);
-  }
-  return fn;
-}
-
-// A [rows, cols] row-major bf16 matrix read in boxes of box_rows x 64 with the 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-  EncodeTiled encode = encode_tiled();
-  if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
-}
-
 static int sm_count() {
   static int sms = 0;
   if (sms == 0) {

@@ -335,7 +335,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         if lib.rl_attention_head_dim() != head_dim:
@@ -366,8 +366,14 @@ def attention_mma(
     window: int,
     scale: float,
     fault: torch.Tensor,
+    decode_kernel: str = "auto",
+    decode_rows: int = 0,
 ) -> torch.Tensor:
     """bfloat16 paged causal attention over work items the host cut the step into.
+
+    Decode tiles run on the tcgen05 kernel where it applies (head size 128, pages of 8 to 64 or
+    a multiple of 128 tokens) unless ``decode_kernel`` is ``"mma"``; ``decode_rows`` is the most
+    packed rows any decode tile has (0 = not known), which lets that kernel unroll over fewer rows.
 
     ``chunk_items`` / ``decode_items`` are int32 ``[n, 4]`` rows ``(entry, first packed row,
     split, 0)`` for tiles of :data:`CHUNK_TILE_ROWS` / :data:`DECODE_TILE_ROWS` packed rows
@@ -403,7 +409,7 @@ def attention_mma(
             _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
-            _ptr(fault), int(PDL), _stream(),
+            _ptr(fault), int(PDL), 1 if decode_kernel == "mma" else 0, int(decode_rows), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )

@@ -24,6 +24,7 @@ from .base import (
 )
 
 TARGET_CTAS = 2 * 148     # work items the attention kernels want in flight on a B200
+DECODE_TARGET_CTAS = 148  # ... in a decode-only step, whose kernel keeps a whole SM's shared memory busy
 MAX_SPLITS = 16
 MIN_KEYS_PER_SPLIT = 256
 
@@ -57,7 +58,8 @@ class AttentionItems(StepPlanner):
         tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, kernels.CHUNK_TILE_ROWS)
         tiles = -(-rows // tile_rows)
         ctas = int(tiles.sum()) * self.num_kv_heads
-        splits = max(1, min(MAX_SPLITS, TARGET_CTAS // max(ctas, 1)))
+        target = DECODE_TARGET_CTAS if shape.decode_only else TARGET_CTAS
+        splits = max(1, min(MAX_SPLITS, target // max(ctas, 1)))
         if not shape.decode_only:
             longest = int((np.asarray(shape.starts, dtype=np.int64) + lengths).max())
             splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
@@ -75,7 +77,9 @@ class AttentionItems(StepPlanner):
             out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), count)
             return out
 
-        return {"chunk_items": items(~decode_tile), "decode_items": items(decode_tile), "splits": splits}
+        decode_rows = int(np.minimum(rows[is_decode], kernels.DECODE_TILE_ROWS).max()) if is_decode.any() else 0
+        return {"chunk_items": items(~decode_tile), "decode_items": items(decode_tile), "splits": splits,
+                "decode_rows": decode_rows}
 
 
 @MIXERS.register("gqa_attention")
@@ -207,7 +211,7 @@ class GQAAttention(Mixer):
                 part_out=part_out, part_lse=part_lse,
                 cu_seqlens=batch.cu_seqlens, entry_start=batch.entry_start, entry_slot=batch.entry_slot,
                 block_table=group.block_table, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
-                window=self.window, scale=self.scale, fault=batch.fault,
+                window=self.window, scale=self.scale, fault=batch.fault, decode_rows=plan.get("decode_rows", 0),
             )
             return
         kernels.attention_generic(

@@ -333,7 +333,7 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
         assert bool(close) == expect_far
 
 
-def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None):
+def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None, decode_kernel="auto"):
     """The tensor-core kernels over the same paged case, items cut by the part's own planner."""
     import numpy as np
 
@@ -369,7 +369,7 @@ def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None):
         entry_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
         entry_slot=torch.tensor(case["slots"], dtype=torch.int32, device=DEV),
         block_table=case["table"].to(DEV), num_heads=hq, num_kv_heads=hkv, head_dim=d,
-        window=window, scale=scale, fault=fault,
+        window=window, scale=scale, fault=fault, decode_kernel=decode_kernel,
     )
     assert fault.item() == 0
     return out.float().cpu().view(tokens, hq, d)
@@ -389,6 +389,26 @@ def test_attention_mma(hq, hkv, d, page, window, splits):
     case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=d + page)
     scale = d**-0.5
     got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, window)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+@pytest.mark.parametrize("decode_kernel", ["auto", "mma"])
+@pytest.mark.parametrize(
+    "hq,hkv,page,window,splits,lengths,new_counts",
+    [(32, 8, 16, 0, None, [1, 5, 128, 129, 1000, 257, 2049], [1, 1, 1, 1, 1, 1, 1]),
+     (8, 2, 16, 0, 3, [700, 64, 1], [1, 1, 1]),
+     (12, 3, 8, 100, None, [333, 50, 128], [1, 1, 2]),          # a window; two tokens still fit a decode tile
+     (40, 2, 64, 0, 2, [400, 90], [1, 1]),                      # a group of 20 rows: two decode tiles per request
+     (4, 4, 128, 0, None, [513, 127], [3, 1]),                  # pages as long as a block
+     (8, 8, 256, 77, 4, [900], [5])],
+)
+def test_attention_decode_kernels(hq, hkv, page, window, splits, lengths, new_counts, decode_kernel):
+    """Decode tiles at head size 128: the tcgen05 kernel (auto) and the mma.sync tiles give the plain result."""
+    dtype, d = torch.bfloat16, 128
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=page + hq)
+    scale = d**-0.5
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits, decode_kernel)
     want = plain_paged(case, dtype, lengths, new_counts, scale, window)
     torch.testing.assert_close(got, want, **for_dtype(dtype))
 
