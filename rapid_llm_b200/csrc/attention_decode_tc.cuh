@@ -73,34 +73,11 @@ struct DecodeTcArgs {
   int* fault;
 };
 
-__device__ __forceinline__ void tc_named_barrier(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-// 2^x for x <= 0 (or -inf): the bare instruction, without the library's handling of large inputs
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 // Largest value over the warp's lanes in one instruction.
 __device__ __forceinline__ float warp_max_redux(float v) {
   float r;
   asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
   return r;
-}
-// Whether the phase of the given parity has completed, without waiting for it.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ void fence_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // kRows: how many of the 16 columns of the products carry query rows (a power of two); the
@@ -417,7 +394,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
         const float m = warp_max_redux(s[n]);
         if (lane == 0) block_maxes[team][buf][quarter][n] = m;
       }
-      tc_named_barrier(1 + team, 128);
+      named_barrier(1 + team, 128);
       if (*aborted) break;
       float alpha[kRows], block_max[kRows];
 #pragma unroll

@@ -515,6 +515,7 @@ int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStrea
 }  // namespace rl
 
 #include "attention_decode_tc.cuh"
+#include "attention_prefill_tc.cuh"
 
 namespace rl {
 namespace RL_ATTENTION_NS {
@@ -522,6 +523,29 @@ namespace RL_ATTENTION_NS {
 // Whether the tcgen05 decode kernel takes this geometry (everything else: the mma.sync tiles).
 static bool decode_tc_supported(int page_size) {
   return kD == kTcD && page_size % 8 == 0 && (kTcKeys % page_size == 0 || page_size % kTcKeys == 0);
+}
+
+static bool g_prefill_tc_configured = false;   // file-local on purpose
+
+// Chunk tiles of 256 packed rows on the tcgen05 kernel (unsplit key ranges only).
+static int launch_prefill_tc(const AttentionArgs& a, int n_items, bool pdl, cudaStream_t stream) {
+  if (!g_prefill_tc_configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kPfSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_prefill_tc_configured = true;
+  }
+  CUtensorMap map;
+  const long long rows = static_cast<long long>(a.num_pages) * 2 * a.hkv * a.page_size;
+  int status = make_map(&map, a.cache, rows, kD, a.page_size < kPfKeys ? a.page_size : kPfKeys);
+  if (status != 0) return status;
+  PrefillTcArgs t;
+  t.q = a.q; t.out = a.out; t.items = a.items; t.cu_seqlens = a.cu_seqlens; t.entry_start = a.entry_start;
+  t.entry_slot = a.entry_slot; t.block_table = a.block_table; t.hq = a.hq; t.hkv = a.hkv;
+  t.page_size = a.page_size; t.num_pages = a.num_pages; t.max_pages = a.max_pages; t.slots = a.slots;
+  t.window = a.window; t.scale_log2 = a.scale_log2; t.fault = a.fault;
+  return launch_kernel(attention_prefill_tc_kernel, dim3(n_items, a.hkv), dim3(kPfThreads), kPfSmemBytes, stream, pdl,
+                       map, t);
 }
 
 static bool g_decode_tc_configured[5] = {};   // per row-count instantiation; file-local on purpose
@@ -593,8 +617,12 @@ int rl_attention_head_dim() { return attn::kD; }
 
 // Rows of a chunk tile and of a decode tile: the host cuts requests into items with these.
 int rl_attention_chunk_rows() { return 64; }
+// ... of a chunk tile of the tcgen05 kernel, or 0 where this build (head size) has none.
+int rl_attention_chunk_rows_tc() { return attn::kD == attn::kPfD ? attn::kPfRows : 0; }
 int rl_attention_decode_rows() { return 16; }
 
+// chunk_rows: packed rows per chunk item: 64 (or 0) = the mma.sync tiles, 256 = the tcgen05
+// kernel (head size 128, pages it takes, splits == 1).
 // decode_kernel: 0 = the tcgen05 kernel for decode tiles where it applies, 1 = always the
 // mma.sync tiles.  decode_rows: the most packed rows any decode tile has (0 = not known).
 // chunk_items / decode_items: [n, 4] int32 (entry, first packed row, split, 0).  With
@@ -606,7 +634,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
                      int window, int splits, float scale, int* fault, int pdl, int decode_kernel, int decode_rows,
-                     cudaStream_t stream) {
+                     int chunk_rows, cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
@@ -630,7 +658,16 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   bool merged_in_cluster = false;
   if (n_chunk_items > 0) {
     args.items = chunk_items;
-    status = attn::launch_attention<4, 1, 2>(args, n_chunk_items, pdl != 0, stream);
+    if (chunk_rows == attn::kPfRows) {
+      // the host cut the portions into tiles of the tcgen05 kernel: it must apply
+      if (attn::kD != attn::kPfD || !attn::decode_tc_supported(page_size) || splits != 1)
+        return static_cast<int>(cudaErrorInvalidValue);
+      status = attn::launch_prefill_tc(args, n_chunk_items, pdl != 0, stream);
+    } else if (chunk_rows == 64 || chunk_rows == 0) {
+      status = attn::launch_attention<4, 1, 2>(args, n_chunk_items, pdl != 0, stream);
+    } else {
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
     if (status != 0) return status;
   }
   if (n_decode_items > 0) {
@@ -737,7 +774,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, stream);
 }
 
 }  // extern "C"

@@ -224,6 +224,7 @@ class ModelRunner:
             lengths=np.asarray(lengths + [1] * pad, dtype=np.int32),
             starts=np.asarray(starts + [0] * pad, dtype=np.int32),
             decode_only=max(lengths) == 1,
+            page_size=cache.page_size,
         )
         planned: dict[tuple, dict[str, Any]] = {}
         for planner in self._planners:

@@ -323,8 +323,17 @@ def attention_generic(
 
 _ATTENTION_LIBS: dict[int, ctypes.CDLL] = {}
 
-CHUNK_TILE_ROWS = 64    # packed rows (token, head of the group) of a chunk tile
-DECODE_TILE_ROWS = 16   # ... of a decode tile
+CHUNK_TILE_ROWS = 64       # packed rows (token, head of the group) of a chunk tile of the mma.sync kernel
+CHUNK_TILE_ROWS_TC = 256   # ... of the tcgen05 kernel (head size 128, unsplit key ranges)
+DECODE_TILE_ROWS = 16      # ... of a decode tile
+TC_HEAD_DIM = 128
+
+
+def attention_tc_takes(head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention kernels take this head size and page size."""
+    if head_dim != TC_HEAD_DIM or page_size <= 0 or page_size % 8:
+        return False
+    return 128 % page_size == 0 or page_size % 128 == 0
 
 
 def attention_lib(head_dim: int) -> ctypes.CDLL:
@@ -335,13 +344,15 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         if lib.rl_attention_head_dim() != head_dim:
             raise KernelError(f"the attention library for head size {head_dim} was built for another size")
         if lib.rl_attention_chunk_rows() != CHUNK_TILE_ROWS or lib.rl_attention_decode_rows() != DECODE_TILE_ROWS:
             raise KernelError("the attention library's tile sizes differ from the host's")
+        if lib.rl_attention_chunk_rows_tc() != (CHUNK_TILE_ROWS_TC if head_dim == TC_HEAD_DIM else 0):
+            raise KernelError("the attention library's tensor-core tile size differs from the host's")
         _ATTENTION_LIBS[head_dim] = lib
     return lib
 
@@ -368,12 +379,15 @@ def attention_mma(
     fault: torch.Tensor,
     decode_kernel: str = "auto",
     decode_rows: int = 0,
+    chunk_rows: int = CHUNK_TILE_ROWS,
 ) -> torch.Tensor:
     """bfloat16 paged causal attention over work items the host cut the step into.
 
     Decode tiles run on the tcgen05 kernel where it applies (head size 128, pages of 8 to 64 or
     a multiple of 128 tokens) unless ``decode_kernel`` is ``"mma"``; ``decode_rows`` is the most
     packed rows any decode tile has (0 = not known), which lets that kernel unroll over fewer rows.
+    ``chunk_rows`` says how the chunk items were cut: :data:`CHUNK_TILE_ROWS` for the mma.sync
+    tiles, :data:`CHUNK_TILE_ROWS_TC` for the tcgen05 kernel (``splits`` must then be 1).
 
     ``chunk_items`` / ``decode_items`` are int32 ``[n, 4]`` rows ``(entry, first packed row,
     split, 0)`` for tiles of :data:`CHUNK_TILE_ROWS` / :data:`DECODE_TILE_ROWS` packed rows
@@ -409,7 +423,7 @@ def attention_mma(
             _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
-            _ptr(fault), int(PDL), 1 if decode_kernel == "mma" else 0, int(decode_rows), _stream(),
+            _ptr(fault), int(PDL), 1 if decode_kernel == "mma" else 0, int(decode_rows), int(chunk_rows), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )

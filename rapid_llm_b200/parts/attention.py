@@ -33,18 +33,20 @@ class AttentionItems(StepPlanner):
     """Cuts a step into the work items of the tensor-core attention kernels.
 
     Every entry's packed rows (token, head of the group) are tiled: entries of one token, or
-    of at most 16 packed rows, into decode tiles of 16 rows; the others into chunk tiles of
-    64.  When the tiles are too few to fill the GPU, each tile's key range is split into
-    ``splits`` parts (the same number for the whole step): a function of the number of
-    entries alone in a decode-only step, so that a captured decode graph replays the same
-    item list at every context length; bounded by the longest context otherwise.
+    of at most 16 packed rows, into decode tiles of 16 rows; the others into chunk tiles.  When
+    the tiles are too few to fill the GPU, each tile's key range is split into ``splits`` parts
+    (the same number for the whole step): a function of the number of entries alone in a
+    decode-only step, so that a captured decode graph replays the same item list at every
+    context length; bounded by the longest context otherwise.  Chunk tiles have 256 rows for the
+    tcgen05 kernel, which takes head size 128, the usual page sizes and unsplit key ranges, and
+    64 rows for the mma.sync kernel otherwise; the longest tiles come first in the list.
     The reference picks its split size per launch in the same spirit
     (``rapid_llm/kernels/ops/attention/flashdecoding.py:43-112``).
     """
 
-    def __init__(self, group: int, num_kv_heads: int) -> None:
-        self.group, self.num_kv_heads = int(group), int(num_kv_heads)
-        self.key = ("attention_items", self.group, self.num_kv_heads)
+    def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0) -> None:
+        self.group, self.num_kv_heads, self.head_dim = int(group), int(num_kv_heads), int(head_dim)
+        self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim)
 
     def capacity(self, max_tokens: int, max_entries: int) -> int:
         chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
@@ -53,33 +55,42 @@ class AttentionItems(StepPlanner):
 
     def plan(self, shape: StepShape) -> dict:
         lengths = np.asarray(shape.lengths, dtype=np.int64)
+        starts = np.asarray(shape.starts, dtype=np.int64)
         rows = lengths * self.group
         is_decode = (lengths == 1) | (rows <= kernels.DECODE_TILE_ROWS)
-        tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, kernels.CHUNK_TILE_ROWS)
-        tiles = -(-rows // tile_rows)
-        ctas = int(tiles.sum()) * self.num_kv_heads
-        target = DECODE_TARGET_CTAS if shape.decode_only else TARGET_CTAS
-        splits = max(1, min(MAX_SPLITS, target // max(ctas, 1)))
-        if not shape.decode_only:
-            longest = int((np.asarray(shape.starts, dtype=np.int64) + lengths).max())
-            splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
+        tensor_core = kernels.attention_tc_takes(self.head_dim, shape.page_size)
+        for chunk_rows in ((kernels.CHUNK_TILE_ROWS_TC, kernels.CHUNK_TILE_ROWS) if tensor_core else (kernels.CHUNK_TILE_ROWS,)):
+            tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, chunk_rows)
+            tiles = -(-rows // tile_rows)
+            ctas = int(tiles.sum()) * self.num_kv_heads
+            target = DECODE_TARGET_CTAS if shape.decode_only else TARGET_CTAS
+            splits = max(1, min(MAX_SPLITS, target // max(ctas, 1)))
+            if not shape.decode_only:
+                longest = int((starts + lengths).max())
+                splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
+            if splits == 1 or chunk_rows == kernels.CHUNK_TILE_ROWS or bool(is_decode.all()):
+                break                  # the tcgen05 chunk kernel does not split key ranges
         entry = np.repeat(np.arange(len(lengths), dtype=np.int64), tiles)
         first = np.concatenate(([0], np.cumsum(tiles)[:-1]))
         tile_index = np.arange(int(tiles.sum()), dtype=np.int64) - np.repeat(first, tiles)
         row0 = tile_index * np.repeat(tile_rows, tiles)
         decode_tile = np.repeat(is_decode, tiles)
+        # keys a tile has to walk: the tiles with the most go first, so that the last wave is short
+        keys = np.repeat(starts, tiles) + (row0 + np.repeat(tile_rows, tiles)) // self.group
 
         def items(mask: np.ndarray) -> np.ndarray:
-            count = int(mask.sum())
+            order = np.flatnonzero(mask)
+            order = order[np.argsort(-keys[order], kind="stable")]
+            count = len(order)
             out = np.zeros((count * splits, 4), dtype=np.int32)
-            out[:, 0] = np.repeat(entry[mask], splits)
-            out[:, 1] = np.repeat(row0[mask], splits)
+            out[:, 0] = np.repeat(entry[order], splits)
+            out[:, 1] = np.repeat(row0[order], splits)
             out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), count)
             return out
 
         decode_rows = int(np.minimum(rows[is_decode], kernels.DECODE_TILE_ROWS).max()) if is_decode.any() else 0
         return {"chunk_items": items(~decode_tile), "decode_items": items(decode_tile), "splits": splits,
-                "decode_rows": decode_rows}
+                "decode_rows": decode_rows, "chunk_rows": int(chunk_rows)}
 
 
 @MIXERS.register("gqa_attention")
@@ -111,7 +122,7 @@ class GQAAttention(Mixer):
         self.window = int(window)
         self.scale = float(scale) if scale is not None else self.d**-0.5
         self.shares_cache = bool(shares_cache)
-        self._items = AttentionItems(self.hq // self.hkv, self.hkv)
+        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", self.d))
 
@@ -212,6 +223,7 @@ class GQAAttention(Mixer):
                 cu_seqlens=batch.cu_seqlens, entry_start=batch.entry_start, entry_slot=batch.entry_slot,
                 block_table=group.block_table, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
                 window=self.window, scale=self.scale, fault=batch.fault, decode_rows=plan.get("decode_rows", 0),
+                chunk_rows=plan.get("chunk_rows", kernels.CHUNK_TILE_ROWS),
             )
             return
         kernels.attention_generic(

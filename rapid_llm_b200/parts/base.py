@@ -85,6 +85,7 @@ class StepShape:
     lengths: Any          # numpy int32 [entries]
     starts: Any           # numpy int32 [entries]
     decode_only: bool
+    page_size: int = 0    # tokens per cache page (0 = not said)
 
 
 class StepPlanner:

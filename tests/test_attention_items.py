@@ -61,3 +61,21 @@ def test_short_contexts_are_not_split_in_a_mixed_step():
     assert plan["splits"] == 1
     plan = planner.plan(StepShape(np.array([30, 1], np.int32), np.array([4000, 100], np.int32), decode_only=False))
     assert plan["splits"] > 1
+
+
+def test_chunk_tiles_follow_the_kernel_that_will_run():
+    planner = AttentionItems(4, 8, 128)
+    whole = StepShape(np.asarray([2048], dtype=np.int32), np.asarray([0], dtype=np.int32), False, page_size=16)
+    plan = planner.plan(whole)
+    assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1
+    assert len(plan["chunk_items"]) == 2048 * 4 // 256
+    # the longest tiles first
+    assert list(plan["chunk_items"][:, 1]) == sorted(plan["chunk_items"][:, 1], reverse=True)
+    # a short portion far into a long context wants its key range split: the mma.sync tiles take it
+    late = StepShape(np.asarray([40], dtype=np.int32), np.asarray([6000], dtype=np.int32), False, page_size=16)
+    plan = planner.plan(late)
+    assert plan["splits"] > 1 and plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS
+    # other head sizes or page sizes: the mma.sync tiles
+    assert AttentionItems(4, 8, 64).plan(whole)["chunk_rows"] == kernels.CHUNK_TILE_ROWS
+    odd = StepShape(np.asarray([2048], dtype=np.int32), np.asarray([0], dtype=np.int32), False, page_size=4)
+    assert planner.plan(odd)["chunk_rows"] == kernels.CHUNK_TILE_ROWS

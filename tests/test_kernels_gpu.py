@@ -333,17 +333,20 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
         assert bool(close) == expect_far
 
 
-def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None, decode_kernel="auto"):
-    """The tensor-core kernels over the same paged case, items cut by the part's own planner."""
+def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None, decode_kernel="auto", page=0):
+    """The tensor-core kernels over the same paged case, items cut by the part's own planner.
+
+    ``page`` (the cache's page size) lets the planner cut chunk tiles for the tcgen05 kernel
+    where it applies; 0 keeps the mma.sync tiles."""
     import numpy as np
 
     from rapid_llm_b200.parts.attention import AttentionItems
     from rapid_llm_b200.parts.base import StepShape
 
     starts = [length - new for length, new in zip(lengths, new_counts)]
-    planner = AttentionItems(hq // hkv, hkv)
+    planner = AttentionItems(hq // hkv, hkv, d)
     shape = StepShape(np.asarray(new_counts, dtype=np.int32), np.asarray(starts, dtype=np.int32),
-                      decode_only=max(new_counts) == 1)
+                      decode_only=max(new_counts) == 1, page_size=page)
     plan = planner.plan(shape)
     if splits is not None and splits != plan["splits"]:
         def respread(items):
@@ -351,7 +354,7 @@ def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None, d
             out = np.repeat(base, splits, axis=0)
             out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), len(base))
             return out
-        plan = {"chunk_items": respread(plan["chunk_items"]), "decode_items": respread(plan["decode_items"]), "splits": splits}
+        plan = dict(plan, chunk_items=respread(plan["chunk_items"]), decode_items=respread(plan["decode_items"]), splits=splits)
     q = case["q"].to(DEV).reshape(-1, hq * d).contiguous()
     out = torch.full_like(q, float("nan"))
     tokens = q.shape[0]
@@ -370,6 +373,7 @@ def run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits=None, d
         entry_slot=torch.tensor(case["slots"], dtype=torch.int32, device=DEV),
         block_table=case["table"].to(DEV), num_heads=hq, num_kv_heads=hkv, head_dim=d,
         window=window, scale=scale, fault=fault, decode_kernel=decode_kernel,
+        decode_rows=plan.get("decode_rows", 0), chunk_rows=plan.get("chunk_rows", 64),
     )
     assert fault.item() == 0
     return out.float().cpu().view(tokens, hq, d)
@@ -411,6 +415,44 @@ def test_attention_decode_kernels(hq, hkv, page, window, splits, lengths, new_co
     got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits, decode_kernel)
     want = plain_paged(case, dtype, lengths, new_counts, scale, window)
     torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+@pytest.mark.parametrize(
+    "hq,hkv,page,window,lengths,new_counts",
+    [(32, 8, 16, 0, [2048], [2048]),                                   # one whole prompt
+     (8, 2, 16, 0, [700, 300, 64, 129, 1], [700, 150, 33, 129, 1]),     # portions at odd offsets beside a decode token
+     (12, 3, 8, 100, [333, 500], [200, 37]),                            # a window, a group of four
+     (6, 1, 64, 0, [900, 130], [64, 130]),                              # six heads a group: tiles straddle tokens
+     (4, 4, 128, 0, [513, 260], [300, 260]),                            # one head a group, pages as long as a block
+     (16, 2, 32, 300, [1500], [257])],
+)
+def test_attention_prefill_tc(hq, hkv, page, window, lengths, new_counts):
+    """Chunk tiles of the tcgen05 kernel (head size 128) against the plain result."""
+    dtype, d = torch.bfloat16, 128
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=hq + page)
+    scale = d**-0.5
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, page=page)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, window)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+def test_attention_prefill_tc_finds_a_far_key_and_respects_the_window_edge():
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 2, 128, 16
+    length, far, new = 700, 13, 300
+    case = paged_case(dtype, hq, hkv, d, page, [length], [new], seed=3)
+    query = case["queries"][0][-1]
+    for head in range(hkv):
+        case["keys"][0][far, head] = 40.0 * query[head * (hq // hkv)] / query[head * (hq // hkv)].norm()
+    page_id = int(case["table"][case["slots"][0], far // page])
+    case["cache"][page_id, 0, :, far % page] = case["keys"][0][far].to(dtype)
+    scale = d**-0.5
+    for window, expect_far in [(0, True), (length - far, True), (length - far - 1, False)]:
+        got = run_mma(case, [length], [new], hq, hkv, d, scale, window, page=page)
+        want = plain_paged(case, dtype, [length], [new], scale, window)
+        torch.testing.assert_close(got, want, **for_dtype(dtype))
+        value = case["values"][0][far, 0].to(dtype).float()
+        close = (got[-1, 0] - value).abs().max() < 0.15
+        assert bool(close) == expect_far
 
 
 def test_attention_mma_decode_only_step_splits_by_entry_count():
