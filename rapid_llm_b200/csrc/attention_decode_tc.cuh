@@ -83,7 +83,7 @@ __device__ __forceinline__ float warp_max_redux(float v) {
 // kRows: how many of the 16 columns of the products carry query rows (a power of two); the
 // per-row work of the softmax threads is unrolled over exactly these.
 template <int kRows>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcThreads, 1)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const DecodeTcArgs args) {
   static_assert(kRows >= 1 && kRows <= kTcRows && (kRows & (kRows - 1)) == 0, "rows: a power of two up to 16");
   extern __shared__ unsigned char tc_smem_raw[];

@@ -58,7 +58,7 @@ struct PrefillTcArgs {
   int* fault;
 };
 
-__global__ void __launch_bounds__(kPfThreads)
+__global__ void __launch_bounds__(kPfThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const PrefillTcArgs args) {
   extern __shared__ unsigned char pf_smem_raw[];
   __shared__ __align__(8) uint64_t full_k[kPfStages], full_v[kPfStages], empty_k[kPfStages], empty_v[kPfStages];
