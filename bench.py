@@ -186,6 +186,41 @@ def prefill_run(llm, warmup: int, seed: int) -> float:
     return min(times)
 
 
+def write_timeline(llm, batch: int, path: str, seed: int) -> dict:
+    """Start, duration and overlap of every kernel of three decode steps (CUPTI through torch.profiler)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from rapid_llm_b200 import SamplingParams
+
+    scheduler, runner = llm.scheduler, llm.runner
+    vocab = runner.model.spec.vocab_size
+    params = SamplingParams.greedy(max_gen_len=64 + -(-batch * PROMPT_LEN // PREFILL_TOKENS))
+    requests = [scheduler.add_request(p, params) for p in random_prompts(batch, PROMPT_LEN, vocab, seed)]
+    while any(r.num_computed_tokens < len(r.prompt_token_ids) for r in requests):
+        scheduler.step()
+    for _ in range(5):
+        scheduler.step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            scheduler.step()
+        torch.cuda.synchronize()
+    events = sorted(
+        (e.time_range.start, e.time_range.end - e.time_range.start, e.name)
+        for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+    )
+    for request in requests:
+        scheduler.abort(request)
+    origin, latest = events[0][0], events[0][0]
+    lines = ["start_us  duration_us  gap_to_previous_end_us  kernel"]
+    for begin, duration, name in events:
+        lines.append(f"{begin - origin:9.1f} {duration:8.1f} {begin - latest:8.1f}  {name[:80]}")
+        latest = max(latest, begin + duration)
+    Path(path).write_text("\n".join(lines) + "\n")
+    return {"timeline": path, "events": len(events), "batch": batch}
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -208,6 +243,8 @@ def run_ours(args) -> dict:
     runner = ModelRunner.from_random(config, seed=0, config=engine)
     llm = LLM.from_runner(runner)
 
+    if args.timeline:
+        return write_timeline(llm, args.batch, args.timeline, seed=args.batch)
     prefill_ms = prefill_run(llm, args.warmup, seed=11) if "prefill" in args.parts else float("nan")
     results = {}
     for batch in batches:
@@ -339,6 +376,8 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--parts", default="prefill,points", help="extra measurements beside the main decode run "
                         "(comma-separated: prefill, points); an empty string leaves only the main run, for profiling")
+    parser.add_argument("--timeline", default=None, help="instead of measuring, write the kernel timeline of three "
+                        "decode steps at --batch (start, duration, gap; CUPTI through torch.profiler) to this file")
     parser.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = parser.parse_args()
     if args.gpus != 1:

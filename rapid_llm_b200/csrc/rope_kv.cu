@@ -32,120 +32,145 @@ struct RopeArgs {
   int* fault;
 };
 
-// One warp per (token, head).  kVec > 0: the head size is 32 * kVec, the whole head rotates
-// (rotary == d), and lane l holds the kVec consecutive elements from l * kVec in registers;
-// its rotation partner (element + d/2) sits in lane l ^ 16.  kVec == 0: any head size up to
-// 256 and any even rotary width, element by element through shared memory.
+// One warp per (token, run of heads).  kVec > 0: the head size is 32 * kVec, the whole head
+// rotates (rotary == d), and lane l holds the kVec consecutive elements from l * kVec in
+// registers; its rotation partner (element + d/2) sits in lane l ^ 16.  A warp then takes
+// `heads_per_warp` consecutive heads of its token and fetches the token's angles and the norm
+// weights once for all of them (many heads a warp when there are many tokens, one when there
+// are few and the work has to spread over the SMs).  kVec == 0: any head size up to 256 and
+// any even rotary width, one head a warp, element by element through shared memory.
 template <typename T, int kVec>
-__global__ void qk_norm_rope_write_kernel(const RopeArgs a) {
+__global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_warp) {
   __shared__ float staged[kVec == 0 ? kRopeWarps : 1][kVec == 0 ? kMaxHeadDim : 1];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_per_token = a.kv_dest ? a.hq + 2 * a.hkv : a.hq;
-  const long long item = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
-  if (item >= static_cast<long long>(a.tokens) * heads_per_token) {
+  const int warps_per_token = (heads_per_token + heads_per_warp - 1) / heads_per_warp;
+  const long long index = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
+  if (index >= static_cast<long long>(a.tokens) * warps_per_token) {
     pdl_wait();
     return;
   }
   const int d = a.d;
-  const int t = static_cast<int>(item / heads_per_token);
-  const int head = static_cast<int>(item - static_cast<long long>(t) * heads_per_token);
-  const T* src = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
-  const float* b = a.bias ? a.bias + static_cast<size_t>(head) * d : nullptr;
-
-  // 0 = q, 1 = k, 2 = v
-  const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);
-  T* dst = nullptr;
-  bool bad_page = false;
-  if (kind == 0) {
-    dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
-  } else {
-    const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
-    const int dest = a.kv_dest[t];
-    const int page = dest / a.page_size, offset = dest - page * a.page_size;
-    if (dest < 0 || page >= a.num_pages) {
-      if (lane == 0) atomicOr(a.fault, kFaultPageId);
-      bad_page = true;
-    } else {
-      dst = static_cast<T*>(a.cache) +
-            ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
-    }
-  }
+  const int t = static_cast<int>(index / warps_per_token);
+  const int head_begin = static_cast<int>(index - static_cast<long long>(t) * warps_per_token) * heads_per_warp;
+  const int head_end = min(heads_per_token, head_begin + heads_per_warp);
   int pos = a.positions[t];
-  if (kind != 2 && (pos < 0 || pos >= a.max_pos)) {
-    if (lane == 0) atomicOr(a.fault, kFaultPosition);
+  if (pos < 0 || pos >= a.max_pos) {
+    if (lane == 0 && head_begin < a.hq + a.hkv) atomicOr(a.fault, kFaultPosition);   // only rotated heads need it
     pos = 0;
   }
-  const float* w = kind == 0 ? a.q_weight : (kind == 1 ? a.k_weight : nullptr);
   const int half = a.rotary >> 1;
+  // where the token's key and value go
+  int page = 0, offset = 0;
+  bool bad_page = false;
+  if (a.kv_dest) {
+    const int dest = a.kv_dest[t];
+    page = dest / a.page_size;
+    offset = dest - page * a.page_size;
+    bad_page = dest < 0 || page >= a.num_pages;
+  }
 
   if constexpr (kVec > 0) {
     const int at = lane * kVec;
-    float v[kVec], wv[kVec], c[kVec], s[kVec];
     const int angle = at < half ? at : at - half;      // kVec divides d / 2, so a lane never straddles
+    float c[kVec], s[kVec], qw[kVec], kw[kVec];
 #pragma unroll
     for (int i = 0; i < kVec; ++i) {
-      wv[i] = w ? w[at + i] : 1.0f;
-      c[i] = kind == 2 ? 1.0f : a.cos_table[static_cast<size_t>(pos) * half + angle + i];
-      s[i] = kind == 2 ? 0.0f : a.sin_table[static_cast<size_t>(pos) * half + angle + i];
+      c[i] = a.cos_table[static_cast<size_t>(pos) * half + angle + i];
+      s[i] = a.sin_table[static_cast<size_t>(pos) * half + angle + i];
+      qw[i] = a.q_weight ? a.q_weight[at + i] : 1.0f;
+      kw[i] = a.k_weight ? a.k_weight[at + i] : 1.0f;
     }
     pdl_wait();
-    if (bad_page) return;
-    if constexpr (kVec == 8) {
-      load8(src + at, v);
-    } else if constexpr (sizeof(T) == 2 && kVec == 4) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(src + at);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
-      v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
-    } else {
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) v[i] = to_float(src[at + i]);
-    }
-    float sum_sq = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) {
-      if (b) v[i] += b[at + i];
-      sum_sq += v[i] * v[i];
-    }
-    if (kind != 2) {
-      if (w) {
-        sum_sq = warp_sum(sum_sq);
-        const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) v[i] = v[i] * inv_rms * wv[i];
+    for (int head = head_begin; head < head_end; ++head) {
+      const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // q, k, v
+      const T* src = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
+      T* dst;
+      if (kind == 0) {
+        dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
+      } else {
+        if (bad_page) {
+          if (lane == 0) atomicOr(a.fault, kFaultPageId);
+          continue;
+        }
+        const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+        dst = static_cast<T*>(a.cache) +
+              ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
       }
+      float v[kVec];
+      if constexpr (kVec == 8) {
+        load8(src + at, v);
+      } else if constexpr (sizeof(T) == 2 && kVec == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(src + at);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+      } else {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) v[i] = to_float(src[at + i]);
+      }
+      float sum_sq = 0.0f;
 #pragma unroll
       for (int i = 0; i < kVec; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-        // first half: x1 * c - x2 * s; second half: x2 * c + x1 * s
-        v[i] = lane < 16 ? v[i] * c[i] - other * s[i] : v[i] * c[i] + other * s[i];
+        if (a.bias) v[i] += a.bias[static_cast<size_t>(head) * d + at + i];
+        sum_sq += v[i] * v[i];
       }
-    }
-    if constexpr (kVec == 8) {
-      if constexpr (sizeof(T) == 2) {
-        uint4 raw;
+      if (kind != 2) {
+        if (kind == 0 ? a.q_weight != nullptr : a.k_weight != nullptr) {
+          sum_sq = warp_sum(sum_sq);
+          const float inv_rms = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+#pragma unroll
+          for (int i = 0; i < kVec; ++i) v[i] = v[i] * inv_rms * (kind == 0 ? qw[i] : kw[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+          // first half: x1 * c - x2 * s; second half: x2 * c + x1 * s
+          v[i] = lane < 16 ? v[i] * c[i] - other * s[i] : v[i] * c[i] + other * s[i];
+        }
+      }
+      if constexpr (kVec == 8) {
+        if constexpr (sizeof(T) == 2) {
+          uint4 raw;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+          *reinterpret_cast<uint4*>(dst + at) = raw;
+        } else {
+          *reinterpret_cast<float4*>(dst + at) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(dst + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      } else if constexpr (sizeof(T) == 2 && kVec == 4) {
+        uint2 raw;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        *reinterpret_cast<uint4*>(dst + at) = raw;
+        h[0] = __floats2bfloat162_rn(v[0], v[1]);
+        h[1] = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(dst + at) = raw;
       } else {
-        *reinterpret_cast<float4*>(dst + at) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(dst + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      }
-    } else if constexpr (sizeof(T) == 2 && kVec == 4) {
-      uint2 raw;
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-      h[0] = __floats2bfloat162_rn(v[0], v[1]);
-      h[1] = __floats2bfloat162_rn(v[2], v[3]);
-      *reinterpret_cast<uint2*>(dst + at) = raw;
-    } else {
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) dst[at + i] = from_float<T>(v[i]);
+        for (int i = 0; i < kVec; ++i) dst[at + i] = from_float<T>(v[i]);
+      }
     }
   } else {
     pdl_wait();
-    if (bad_page) return;
+    const int head = head_begin;                       // one head a warp on this path
+    const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);
+    const T* src = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
+    const float* b = a.bias ? a.bias + static_cast<size_t>(head) * d : nullptr;
+    T* dst;
+    if (kind == 0) {
+      dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
+    } else {
+      if (bad_page) {
+        if (lane == 0) atomicOr(a.fault, kFaultPageId);
+        return;
+      }
+      const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+      dst = static_cast<T*>(a.cache) +
+            ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
+    }
+    const float* w = kind == 0 ? a.q_weight : (kind == 1 ? a.k_weight : nullptr);
     float* mine = staged[warp];
     float sum_sq = 0.0f;
     for (int i = lane; i < d; i += 32) {
@@ -194,9 +219,7 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
   if (d > rl::kMaxHeadDim || d <= 0 || rotary < 0 || rotary > d || (rotary & 1) ||
       (kv_dest != nullptr && cache == nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
-  const long long items =
-      static_cast<long long>(tokens) * (kv_dest ? hq + 2 * hkv : hq);
-  const unsigned blocks = static_cast<unsigned>((items + rl::kRopeWarps - 1) / rl::kRopeWarps);
+  const int heads_per_token = kv_dest ? hq + 2 * hkv : hq;
   rl::RopeArgs a;
   a.qkv = qkv; a.bias = bias; a.q_weight = q_weight; a.k_weight = k_weight;
   a.cos_table = cos_table; a.sin_table = sin_table; a.positions = positions; a.kv_dest = kv_dest;
@@ -207,13 +230,18 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
   const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                          reinterpret_cast<uintptr_t>(cache)) & 15) == 0 && row_width % 8 == 0;
   const int vec = (rotary == d && d % 32 == 0 && aligned) ? d / 32 : 0;
-  const dim3 grid(blocks), block(rl::kRopeWarps * 32);
+  // a warp takes several heads of a token once there are enough tokens to fill the GPU anyway
+  int heads_per_warp = 1;
+  if (vec > 0 && static_cast<long long>(tokens) * heads_per_token >= 148ll * 64 * 8)
+    heads_per_warp = 8;
+  const long long warps = static_cast<long long>(tokens) * ((heads_per_token + heads_per_warp - 1) / heads_per_warp);
+  const dim3 grid(static_cast<unsigned>((warps + rl::kRopeWarps - 1) / rl::kRopeWarps)), block(rl::kRopeWarps * 32);
   RL_DISPATCH_DTYPE(dtype, {
-    if (vec == 8) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 8>, grid, block, 0, stream, pdl != 0, a);
-    if (vec == 4) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 4>, grid, block, 0, stream, pdl != 0, a);
-    if (vec == 2) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 2>, grid, block, 0, stream, pdl != 0, a);
-    if (vec == 1) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 1>, grid, block, 0, stream, pdl != 0, a);
-    return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 0>, grid, block, 0, stream, pdl != 0, a);
+    if (vec == 8) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 8>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
+    if (vec == 4) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 4>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
+    if (vec == 2) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 2>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
+    if (vec == 1) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 1>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
+    return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 0>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
   });
   return 0;
 }

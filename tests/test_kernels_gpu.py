@@ -200,7 +200,17 @@ def test_gemm_bf16_refuses_rows_that_are_no_multiple_of_16_bytes():
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hkv,d,rotary,page", [(4, 2, 16, 16, 4), (6, 1, 48, 48, 8), (5, 5, 128, 64, 16), (3, 3, 256, 256, 1)])
 def test_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page):
-    tokens, eps, theta, max_pos, pages = 21, 1e-5, 50000.0, 300, 40
+    check_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page, tokens=21, pages=40)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_norm_rope_write_with_many_tokens(dtype):
+    """Enough tokens that a warp takes a run of heads of its token (10 heads: runs of 8 and 2)."""
+    check_qk_norm_rope_write(dtype, hq=6, hkv=2, d=128, rotary=128, page=16, tokens=7600, pages=500)
+
+
+def check_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page, tokens, pages):
+    eps, theta, max_pos = 1e-5, 50000.0, 300
     qkv = rand((tokens, (hq + 2 * hkv) * d), dtype, seed=8).to(DEV)
     qw = (1 + 0.1 * rand((d,), torch.float32, seed=9)).to(DEV)
     kw = (1 + 0.1 * rand((d,), torch.float32, seed=10)).to(DEV)
