@@ -78,7 +78,7 @@ def run_batch(args) -> int:
         _model_dir(args), max_seq_len=args.max_seq_len, max_gpu_num_blocks=args.max_gpu_num_blocks,
         device=args.device, use_cuda_graph=args.cuda_graph, dtype=args.dtype, page_size=args.page_size,
         max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
-        max_chunk_size=args.max_chunk_size,
+        max_chunk_size=args.max_chunk_size, run_ahead=args.run_ahead,
     )
     started = time.perf_counter()
     outputs = llm.generate(prompts, _sampling(args))
@@ -123,6 +123,8 @@ def build_parser() -> argparse.ArgumentParser:
     batch.add_argument("--max-num-seqs", type=int, default=32)
     batch.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=True,
                        help="Capture decode CUDA graphs (default: %(default)s)")
+    batch.add_argument("--run-ahead", action=argparse.BooleanOptionalAction, default=True,
+                       help="Enqueue a step before the previous step's tokens are read (default: %(default)s)")
     batch.add_argument("--show-stats", action="store_true", help="Print throughput and per-request timings")
     batch.set_defaults(handler=run_batch)
 

@@ -77,6 +77,28 @@ __device__ __forceinline__ MaxIndex block_argmax(MaxIndex v, float* fscratch, in
   return r;
 }
 
+constexpr int kCuts = 15;     // thresholds tried per sweep of the nucleus search (a 16-way split)
+
+// Sums of kCuts values over the block, every thread gets all of them; the tree is fixed.
+__device__ __forceinline__ void block_sum_many(float (&v)[kCuts], float (*scratch)[kCuts]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int k = 0; k < kCuts; ++k) v[k] = warp_sum(v[k]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < kCuts; ++k) scratch[warp][k] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kCuts; ++k) {
+    float total = 0.0f;
+    for (int w = 0; w < warps; ++w) total += scratch[w][k];
+    v[k] = total;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
@@ -92,6 +114,7 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
   __shared__ float fscratch[32];
   __shared__ int iscratch[32];
   __shared__ float warp_totals[32];
+  __shared__ float many_scratch[32][kCuts];
   pdl_trigger();
   const int row = blockIdx.x;
   const T* x = logits + static_cast<size_t>(row) * row_stride;
@@ -111,38 +134,34 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
     }
     __syncthreads();
   }
-  auto value = [&](int i) -> float {
-    float v = to_float(x[i]);
+  auto adjust = [&](float v, int i) -> float {
     if (has_pen && ((seen_bits[i >> 5] >> (i & 31)) & 1u)) v = v < 0.0f ? v * pen : v / pen;
     return v;
   };
-
-  // Greedy pick: needed for greedy rows and as the fallback of the draw.
-  MaxIndex best{-INFINITY, 0x7fffffff};
-  // rows that start on a 16-byte boundary are read eight elements at a time; a thread still
-  // meets its indices in rising order, so its strict comparison keeps the first maximum
+  // Every sweep over the row: rows that start on a 16-byte boundary are read eight elements at
+  // a time (thread t takes elements 8 t .. 8 t + 7, then 8 (t + threads) ..., in rising order),
+  // the rest element by element.  fn(index, value) sees each element once.
   const bool vector = (reinterpret_cast<uintptr_t>(x) & (sizeof(T) == 2 ? 15 : 31)) == 0;
   const int vector_end = vector ? (vocab & ~7) : 0;
-  for (int c = threadIdx.x * 8; c < vector_end; c += blockDim.x * 8) {
-    float v[8];
-    load8(x + c, v);
+  auto sweep = [&](auto&& fn) {
+    for (int c = threadIdx.x * 8; c < vector_end; c += blockDim.x * 8) {
+      float v[8];
+      load8(x + c, v);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float e = v[j];
-      if (has_pen && ((seen_bits[(c + j) >> 5] >> ((c + j) & 31)) & 1u)) e = e < 0.0f ? e * pen : e / pen;
-      if (e > best.value) {
-        best.value = e;
-        best.index = c + j;
-      }
+      for (int j = 0; j < 8; ++j) fn(c + j, adjust(v[j], c + j));
     }
-  }
-  for (int i = vector_end + threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = value(i);
+    for (int i = vector_end + threadIdx.x; i < vocab; i += blockDim.x) fn(i, adjust(to_float(x[i]), i));
+  };
+
+  // Greedy pick: needed for greedy rows and as the fallback of the draw.  A thread meets its
+  // indices in rising order, so its strict comparison keeps the first maximum.
+  MaxIndex best{-INFINITY, 0x7fffffff};
+  sweep([&](int i, float v) {
     if (v > best.value) {
       best.value = v;
       best.index = i;
     }
-  }
+  });
   best = block_argmax(best, fscratch, iscratch);
   if (best.index < 0 || best.index >= vocab) best.index = 0;  // all -inf or NaN
   if (temp <= 0.0f) {
@@ -153,25 +172,48 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
   const float inv_t = 1.0f / temp;
   const float peak = best.value * inv_t;
   float z = 0.0f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) z += expf(value(i) * inv_t - peak);
+  sweep([&](int, float v) { z += expf(v * inv_t - peak); });
   z = block_sum(z, fscratch);
 
   float threshold = 0.0f;
   const float p = top_p ? top_p[row] : 1.0f;
   if (p < 1.0f) {
     // Smallest e* with (mass of tokens whose weight exceeds e*) <= p * Z; kept = weight >= e*.
+    // The mass above a cut falls as the cut rises, so the search over the cut's bit pattern
+    // tries kCuts cuts per sweep and keeps the sixteenth of the range that holds e*.
     const float budget = p * z;
     unsigned lo = 0u, hi = __float_as_uint(1.0f);
     while (lo < hi) {
-      const unsigned mid = lo + ((hi - lo) >> 1);
-      const float cut = __uint_as_float(mid);
-      float above = 0.0f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float e = expf(value(i) * inv_t - peak);
-        if (e > cut) above += e;
+      const unsigned width = hi - lo;
+      unsigned cut_bits[kCuts];
+      float cut[kCuts], above[kCuts];
+#pragma unroll
+      for (int k = 0; k < kCuts; ++k) {
+        // distinct and rising while width >= 16; for narrow ranges some repeat, which is harmless
+        cut_bits[k] = lo + static_cast<unsigned>((static_cast<unsigned long long>(width) * (k + 1)) >> 4);
+        if (cut_bits[k] >= hi) cut_bits[k] = hi - 1;
+        cut[k] = __uint_as_float(cut_bits[k]);
+        above[k] = 0.0f;
       }
-      above = block_sum(above, fscratch);
-      if (above <= budget) hi = mid; else lo = mid + 1u;
+      sweep([&](int, float v) {
+        const float e = expf(v * inv_t - peak);
+#pragma unroll
+        for (int k = 0; k < kCuts; ++k)
+          if (e > cut[k]) above[k] += e;
+      });
+      block_sum_many(above, many_scratch);
+      // the first cut that satisfies the budget bounds e* from above, the one before from below
+      unsigned new_lo = cut_bits[kCuts - 1] + 1u, new_hi = hi;
+#pragma unroll
+      for (int k = kCuts - 1; k >= 0; --k) {
+        if (above[k] <= budget) {
+          new_hi = cut_bits[k];
+          new_lo = k > 0 ? cut_bits[k - 1] + 1u : lo;
+        }
+      }
+      if (new_lo > new_hi) new_lo = new_hi;
+      lo = new_lo;
+      hi = new_hi;
     }
     threshold = __uint_as_float(lo);
   }
@@ -183,7 +225,7 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
   const int end = min(vocab, begin + chunk);
   float local = 0.0f;
   for (int i = begin; i < end; ++i) {
-    const float e = expf(value(i) * inv_t - peak);
+    const float e = expf(adjust(to_float(x[i]), i) * inv_t - peak);
     if (e >= threshold) local += e;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -220,7 +262,7 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
     float running = before;
     int pick = -1;
     for (int i = begin; i < end; ++i) {
-      const float e = expf(value(i) * inv_t - peak);
+      const float e = expf(adjust(to_float(x[i]), i) * inv_t - peak);
       if (e >= threshold) {
         running += e;
         pick = i;
@@ -229,6 +271,258 @@ sample_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
     }
     if (pick >= 0) out[row] = pick;
   }
+}
+
+// ------------------------------------------------------------------------------------------
+// The same selection with a row spread over a thread-block cluster: each CTA keeps its slice of
+// the row's (penalised) values in shared memory, so the row is read from global memory once,
+// exponentials are taken once, and the sweeps of the nucleus search run over shared memory on
+// kSampleCluster SMs instead of one.  Sums and maxima are combined over the cluster through
+// distributed shared memory in rank order, so the result does not depend on timing.
+constexpr int kSampleCluster = 8;
+constexpr int kSampleThreads = 512;
+constexpr int kSampleMaxSlice = 48 * 1024;      // floats of one CTA's slice (192 KB)
+
+__device__ __forceinline__ void sample_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float sample_peer_f32(const float* local, unsigned rank) {
+  unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(local)), remote;
+  float value;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(address), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+  return value;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads, 1)
+sample_cluster_kernel(const T* __restrict__ logits, int vocab, long long row_stride, int slice,
+                      const float* __restrict__ temperature, const float* __restrict__ top_p,
+                      const float* __restrict__ penalty, const unsigned long long* __restrict__ seeds,
+                      const int* __restrict__ counters, const int* __restrict__ seen_tokens,
+                      const int* __restrict__ seen_offsets, int* __restrict__ out) {
+  extern __shared__ float slice_values[];          // [slice]
+  __shared__ float fscratch[32];
+  __shared__ int iscratch[32];
+  __shared__ float many_scratch[32][kCuts];
+  __shared__ float warp_totals[32];
+  __shared__ float share_f[2][kCuts + 1];          // this CTA's partial sums, read by its peers
+  __shared__ float gathered[kCuts + 1];            // the cluster's sums, fetched by a few threads for all
+  __shared__ int share_i;
+  pdl_trigger();
+  const int row = blockIdx.y;
+  const unsigned rank = blockIdx.x;                // cluster = the x dimension
+  const T* x = logits + static_cast<size_t>(row) * row_stride;
+  const int begin = min(vocab, static_cast<int>(rank) * slice), end = min(vocab, begin + slice);
+  const int count = end - begin;
+  pdl_wait();
+  const float temp = temperature ? temperature[row] : 0.0f;
+  const float pen = penalty ? penalty[row] : 1.0f;
+  const int seen_begin = seen_offsets ? seen_offsets[row] : 0;
+  const int seen_end = seen_offsets ? seen_offsets[row + 1] : 0;
+  const bool has_pen = pen != 1.0f && seen_tokens != nullptr && seen_end > seen_begin;
+
+  // the slice, as float; slices start on multiples of 8 elements, so an aligned row reads 16 bytes a time
+  const bool vector = (reinterpret_cast<uintptr_t>(x) & (sizeof(T) == 2 ? 15 : 31)) == 0;
+  const int vector_count = vector ? (count & ~7) : 0;
+  for (int c = threadIdx.x * 8; c < vector_count; c += blockDim.x * 8) {
+    float v[8];
+    load8(x + begin + c, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) slice_values[c + j] = v[j];
+  }
+  for (int i = vector_count + threadIdx.x; i < count; i += blockDim.x) slice_values[i] = to_float(x[begin + i]);
+  __syncthreads();
+  if (has_pen) {
+    // every generated token once: the first of equal ids in the list applies the penalty
+    for (int i = seen_begin + threadIdx.x; i < seen_end; i += blockDim.x) {
+      const int id = seen_tokens[i];
+      if (id < begin || id >= end) continue;
+      bool first = true;
+      for (int j = seen_begin; j < i && first; ++j) first = seen_tokens[j] != id;
+      if (first) {
+        const float v = slice_values[id - begin];
+        slice_values[id - begin] = v < 0.0f ? v * pen : v / pen;
+      }
+    }
+    __syncthreads();
+  }
+
+  // over the cluster: partial results go to share_f / share_i, every CTA reads all ranks
+  int round = 0;
+  auto cluster_sum = [&](float mine) {
+    const int slot = round++ & 1;
+    if (threadIdx.x == 0) share_f[slot][0] = mine;
+    sample_cluster_sync();
+    if (threadIdx.x == 0) {                          // remote reads are slow: one thread does them for all
+      float total = 0.0f;
+      for (unsigned r = 0; r < kSampleCluster; ++r) total += sample_peer_f32(&share_f[slot][0], r);
+      gathered[0] = total;
+    }
+    __syncthreads();
+    const float total = gathered[0];
+    __syncthreads();
+    return total;
+  };
+
+  // ---- the first maximum ---------------------------------------------------------------
+  MaxIndex best{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    const float v = slice_values[i];
+    if (v > best.value) {
+      best.value = v;
+      best.index = begin + i;
+    }
+  }
+  best = block_argmax(best, fscratch, iscratch);
+  {
+    const int slot = round++ & 1;
+    if (threadIdx.x == 0) {
+      share_f[slot][0] = best.value;
+      share_i = best.index;
+    }
+    sample_cluster_sync();
+    MaxIndex all{-INFINITY, 0x7fffffff};
+    for (unsigned r = 0; r < kSampleCluster; ++r) {
+      MaxIndex theirs;
+      theirs.value = sample_peer_f32(&share_f[slot][0], r);
+      theirs.index = __float_as_int(sample_peer_f32(reinterpret_cast<const float*>(&share_i), r));
+      all = better(all, theirs);
+    }
+    best = all;
+    sample_cluster_sync();                           // share_i may be rewritten only after every read
+  }
+  if (best.index < 0 || best.index >= vocab) best.index = 0;
+  if (temp <= 0.0f) {
+    if (rank == 0 && threadIdx.x == 0) out[row] = best.index;
+    return;                                          // the whole cluster takes this branch
+  }
+
+  // ---- weights, their sum, the nucleus -----------------------------------------------------
+  const float inv_t = 1.0f / temp;
+  const float peak = best.value * inv_t;
+  float z = 0.0f;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    const float e = expf(slice_values[i] * inv_t - peak);
+    slice_values[i] = e;
+    z += e;
+  }
+  z = cluster_sum(block_sum(z, fscratch));
+
+  float threshold = 0.0f;
+  const float p = top_p ? top_p[row] : 1.0f;
+  if (p < 1.0f) {
+    const float budget = p * z;
+    unsigned lo = 0u, hi = __float_as_uint(1.0f);
+    while (lo < hi) {
+      const unsigned width = hi - lo;
+      unsigned cut_bits[kCuts];
+      float cut[kCuts], above[kCuts];
+#pragma unroll
+      for (int k = 0; k < kCuts; ++k) {
+        cut_bits[k] = lo + static_cast<unsigned>((static_cast<unsigned long long>(width) * (k + 1)) >> 4);
+        if (cut_bits[k] >= hi) cut_bits[k] = hi - 1;
+        cut[k] = __uint_as_float(cut_bits[k]);
+        above[k] = 0.0f;
+      }
+      for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        const float e = slice_values[i];
+#pragma unroll
+        for (int k = 0; k < kCuts; ++k)
+          if (e > cut[k]) above[k] += e;
+      }
+      block_sum_many(above, many_scratch);
+      const int slot = round++ & 1;
+      if (threadIdx.x == 0) {
+#pragma unroll
+        for (int k = 0; k < kCuts; ++k) share_f[slot][k] = above[k];
+      }
+      sample_cluster_sync();
+      if (threadIdx.x < kCuts) {
+        float total = 0.0f;
+        for (unsigned r = 0; r < kSampleCluster; ++r) total += sample_peer_f32(&share_f[slot][threadIdx.x], r);
+        gathered[threadIdx.x] = total;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < kCuts; ++k) above[k] = gathered[k];
+      __syncthreads();
+      unsigned new_lo = cut_bits[kCuts - 1] + 1u, new_hi = hi;
+#pragma unroll
+      for (int k = kCuts - 1; k >= 0; --k) {
+        if (above[k] <= budget) {
+          new_hi = cut_bits[k];
+          new_lo = k > 0 ? cut_bits[k - 1] + 1u : lo;
+        }
+      }
+      if (new_lo > new_hi) new_lo = new_hi;
+      lo = new_lo;
+      hi = new_hi;
+    }
+    threshold = __uint_as_float(lo);
+  }
+
+  // ---- the draw: inverse CDF in index order over the kept weights ----------------------------
+  const int chunk = (count + blockDim.x - 1) / blockDim.x;
+  const int my_begin = min(count, static_cast<int>(threadIdx.x) * chunk), my_end = min(count, my_begin + chunk);
+  float local = 0.0f;
+  for (int i = my_begin; i < my_end; ++i) {
+    const float e = slice_values[i];
+    if (e >= threshold) local += e;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  float inclusive = local;
+#pragma unroll
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, inclusive, offset);
+    if (lane >= offset) inclusive += up;
+  }
+  __syncthreads();
+  if (lane == 31) warp_totals[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    float total = lane < warps ? warp_totals[lane] : 0.0f;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, total, offset);
+      if (lane >= offset) total += up;
+    }
+    warp_totals[lane] = total;  // inclusive over warps
+  }
+  __syncthreads();
+  // the CTAs' kept sums, in rank order: what lies before this CTA, and the whole
+  const int slot = round++ & 1;
+  if (threadIdx.x == 0) share_f[slot][0] = warp_totals[warps - 1];
+  sample_cluster_sync();
+  float cta_base = 0.0f, total = 0.0f;
+  for (unsigned r = 0; r < kSampleCluster; ++r) {
+    const float theirs = sample_peer_f32(&share_f[slot][0], r);
+    if (r < rank) cta_base += theirs;
+    total += theirs;
+  }
+  const float warp_base = cta_base + (warp == 0 ? 0.0f : warp_totals[warp - 1]);
+  const float upto = warp_base + inclusive;
+  float before = __shfl_up_sync(0xffffffffu, upto, 1);
+  if (lane == 0) before = warp_base;
+  const float u = philox_uniform(seeds[row], static_cast<uint32_t>(counters[row]));
+  const float target = u * total;
+  if (rank == 0 && threadIdx.x == 0) out[row] = best.index;    // stands if rounding leaves the target uncovered
+  sample_cluster_sync();                                         // ... and is overwritten only after it is written
+  if (local > 0.0f && before <= target && target < upto) {
+    float running = before;
+    int pick = -1;
+    for (int i = my_begin; i < my_end; ++i) {
+      const float e = slice_values[i];
+      if (e >= threshold) {
+        running += e;
+        pick = begin + i;
+        if (target < running) break;
+      }
+    }
+    if (pick >= 0) out[row] = pick;
+  }
+  sample_cluster_sync();                                         // nobody leaves while its shared memory may be read
 }
 
 }  // namespace rl
@@ -244,6 +538,38 @@ extern "C" int rl_sample(int dtype, const void* logits, int rows, int vocab, lon
   if (rows == 0) return 0;
   if (vocab <= 0 || (temperature != nullptr && (seeds == nullptr || counters == nullptr)))
     return static_cast<int>(cudaErrorInvalidValue);
+  if (temperature != nullptr) {
+    // rows that may draw: the row spread over a cluster, its values kept in shared memory
+    const int slice = ((vocab + rl::kSampleCluster - 1) / rl::kSampleCluster + 7) & ~7;
+    if (slice <= rl::kSampleMaxSlice) {
+      const size_t bytes = static_cast<size_t>(slice) * sizeof(float);
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(rl::kSampleCluster, rows);
+      config.blockDim = dim3(rl::kSampleThreads);
+      config.dynamicSmemBytes = bytes;
+      config.stream = stream;
+      cudaLaunchAttribute attributes[2];
+      attributes[0].id = cudaLaunchAttributeClusterDimension;
+      attributes[0].val.clusterDim.x = rl::kSampleCluster;
+      attributes[0].val.clusterDim.y = 1;
+      attributes[0].val.clusterDim.z = 1;
+      attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attributes[1].val.programmaticStreamSerializationAllowed = 1;
+      config.attrs = attributes;
+      config.numAttrs = pdl ? 2 : 1;
+      RL_DISPATCH_DTYPE(dtype, {
+        auto kernel = rl::sample_cluster_kernel<scalar_t>;
+        if (bytes > 40 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(bytes));
+          if (e != cudaSuccess) return static_cast<int>(e);
+        }
+        return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<const scalar_t*>(logits), vocab,
+                                                   row_stride, slice, temperature, top_p, penalty, seeds, counters,
+                                                   seen_tokens, seen_offsets, out));
+      });
+    }
+  }
   const size_t smem = (penalty && seen_tokens) ? static_cast<size_t>((vocab + 31) / 32) * 4 : 0;
   if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
   const int threads = vocab >= 8192 ? 1024 : 256;

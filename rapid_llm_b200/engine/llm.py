@@ -6,8 +6,10 @@ caps the cache, ``use_cuda_graph`` replays decode steps from captured graphs,
 ``hf_overrides`` replaces keys of ``config.json``.  Differences: prompts may be token-id
 lists (a random-weight model has no tokenizer), generation always goes through the
 continuous-batching scheduler, ``max_gpu_num_blocks`` counts cache pages of ``page_size``
-tokens (the reference counts token rows), and ``dtype`` selects the bfloat16 or the true
-float32 path.
+tokens (the reference counts token rows), ``dtype`` selects the bfloat16 or the true
+float32 path, and ``run_ahead`` (on by default) lets the scheduler enqueue a step before it has
+read the previous step's tokens, as the reference's launch/harvest pipeline does
+(``rapid_llm/engine/scheduler.py:817-933``).
 """
 
 from __future__ import annotations
@@ -57,6 +59,7 @@ class LLM:
         max_chunk_size: int = 512,
         enable_chunked_prefill: bool = True,
         enable_preemption: bool = True,
+        run_ahead: bool = True,
         hf_overrides: Mapping[str, Any] | None = None,
         stop_token_ids: Sequence[int] | None = None,
         runner: ModelRunner | None = None,
@@ -73,6 +76,7 @@ class LLM:
             max_chunk_size=max_chunk_size,
             enable_chunked_prefill=enable_chunked_prefill,
             enable_preemption=enable_preemption,
+            run_ahead=run_ahead,
             use_cuda_graph=True if use_cuda_graph is None else bool(use_cuda_graph),
         )
         if runner is not None:

@@ -108,3 +108,28 @@ def test_stop_token_ends_a_request(tiny_dirs, tiny_plain):
     output = llm.generate([prompt], SamplingParams.greedy(max_gen_len=6))[0]
     first_stop = free.index(free[3])
     assert output.token_ids == free[:first_stop] and output.outputs[0].finish_reason == "eos"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_does_not_change_a_token(tiny_dirs, tiny_dirs_bf16, dtype):
+    """Greedy and seeded temperature requests, a stop token, a pool small enough to evict: the same
+    tokens whether the scheduler reads every step's ids before planning the next or runs ahead."""
+    from rapid_llm_b200 import SamplingParams
+
+    folder = (tiny_dirs if dtype == "float32" else tiny_dirs_bf16)["B"]
+    prompts = random_prompts(384, [1, 7, 31, 64, 40, 3], 5)
+    params = [SamplingParams.greedy(max_gen_len=20), SamplingParams(temperature=0.7, top_p=0.9, repetition_penalty=1.0, max_gen_len=15, seed=3),
+              SamplingParams.greedy(max_gen_len=12), SamplingParams(temperature=1.0, top_p=1.0, repetition_penalty=1.0, max_gen_len=9, seed=8),
+              SamplingParams.greedy(max_gen_len=30), SamplingParams.greedy(max_gen_len=25)]
+    results = {}
+    for ahead in (False, True):
+        llm = make_llm(folder, dtype, "B", max_gpu_num_blocks=30, run_ahead=ahead)
+        # whatever the second request samples first becomes a stop token for everybody
+        probe = llm.generate([prompts[1]], [params[1]])[0].token_ids
+        llm.scheduler.stop_token_ids = {probe[4]}
+        outputs = llm.generate(prompts, params)
+        results[ahead] = [(o.token_ids, o.outputs[0].finish_reason) for o in outputs]
+        llm.runner.cache.check()
+        assert llm.runner.cache.num_free_slots == 4 and llm.scheduler._inflight is None
+    assert results[True] == results[False]
+    assert any(reason == "eos" for _, reason in results[True])
