@@ -279,11 +279,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int tile = static_cast<int>(blockIdx.y);
       const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
       const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
+      // where the other ranks keep this thread's row of the partial tile
+      uint32_t peer[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) peer[q] = q < args.k_split ? peer_smem(smem_base + n_local * 4, q) : 0u;
       for (int j = rank; j < BN && t0 + j < args.T; j += args.k_split) {
+        // all loads first, the sums (in rank order) after: a remote load takes hundreds of cycles,
+        // and a warp that adds each value as it arrives pays that once per rank
+        float gate_part[8], up_part[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          gate_part[q] = q < args.k_split ? load_peer_f32(peer[q] + j * kTileN * 4) : 0.0f;
+          up_part[q] = kSwiglu && q < args.k_split ? load_peer_f32(peer[q] + (BN + j) * kTileN * 4) : 0.0f;
+        }
         float gate = 0.0f, up = 0.0f;
-        for (int q = 0; q < args.k_split; ++q) {
-          gate += load_cluster_f32(smem_base + (j * kTileN + n_local) * 4, q);
-          if (kSwiglu) up += load_cluster_f32(smem_base + ((BN + j) * kTileN + n_local) * 4, q);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (q < args.k_split) {
+            gate += gate_part[q];
+            up += up_part[q];
+          }
         }
         if (n < args.N)
           args.out[static_cast<size_t>(t0 + j) * args.N + n] =

@@ -190,6 +190,20 @@ __device__ __forceinline__ float load_cluster_f32(uint32_t local_address, uint32
   return value;
 }
 
+// The address of `local_address` in the shared memory of the cluster's CTA `cta_rank`, and a load
+// from such an address (not volatile: the caller orders them with cluster barriers, and several
+// may be in flight at once).
+__device__ __forceinline__ uint32_t peer_smem(uint32_t local_address, uint32_t cta_rank) {
+  uint32_t remote;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(cta_rank));
+  return remote;
+}
+__device__ __forceinline__ float load_peer_f32(uint32_t remote_address) {
+  float value;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote_address));
+  return value;
+}
+
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
 // eight rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
 __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_address) {
