@@ -110,8 +110,10 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None)
+    parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     parser.add_argument("--workdir", default="/tmp/rapid_llm_b200_reference_arm")
     args = parser.parse_args()
+    globals()["PROMPT_LEN"] = args.prompt_len
 
     import torch
 

@@ -227,6 +227,8 @@ def run_ours(args) -> dict:
     from rapid_llm_b200 import LLM, EngineConfig, Qwen3Config
     from rapid_llm_b200.engine.runner import ModelRunner
 
+    if args.prompt_len + 2 * (args.steps + args.warmup) + 128 > CONTEXT:
+        raise SystemExit(f"--prompt-len {args.prompt_len} leaves no room to decode within the context of {CONTEXT}")
     peaks = measured_peaks()
     raw = dict(QWEN3_8B)
     layers_full = raw["num_hidden_layers"]
@@ -262,7 +264,7 @@ def run_ours(args) -> dict:
     flops = prefill_flops(raw, layers, PREFILL_TOKENS)
     meta_bytes = 4 * (args.batch * (3 + 1) + 3 * args.batch + 1 + args.batch)
     return {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 1024-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B shape, {PROMPT_LEN}-token prompts)",
         "value": round(value, 1),
         "unit": "tok/s",
         "n_gpus": 1,
@@ -316,7 +318,7 @@ def run_reference(args) -> dict:
     if not (ROOT / "baseline" / "_ref" / "rapid_llm").is_dir():
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
     command = [sys.executable, str(arm), "--steps", str(args.steps), "--warmup", str(args.warmup),
-               "--batch", str(args.batch)]
+               "--batch", str(args.batch), "--prompt-len", str(args.prompt_len)]
     if args.layers:
         command += ["--layers", str(args.layers)]
     try:
@@ -329,6 +331,9 @@ def run_reference(args) -> dict:
         tail = " | ".join((done.stderr or done.stdout).strip().splitlines()[-3:])[:400]
         return {"impl": "reference", "unavailable": f"the reference engine failed here (exit {done.returncode}): {tail}"}
     got = json.loads(lines[-1])
+    globals()["PROMPT_LEN"] = args.prompt_len
+    if PROMPT_LEN + 2 * (args.steps + args.warmup) + 128 > CONTEXT:
+        raise SystemExit(f"--prompt-len {args.prompt_len} leaves no room to decode within the context of {CONTEXT}")
     peaks = measured_peaks()
     raw = dict(QWEN3_8B)
     layers = got["layers"]
@@ -339,7 +344,7 @@ def run_reference(args) -> dict:
     achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
     flops = prefill_flops(raw, layers, PREFILL_TOKENS)
     return {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 1024-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B shape, {PROMPT_LEN}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(value / PUBLISHED_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
@@ -372,6 +377,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each request's prompt: the "
+                        "context that decoding starts from (the default is the configuration's)")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--parts", default="prefill,points", help="extra measurements beside the main decode run "
@@ -386,6 +393,7 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     args.parts = {part for part in args.parts.split(",") if part}
+    globals()["PROMPT_LEN"] = args.prompt_len
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

@@ -94,6 +94,9 @@ class ModelRunner:
         self._meta_host = [
             torch.empty(self._meta_capacity, dtype=torch.int32, pin_memory=True) for _ in range(2)
         ]
+        # a host buffer is written again only after the copy that last read it has run: steps that
+        # sample nothing are never waited for, so the host can be many steps ahead of the device
+        self._meta_copied: list[torch.cuda.Event | None] = [None, None]
         self._meta_flip = 0
         self._meta_device = torch.zeros(self._meta_capacity, dtype=torch.int32, device=self.device)
         # word 0: the kernels' fault word; words 1..: the step's sampled tokens (one read brings both)
@@ -203,8 +206,11 @@ class ModelRunner:
 
         g = len(cache.groups)
         rows = sum(len(entry.want) for entry in entries) + pad
-        host = self._meta_host[self._meta_flip]
+        flip = self._meta_flip
+        host = self._meta_host[flip]
         self._meta_flip ^= 1
+        if self._meta_copied[flip] is not None:
+            self._meta_copied[flip].synchronize()
         meta = host.numpy()
         offsets: dict[str, tuple[int, int]] = {}
         cursor = 0
@@ -278,6 +284,9 @@ class ModelRunner:
         if cursor > self._meta_capacity:
             raise ValueError("the step's metadata does not fit its buffer")
         self._meta_device[:cursor].copy_(host[:cursor], non_blocking=True)
+        if self._meta_copied[flip] is None:
+            self._meta_copied[flip] = torch.cuda.Event()
+        self._meta_copied[flip].record()
 
         def dev(name: str) -> torch.Tensor:
             begin, count = offsets[name]

@@ -154,6 +154,36 @@ def test_long_decoding(dtype, models):
     compare(rows, {"d": forward_logits(config, weights, tokens)}, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_that_nobody_waits_for(dtype, models):
+    """Portions that want no logits are never read back, so the host prepares several steps
+    while the device still works on an earlier one: held back here by a timed spin in front of
+    them.  Each step's metadata must reach the device as the host wrote it for that step."""
+    from rapid_llm_b200.engine.runner import StepEntry
+
+    dirs, plains = models[dtype]
+    config, weights = plains["A"]
+    tokens = random_tokens(config["vocab_size"], 90, 77)
+    plain = forward_logits(config, weights, tokens)
+    runner = make_runner(dirs["A"], dtype, max_tokens=128, page_size=PAGE_SIZES["A"])
+    cuts = [0, 7, 20, 23, 41, 52, 66, 81, 90]
+    assert runner.admit("warm")               # whatever the first steps load or allocate is done before
+    for begin, end in zip(cuts[:-1], cuts[1:]):
+        runner.step([StepEntry("warm", tokens[begin:end], [])])
+    runner.release("warm")
+    assert runner.admit("r")
+    torch.cuda.synchronize()
+    torch.cuda._sleep(400_000_000)          # about a fifth of a second of device time
+    for begin, end in zip(cuts[:-2], cuts[1:-1]):
+        runner.step([StepEntry("r", tokens[begin:end], [])])
+    logits = runner.step([StepEntry("r", tokens[cuts[-2]:], list(range(cuts[-1] - cuts[-2])))])
+    runner.check_fault()
+    got = logits.float().cpu()
+    torch.testing.assert_close(got, plain[cuts[-2]:], **for_dtype(dtype))
+    runner.release("r")
+    runner.cache.check()
+
+
 def test_window_pages_are_given_back(models):
     dirs, plains = models["float32"]
     config, _ = plains["C"]
