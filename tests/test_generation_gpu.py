@@ -133,3 +133,26 @@ def test_running_ahead_does_not_change_a_token(tiny_dirs, tiny_dirs_bf16, dtype)
         assert llm.runner.cache.num_free_slots == 4 and llm.scheduler._inflight is None
     assert results[True] == results[False]
     assert any(reason == "eos" for _, reason in results[True])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_many_requests_under_pressure_equal_plain(tiny_dirs, tiny_plain, name):
+    """Twenty requests of every length through four slots and a pool that holds two of the longest:
+    portions beside decoded tokens, evictions, pages and slots used again, graphs and run-ahead on.
+    Every request's greedy tokens are the plain implementation's."""
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain[name]
+    generator = torch.Generator().manual_seed(99)
+    lengths = torch.randint(1, 90, (20,), generator=generator).tolist()
+    budgets = torch.randint(1, 24, (20,), generator=generator).tolist()
+    prompts = random_prompts(config["vocab_size"], lengths, 17)
+    page = PAGE_SIZES[name]
+    llm = make_llm(tiny_dirs[name], "float32", name, max_gpu_num_blocks=2 * (-(-128 // page)) + 1,
+                   max_chunk_size=29, max_num_batched_tokens=48, use_cuda_graph=True, run_ahead=True)
+    outputs = llm.generate(prompts, [SamplingParams.greedy(max_gen_len=n) for n in budgets])
+    for prompt, budget, output in zip(prompts, budgets, outputs):
+        assert output.token_ids == greedy_generate(config, weights, prompt, budget), (len(prompt), budget)
+    llm.runner.cache.check()
+    assert llm.runner.cache.num_free_slots == 4
+    assert llm.scheduler.num_preemptions >= 1
