@@ -12,9 +12,10 @@
 //
 // S and O live in tensor memory (2 x (128 + 128) columns).  A softmax thread owns one row —
 // one lane of S and O — so the row maximum and sum need no exchange between threads: it reads
-// its 128 scores, scales and masks them (only blocks that touch the causal diagonal or the
-// window's edge need the mask), exponentiates in base 2 and writes P as bfloat16 over the
-// columns S occupied, where the next product reads it.  O is rescaled lazily: the reference
+// its 128 scores into registers once (the softmax warpgroups take the registers the first
+// warpgroup gives up), masks them (only blocks that touch the causal diagonal or the window's
+// edge need it), exponentiates in base 2 and writes P as bfloat16 over the columns S occupied,
+// where the next product reads it.  O is rescaled lazily: the reference
 // point of the exponentials moves only when the row maximum has grown by more than 2^8, so most
 // blocks leave the accumulator untouched; the final division by the row sum makes the result
 // the same.  Scores, maxima, sums and the accumulator are float32; P is rounded to bfloat16
@@ -35,8 +36,16 @@ constexpr int kPfTileRows = 128;                // rows of one query tile
 constexpr int kPfTiles = 2;                     // query tiles per CTA
 constexpr int kPfRows = kPfTiles * kPfTileRows; // packed rows per work item
 constexpr int kPfStages = 2;                    // key tiles and value tiles in flight, each
-constexpr int kPfFirstSoftmaxWarp = 3;          // warp 0: TMA of keys, warp 1: TMA of values, warp 2: MMA
+constexpr int kPfFirstSoftmaxWarp = 4;          // warp 0: TMA of keys, warp 1: TMA of values, warp 2: MMA, warp 3: idle
+constexpr int kPfFewRegisters = 80;             // per thread of warps 0..3 once the kernel is set up
+constexpr int kPfManyRegisters = 208;           // per softmax thread: a row of 128 scores stays in registers
 constexpr int kPfThreads = kPfFirstSoftmaxWarp * 32 + kPfTiles * 128;
+// The kernel starts with the registers its launch bounds allow every thread; what the softmax
+// warpgroups take must have been given up by the first, or they would wait for ever.
+constexpr int kPfLaunchRegisters = 65536 / kPfThreads / 8 * 8;
+static_assert(kPfFirstSoftmaxWarp == 4 && kPfFewRegisters % 8 == 0 && kPfManyRegisters % 8 == 0 &&
+              128 * kPfFewRegisters + kPfTiles * 128 * kPfManyRegisters <= kPfThreads * kPfLaunchRegisters,
+              "register budgets of the warpgroups");
 constexpr int kPfHalfBytes = 128 * 128;         // 128 rows of one 64-wide half
 constexpr int kPfTileBytes = 2 * kPfHalfBytes;  // Q tile, K tile or V tile
 constexpr int kPfSmemBytes = (kPfTiles + 2 * kPfStages) * kPfTileBytes + 1024;
@@ -148,129 +157,135 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
   auto tmem_score = [&](int tile) { return tmem_base + tile * 256; };        // 128 columns; P over its first 64
   auto tmem_out = [&](int tile) { return tmem_base + tile * 256 + 128; };    // 128 columns
 
-  if (warp < 2) {
-    // -------------------------------------------------------------------- TMA producers
-    const int is_value = warp;
-    uint64_t* fulls = is_value ? full_v : full_k;
-    uint64_t* empties = is_value ? empty_v : empty_k;
-    const int box_rows = min(args.page_size, kPfKeys);
-    const int boxes = kPfKeys / box_rows;
-    bool waited = false, ok = true;
-    int issued = 0;
-    for (int b = 0; b < n_blocks && ok; ++b) {
-      const int stage = b % kPfStages;
-      const int kb = k_begin + b * kPfKeys;
-      if (b >= kPfStages) {
-        int got = 1;
-        if (lane == 0)
-          got = mbar_wait(smem_addr(&empties[stage]), ((b / kPfStages) - 1) & 1, aborted, args.fault, is_value ? 1 << 9 : 1 << 8) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, got, 0) != 0;
-        if (!ok) break;
-      }
-      // keys from `start` on are written by this step's earlier kernels
-      if (!waited && kb + kPfKeys > start) {
-        pdl_wait();
-        waited = true;
-      }
-      if (lane == 0) mbar_expect_tx(smem_addr(&fulls[stage]), kPfTileBytes);
-      __syncwarp();
-      for (int i = lane; i < boxes * 2; i += 32) {
-        const int x = i >> 1, half = i & 1;
-        const int j = kb + x * box_rows;                   // first key of the box
-        int page = 0, in_page = 0;                         // past the range: any readable page, masked later
-        if (j < hi) {
-          const int page_index = j / args.page_size;
-          in_page = j - page_index * args.page_size;
-          if (staged) {
-            page = staged_pages[page_index - first_page];
-          } else {
-            page = table[page_index];
-            if (page < 0 || page >= args.num_pages) {
-              atomicOr(args.fault, kFaultPageId);
-              page = 0;
-            }
-          }
-        }
-        const int row = ((page * 2 + is_value) * args.hkv + kv_head) * args.page_size + in_page;
-        const uint32_t dst = (is_value ? v_tile(stage) : k_tile(stage)) + half * kPfHalfBytes + x * box_rows * 128;
-        tma_load_2d(dst, &map_cache, smem_addr(&fulls[stage]), half * 64, row);
-      }
-      ++issued;
-    }
-    if (!waited) pdl_wait();
-    if (lane == 0 && n_blocks > 0 && (!ok || *aborted)) {
-      for (int s = 0; s < kPfStages; ++s) {
-        const int fills = (issued - s + kPfStages - 1) / kPfStages;
-        if (fills > 0) mbar_wait(smem_addr(&fulls[s]), (fills - 1) & 1, aborted, args.fault);
-      }
-    }
-  } else if (warp == 2) {
-    // -------------------------------------------------------------------- tensor-core issuer
-    // Per block: the scores of both tiles as soon as the keys are there; then, tile by tile, the
-    // values product once the tile's P is written, followed at once by the tile's next scores,
-    // so that its softmax threads have work while the other tile's values are multiplied.
-    // Products run in the order they are issued: the scores of block j + 1 overwrite the
-    // columns that held P of block j only after the values product that read them.
-    if (lane == 0) {
-      bool ok = n_blocks > 0;
-      if (ok) ok = mbar_wait(smem_addr(&q_ready), 0, aborted, args.fault, 1 << 10);
-      auto issue_scores = [&](int tile, int b) {
-        const int stage = b % kPfStages;
-        const uint64_t q_desc = operand_desc(q_tile(tile)), keys_desc = operand_desc(k_tile(stage));
-#pragma unroll
-        for (int k = 0; k < kPfD / 16; ++k) {
-          const uint32_t half = (k >> 2), within = (k & 3) * 2;
-          umma_bf16(tmem_score(tile), q_desc + half * (kPfHalfBytes >> 4) + within,
-                    keys_desc + half * (kPfHalfBytes >> 4) + within, kPfIdescScore, k > 0 ? 1u : 0u);
-        }
-        umma_commit(smem_addr(&score_ready[tile]));
-      };
-      // the last tile that uses block b releases its key tile
-      auto release_keys = [&](int b) { umma_commit(smem_addr(&empty_k[b % kPfStages])); };
-      if (ok) {
-        ok = mbar_wait(smem_addr(&full_k[0]), 0, aborted, args.fault, 1 << 11);
-        if (ok) {
-          tc_fence_after();
-          for (int tile = 0; tile < kPfTiles; ++tile)
-            if (tile_blocks[tile] > 0) issue_scores(tile, 0);
-          release_keys(0);
-        }
-      }
+  // the first warpgroup gives registers up (one instruction for all four warps), the softmax
+  // warpgroups take them
+  if (warp < kPfFirstSoftmaxWarp) {
+    register_budget_down<kPfFewRegisters>();
+    if (warp < 2) {
+      // -------------------------------------------------------------------- TMA producers
+      const int is_value = warp;
+      uint64_t* fulls = is_value ? full_v : full_k;
+      uint64_t* empties = is_value ? empty_v : empty_k;
+      const int box_rows = min(args.page_size, kPfKeys);
+      const int boxes = kPfKeys / box_rows;
+      bool waited = false, ok = true;
+      int issued = 0;
       for (int b = 0; b < n_blocks && ok; ++b) {
         const int stage = b % kPfStages;
-        bool keys_next = false;
-        for (int tile = 0; tile < kPfTiles && ok; ++tile) {
-          if (b >= tile_blocks[tile]) continue;
-          ok = mbar_wait(smem_addr(&p_ready[tile]), b & 1, aborted, args.fault, 1 << (12 + tile));
+        const int kb = k_begin + b * kPfKeys;
+        if (b >= kPfStages) {
+          int got = 1;
+          if (lane == 0)
+            got = mbar_wait(smem_addr(&empties[stage]), ((b / kPfStages) - 1) & 1, aborted, args.fault, is_value ? 1 << 9 : 1 << 8) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, got, 0) != 0;
           if (!ok) break;
-          ok = mbar_wait(smem_addr(&full_v[stage]), (b / kPfStages) & 1, aborted, args.fault, 1 << 14);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t values_desc = operand_desc_mn(v_tile(stage), kPfHalfBytes);
-#pragma unroll
-          for (int k = 0; k < kPfKeys / 16; ++k)
-            umma_bf16_ts(tmem_out(tile), tmem_score(tile) + k * 8, values_desc + k * (2048 >> 4), kPfIdescValue,
-                         (b > 0 || k > 0) ? 1u : 0u);
-          umma_commit(smem_addr(&value_done[tile]));
-          if (b + 1 < tile_blocks[tile]) {
-            if (!keys_next) {
-              ok = mbar_wait(smem_addr(&full_k[(b + 1) % kPfStages]), ((b + 1) / kPfStages) & 1, aborted, args.fault, 1 << 15);
-              if (!ok) break;
-              tc_fence_after();
-              keys_next = true;
+        }
+        // keys from `start` on are written by this step's earlier kernels
+        if (!waited && kb + kPfKeys > start) {
+          pdl_wait();
+          waited = true;
+        }
+        if (lane == 0) mbar_expect_tx(smem_addr(&fulls[stage]), kPfTileBytes);
+        __syncwarp();
+        for (int i = lane; i < boxes * 2; i += 32) {
+          const int x = i >> 1, half = i & 1;
+          const int j = kb + x * box_rows;                   // first key of the box
+          int page = 0, in_page = 0;                         // past the range: any readable page, masked later
+          if (j < hi) {
+            const int page_index = j / args.page_size;
+            in_page = j - page_index * args.page_size;
+            if (staged) {
+              page = staged_pages[page_index - first_page];
+            } else {
+              page = table[page_index];
+              if (page < 0 || page >= args.num_pages) {
+                atomicOr(args.fault, kFaultPageId);
+                page = 0;
+              }
             }
-            issue_scores(tile, b + 1);
+          }
+          const int row = ((page * 2 + is_value) * args.hkv + kv_head) * args.page_size + in_page;
+          const uint32_t dst = (is_value ? v_tile(stage) : k_tile(stage)) + half * kPfHalfBytes + x * box_rows * 128;
+          tma_load_2d(dst, &map_cache, smem_addr(&fulls[stage]), half * 64, row);
+        }
+        ++issued;
+      }
+      if (!waited) pdl_wait();
+      if (lane == 0 && n_blocks > 0 && (!ok || *aborted)) {
+        for (int s = 0; s < kPfStages; ++s) {
+          const int fills = (issued - s + kPfStages - 1) / kPfStages;
+          if (fills > 0) mbar_wait(smem_addr(&fulls[s]), (fills - 1) & 1, aborted, args.fault);
+        }
+      }
+    } else if (warp == 2) {
+      // -------------------------------------------------------------------- tensor-core issuer
+      // Per block: the scores of both tiles as soon as the keys are there; then, tile by tile, the
+      // values product once the tile's P is written, followed at once by the tile's next scores,
+      // so that its softmax threads have work while the other tile's values are multiplied.
+      // Products run in the order they are issued: the scores of block j + 1 overwrite the
+      // columns that held P of block j only after the values product that read them.
+      if (lane == 0) {
+        bool ok = n_blocks > 0;
+        if (ok) ok = mbar_wait(smem_addr(&q_ready), 0, aborted, args.fault, 1 << 10);
+        auto issue_scores = [&](int tile, int b) {
+          const int stage = b % kPfStages;
+          const uint64_t q_desc = operand_desc(q_tile(tile)), keys_desc = operand_desc(k_tile(stage));
+  #pragma unroll
+          for (int k = 0; k < kPfD / 16; ++k) {
+            const uint32_t half = (k >> 2), within = (k & 3) * 2;
+            umma_bf16(tmem_score(tile), q_desc + half * (kPfHalfBytes >> 4) + within,
+                      keys_desc + half * (kPfHalfBytes >> 4) + within, kPfIdescScore, k > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_addr(&score_ready[tile]));
+        };
+        // the last tile that uses block b releases its key tile
+        auto release_keys = [&](int b) { umma_commit(smem_addr(&empty_k[b % kPfStages])); };
+        if (ok) {
+          ok = mbar_wait(smem_addr(&full_k[0]), 0, aborted, args.fault, 1 << 11);
+          if (ok) {
+            tc_fence_after();
+            for (int tile = 0; tile < kPfTiles; ++tile)
+              if (tile_blocks[tile] > 0) issue_scores(tile, 0);
+            release_keys(0);
           }
         }
-        if (!ok) break;
-        umma_commit(smem_addr(&empty_v[stage]));
-        if (keys_next) release_keys(b + 1);
+        for (int b = 0; b < n_blocks && ok; ++b) {
+          const int stage = b % kPfStages;
+          bool keys_next = false;
+          for (int tile = 0; tile < kPfTiles && ok; ++tile) {
+            if (b >= tile_blocks[tile]) continue;
+            ok = mbar_wait(smem_addr(&p_ready[tile]), b & 1, aborted, args.fault, 1 << (12 + tile));
+            if (!ok) break;
+            ok = mbar_wait(smem_addr(&full_v[stage]), (b / kPfStages) & 1, aborted, args.fault, 1 << 14);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t values_desc = operand_desc_mn(v_tile(stage), kPfHalfBytes);
+  #pragma unroll
+            for (int k = 0; k < kPfKeys / 16; ++k)
+              umma_bf16_ts(tmem_out(tile), tmem_score(tile) + k * 8, values_desc + k * (2048 >> 4), kPfIdescValue,
+                           (b > 0 || k > 0) ? 1u : 0u);
+            umma_commit(smem_addr(&value_done[tile]));
+            if (b + 1 < tile_blocks[tile]) {
+              if (!keys_next) {
+                ok = mbar_wait(smem_addr(&full_k[(b + 1) % kPfStages]), ((b + 1) / kPfStages) & 1, aborted, args.fault, 1 << 15);
+                if (!ok) break;
+                tc_fence_after();
+                keys_next = true;
+              }
+              issue_scores(tile, b + 1);
+            }
+          }
+          if (!ok) break;
+          umma_commit(smem_addr(&empty_v[stage]));
+          if (keys_next) release_keys(b + 1);
+        }
+        umma_commit(smem_addr(&drained));
+        mbar_wait(smem_addr(&drained), 0, aborted, args.fault, 1 << 16);
       }
-      umma_commit(smem_addr(&drained));
-      mbar_wait(smem_addr(&drained), 0, aborted, args.fault, 1 << 16);
     }
   } else {
     // -------------------------------------------------------------------- softmax and output
+    register_budget_up<kPfManyRegisters>();
     const int tile = (warp - kPfFirstSoftmaxWarp) >> 2;
     const int quarter = warp & 3;                      // tensor-memory lanes this warp may touch
     const int r = quarter * 32 + lane;                 // row of the tile = lane of S and O
@@ -305,24 +320,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
       if (!ok) break;
       tc_fence_after();
       const bool masked = kb + kPfKeys - 1 > pos || kb < lo_pos;
-      // first sweep: the row's largest score of the block
-      float block_max = -INFINITY;
+      // the row's 128 scores come into registers once; keys the row may not see become -inf,
+      // whose exponential is zero
+      uint32_t score[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        tmem_load32(tmem_score(tile) + lane_bits + c * 32, raw);
-        tmem_wait_ld();
-        if (masked) {
+      for (int c = 0; c < 4; ++c) tmem_load32(tmem_score(tile) + lane_bits + c * 32, score[c]);
+      tmem_wait_ld();
+      if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = kb + c * 32 + i;
-            if (key <= pos && key >= lo_pos) block_max = fmaxf(block_max, __uint_as_float(raw[i]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) block_max = fmaxf(block_max, __uint_as_float(raw[i]));
+        for (int i = 0; i < kPfKeys; ++i) {
+          const int key = kb + i;
+          if (!(key <= pos && key >= lo_pos)) score[i >> 5][i & 31] = 0xff800000u;
         }
       }
+      float block_max = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kPfKeys; ++i) block_max = fmaxf(block_max, __uint_as_float(score[i >> 5][i & 31]));
       block_max *= args.scale_log2;                    // the scale is positive
       // the values product of the block before has read P and added to O by now (products run
       // in order and this block's scores came after it); the wait also orders the rescale below
@@ -352,22 +365,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
         }
       }
       const float shift = ref_max == -INFINITY ? 0.0f : ref_max;
-      // second sweep: P = 2^(s * scale - ref_max) as bfloat16, two per column, over S's columns
+      // P = 2^(s * scale - ref_max) as bfloat16, two per column, over S's columns
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        tmem_load32(tmem_score(tile) + lane_bits + c * 32, raw);
-        tmem_wait_ld();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float e0 = fast_exp2(__uint_as_float(raw[2 * i]) * args.scale_log2 - shift);
-          float e1 = fast_exp2(__uint_as_float(raw[2 * i + 1]) * args.scale_log2 - shift);
-          if (masked) {
-            const int key = kb + c * 32 + 2 * i;
-            if (!(key <= pos && key >= lo_pos)) e0 = 0.0f;
-            if (!(key + 1 <= pos && key + 1 >= lo_pos)) e1 = 0.0f;
-          }
+          const float e0 = fast_exp2(__uint_as_float(score[c][2 * i]) * args.scale_log2 - shift);
+          const float e1 = fast_exp2(__uint_as_float(score[c][2 * i + 1]) * args.scale_log2 - shift);
           row_sum += e0 + e1;
           const __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
           packed[i] = *reinterpret_cast<const uint32_t*>(&pair);

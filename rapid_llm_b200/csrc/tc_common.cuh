@@ -190,6 +190,17 @@ __device__ __forceinline__ float load_cluster_f32(uint32_t local_address, uint32
   return value;
 }
 
+// Registers per thread from here on, for the whole warpgroup (4 warps, all of which must execute
+// it): the one that takes waits until others have given.  The counts are multiples of 8.
+template <int kRegisters>
+__device__ __forceinline__ void register_budget_up() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegisters));
+}
+template <int kRegisters>
+__device__ __forceinline__ void register_budget_down() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegisters));
+}
+
 // The address of `local_address` in the shared memory of the cluster's CTA `cta_rank`, and a load
 // from such an address (not volatile: the caller orders them with cluster barriers, and several
 // may be in flight at once).
