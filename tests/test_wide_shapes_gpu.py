@@ -1,0 +1,72 @@
+"""One layer at the widths of the large models (hidden 5120, 40 or 64 query heads over 8, head
+size 128, intermediate sizes that are no power of two), bfloat16, against the plain
+implementation: the tcgen05 products with their k-splits, the tcgen05 attention kernels with
+groups of 5 and 8, and the library product above 64 tokens meet sizes here that the tiny
+configurations never reach."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+from plain_qwen3 import forward_logits, load_model_dir
+from tolerances import at_scale
+
+pytestmark = pytest.mark.gpu
+
+WIDE = {
+    "heads40_inter17408": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=17408),
+    "heads64_inter25600": dict(hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600),
+}
+
+
+def wide_config(sizes: dict) -> dict:
+    return {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 1000, "num_hidden_layers": 1,
+        "head_dim": 128, "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+        "tie_word_embeddings": False, "attention_bias": False, "hidden_act": "silu", "sliding_window": None,
+        "use_sliding_window": False, "torch_dtype": "bfloat16", **sizes,
+    }
+
+
+@pytest.mark.parametrize("name", sorted(WIDE))
+def test_one_wide_layer_whole_in_portions_and_decoding(name, tmp_path):
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(WIDE[name])
+    folder = write_random_model(tmp_path / name, Qwen3Config.from_dict(raw), 11, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    generator = torch.Generator().manual_seed(4)
+    tokens = {"a": torch.randint(0, 1000, (300,), generator=generator).tolist(),
+              "b": torch.randint(0, 1000, (90,), generator=generator).tolist()}
+    plain = {key: forward_logits(config, weights, ids) for key, ids in tokens.items()}
+
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=512, page_size=16, num_pages=40, max_num_seqs=4,
+                          max_num_batched_tokens=512, use_cuda_graph=False)
+    runner = ModelRunner.from_folder(folder, engine)
+    tolerance = at_scale("bfloat16", plain["a"])
+
+    # whole: 300 tokens in one step (library products, the prompt attention kernel)
+    runner.admit("a")
+    places = [0, 1, 63, 64, 127, 128, 255, 256, 299]
+    got = runner.step([StepEntry("a", tokens["a"], places)]).float().cpu()
+    torch.testing.assert_close(got, plain["a"][places], **tolerance)
+    runner.release("a")
+
+    # portions of one beside decode tokens of the other (the streaming products, both attention kernels)
+    runner.admit("a")
+    runner.admit("b")
+    runner.step([StepEntry("a", tokens["a"][:250], []), StepEntry("b", tokens["b"][:86], [])])
+    at = {"a": 250, "b": 86}
+    plan = [{"a": 47, "b": 1}, {"a": 1, "b": 1}, {"a": 1, "b": 1}, {"a": 1, "b": 1}]
+    for sizes in plan:
+        entries, wanted = [], []
+        for key, size in sizes.items():
+            entries.append(StepEntry(key, tokens[key][at[key] : at[key] + size], [size - 1]))
+            at[key] += size
+            wanted.append(plain[key][at[key] - 1])
+        got = runner.step(entries).float().cpu()
+        torch.testing.assert_close(got, torch.stack(wanted), **tolerance)
+    runner.check_fault()
+    assert at == {"a": 300, "b": 90}
