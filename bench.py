@@ -34,6 +34,14 @@ QWEN3_8B = {
     "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
     "tie_word_embeddings": False, "torch_dtype": "bfloat16",
 }
+# the other shapes of the baseline description: the same architecture, other sizes
+SHAPES = {
+    "8b": ("Qwen3-8B", {}),
+    "14b": ("Qwen3-14B", {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40,
+                          "num_key_value_heads": 8, "intermediate_size": 17408}),
+    "32b": ("Qwen3-32B", {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64,
+                          "num_key_value_heads": 8, "intermediate_size": 25600}),
+}
 CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
 PUBLISHED_TOK_S = 216.6   # Qwen3-8B bf16, batch 8, 1x A10: docs/benchmark_models.md:191 of the reference
 
@@ -221,6 +229,62 @@ def write_timeline(llm, batch: int, path: str, seed: int) -> dict:
     return {"timeline": path, "events": len(events), "batch": batch}
 
 
+def serve_run(args, config, raw: dict, shape_name: str, layers: int, layers_full: int) -> dict:
+    """Continuous batching as a user meets it: ``--requests`` prompts of uniform-random length
+    (128 to 4,096 tokens) with 64 to 512 tokens to generate each, all handed to ``generate`` at
+    once; prompts are cut into portions of 2,048 tokens a step beside the decoding requests.
+    Timed by the wall clock around the call, host token ids in and out."""
+    import torch
+
+    from rapid_llm_b200 import LLM, EngineConfig, SamplingParams
+    from rapid_llm_b200.engine.runner import ModelRunner
+    from rapid_llm_b200.ops import kernels
+
+    generator = torch.Generator().manual_seed(3)
+    count = args.requests
+    prompt_lengths = torch.randint(128, 4097, (count,), generator=generator).tolist()
+    output_lengths = torch.randint(64, 513, (count,), generator=generator).tolist()
+    vocab = raw["vocab_size"]
+    prompts = [torch.randint(0, vocab, (n,), generator=generator).tolist() for n in prompt_lengths]
+    live = min(count, 64)
+    pages = sum(sorted((-(-(p + o) // PAGE) + 1 for p, o in zip(prompt_lengths, output_lengths)), reverse=True)[:live])
+    engine = EngineConfig(
+        dtype=torch.bfloat16, max_seq_len=CONTEXT, page_size=PAGE, num_pages=pages + PREFILL_TOKENS // PAGE,
+        max_num_seqs=live, max_num_batched_tokens=PREFILL_TOKENS, max_chunk_size=PREFILL_TOKENS, use_cuda_graph=True,
+    )
+    llm = LLM.from_runner(ModelRunner.from_random(config, seed=0, config=engine))
+    params = [SamplingParams.greedy(max_gen_len=n) for n in output_lengths]
+    llm.scheduler.stop_token_ids = set()
+    warm = llm.generate(prompts[:2], [SamplingParams.greedy(max_gen_len=8)] * 2)     # loads, graphs, workspaces
+    assert all(len(o.token_ids) == 8 for o in warm)
+    torch.cuda.synchronize()
+    before = kernels.LAUNCHES.count
+    with ClockSampler() as clocks:
+        begin = time.perf_counter()
+        outputs = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+    generated = sum(len(o.token_ids) for o in outputs)
+    assert generated == sum(output_lengths), (generated, sum(output_lengths))
+    return {
+        "metric": f"generated tok/s, continuous batching of {count} requests ({shape_name} shape)",
+        "value": round(generated / seconds, 1), "unit": "tok/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours", "seconds": round(seconds, 3),
+        "prompt_tokens": sum(prompt_lengths), "generated_tokens": generated,
+        "all_tokens_per_second": round((sum(prompt_lengths) + generated) / seconds, 1),
+        "steps": llm.runner.steps_run, "preemptions": llm.scheduler.num_preemptions,
+        "gpu_launches": kernels.LAUNCHES.count - before,
+        "config": {
+            "model": f"{shape_name} shape, random weights", "layers": layers, "layers_full": layers_full,
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": vocab,
+            "requests": count, "prompt_lengths": "uniform 128-4096", "output_lengths": "uniform 64-512",
+            "tokens_per_step": PREFILL_TOKENS, "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "single GPU",
+        },
+        "clocks": clocks.summary(),
+    }
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -230,12 +294,15 @@ def run_ours(args) -> dict:
     if args.prompt_len + 2 * (args.steps + args.warmup) + 128 > CONTEXT:
         raise SystemExit(f"--prompt-len {args.prompt_len} leaves no room to decode within the context of {CONTEXT}")
     peaks = measured_peaks()
-    raw = dict(QWEN3_8B)
+    shape_name, sizes = SHAPES[args.shape]
+    raw = dict(QWEN3_8B, **sizes)
     layers_full = raw["num_hidden_layers"]
     layers = args.layers or layers_full
     raw["num_hidden_layers"] = layers
     config = Qwen3Config.from_dict(raw)
-    batches = sorted({1, args.batch, 64})
+    if args.workload == "serve":
+        return serve_run(args, config, raw, shape_name, layers, layers_full)
+    batches = sorted({args.batch, *args.points}) if "points" in args.parts else [args.batch]
     longest = PROMPT_LEN + 2 * (args.steps + args.warmup) + max(batches) * PROMPT_LEN // PREFILL_TOKENS + 64
     pages = max(batches) * (-(-longest // PAGE)) + PREFILL_TOKENS // PAGE + 8
     engine = EngineConfig(
@@ -264,7 +331,7 @@ def run_ours(args) -> dict:
     flops = prefill_flops(raw, layers, PREFILL_TOKENS)
     meta_bytes = 4 * (args.batch * (3 + 1) + 3 * args.batch + 1 + args.batch)
     return {
-        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B shape, {PROMPT_LEN}-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name} shape, {PROMPT_LEN}-token prompts)",
         "value": round(value, 1),
         "unit": "tok/s",
         "n_gpus": 1,
@@ -273,12 +340,12 @@ def run_ours(args) -> dict:
         "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True,
         "scaling": "weak",
-        "vs_baseline": round(value / PUBLISHED_TOK_S, 2),
+        "vs_baseline": round(value / PUBLISHED_TOK_S, 2) if (args.shape, args.batch) == ("8b", 8) else None,
         "dtype": "bf16",
         "data": "synthetic",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape, random weights", "layers": layers, "layers_full": layers_full,
+            "model": f"{shape_name} shape, random weights", "layers": layers, "layers_full": layers_full,
             "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
             "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
@@ -331,9 +398,6 @@ def run_reference(args) -> dict:
         tail = " | ".join((done.stderr or done.stdout).strip().splitlines()[-3:])[:400]
         return {"impl": "reference", "unavailable": f"the reference engine failed here (exit {done.returncode}): {tail}"}
     got = json.loads(lines[-1])
-    globals()["PROMPT_LEN"] = args.prompt_len
-    if PROMPT_LEN + 2 * (args.steps + args.warmup) + 128 > CONTEXT:
-        raise SystemExit(f"--prompt-len {args.prompt_len} leaves no room to decode within the context of {CONTEXT}")
     peaks = measured_peaks()
     raw = dict(QWEN3_8B)
     layers = got["layers"]
@@ -379,6 +443,14 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each request's prompt: the "
                         "context that decoding starts from (the default is the configuration's)")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: the 8B shape is the "
+                        "benchmark's; 14b and 32b are the other shapes of the same architecture")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the engine is set up for")
+    parser.add_argument("--points", default="1,64", help="other batch sizes decoded beside --batch")
+    parser.add_argument("--workload", choices=["decode", "serve"], default="decode", help="decode: the benchmark "
+                        "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
+                        "prompts of mixed lengths through generate()")
+    parser.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--parts", default="prefill,points", help="extra measurements beside the main decode run "
@@ -393,7 +465,9 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     args.parts = {part for part in args.parts.split(",") if part}
+    args.points = [int(x) for x in args.points.split(",") if x]
     globals()["PROMPT_LEN"] = args.prompt_len
+    globals()["CONTEXT"] = args.context
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
