@@ -333,17 +333,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
           if (!(key <= pos && key >= lo_pos)) score[i >> 5][i & 31] = 0xff800000u;
         }
       }
-      float block_max = -INFINITY;
+      // eight running maxima: one chain of 128 dependent comparisons would cost their latencies in a row
+      float lane_max[8];
 #pragma unroll
-      for (int i = 0; i < kPfKeys; ++i) block_max = fmaxf(block_max, __uint_as_float(score[i >> 5][i & 31]));
+      for (int i = 0; i < 8; ++i) lane_max[i] = __uint_as_float(score[0][i]);
+#pragma unroll
+      for (int i = 8; i < kPfKeys; ++i) lane_max[i & 7] = fmaxf(lane_max[i & 7], __uint_as_float(score[i >> 5][i & 31]));
+      float block_max = fmaxf(fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])),
+                              fmaxf(fmaxf(lane_max[4], lane_max[5]), fmaxf(lane_max[6], lane_max[7])));
       block_max *= args.scale_log2;                    // the scale is positive
-      // the values product of the block before has read P and added to O by now (products run
-      // in order and this block's scores came after it); the wait also orders the rescale below
-      if (b > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_addr(&value_done[tile]), (b - 1) & 1, aborted, args.fault, 1 << (19 + tile)));
-        if (!ok) break;
-        tc_fence_after();
-      }
+      // The values product of the block before has added to O by now: products run in order, this
+      // block's scores were issued after it, and the barrier that announced them counts everything
+      // the issuing thread had issued before.  So O may be rescaled here without a further wait.
       // tensor-memory accesses are warp-wide: if any row of the warp moves its reference point,
       // the whole warp rewrites its rows of O, the others with a factor of one
       const bool moves = block_max > ref_max + kPfRescaleStep || (ref_max == -INFINITY && block_max > -INFINITY);
