@@ -125,6 +125,17 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
 // ---------------------------------------------------------------- SiLU * up
 // gate_up is [rows, 2 * inter] with the gate in columns [0, inter) and up in
 // [inter, 2 * inter); out[r, c] = silu(gate) * up with silu(z) = z * sigmoid(z), in float32.
+// Sixteen-bit outputs keep 8 bits of mantissa: the fast exponential and division (a few units in
+// the last place of float32) change no result; the 32-bit engine takes the exact ones.
+template <typename T>
+__device__ __forceinline__ float silu_times(float gate, float up) {
+  if constexpr (sizeof(T) == 2) {
+    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+  } else {
+    return gate / (1.0f + expf(-gate)) * up;
+  }
+}
+
 template <typename T, bool kVector>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows,
                                 int inter) {
@@ -143,12 +154,12 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
       load8(gate, g);
       load8(gate + inter, u);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) g[i] = g[i] / (1.0f + expf(-g[i])) * u[i];
+      for (int i = 0; i < 8; ++i) g[i] = silu_times<T>(g[i], u[i]);
       store8(out + r * inter + c, g);
     } else {
       const float g = to_float(gate[0]);
       const float u = to_float(gate[inter]);
-      out[r * inter + c] = from_float<T>(g / (1.0f + expf(-g)) * u);
+      out[r * inter + c] = from_float<T>(silu_times<T>(g, u));
     }
   }
 }

@@ -83,22 +83,12 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
       kw[i] = a.k_weight ? a.k_weight[at + i] : 1.0f;
     }
     pdl_wait();
-    for (int head = head_begin; head < head_end; ++head) {
-      const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // q, k, v
-      const T* src = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
-      T* dst;
-      if (kind == 0) {
-        dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
-      } else {
-        if (bad_page) {
-          if (lane == 0) atomicOr(a.fault, kFaultPageId);
-          continue;
-        }
-        const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
-        dst = static_cast<T*>(a.cache) +
-              ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
-      }
-      float v[kVec];
+    // a head's source and where it goes
+    auto source_of = [&](int head) {
+      return static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width + static_cast<size_t>(head) * d;
+    };
+    auto load_head = [&](int head, float (&v)[kVec]) {
+      const T* src = source_of(head);
       if constexpr (kVec == 8) {
         load8(src + at, v);
       } else if constexpr (sizeof(T) == 2 && kVec == 4) {
@@ -109,6 +99,21 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
       } else {
 #pragma unroll
         for (int i = 0; i < kVec; ++i) v[i] = to_float(src[at + i]);
+      }
+    };
+    auto finish_head = [&](int head, float (&v)[kVec]) {
+      const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // q, k, v
+      T* dst;
+      if (kind == 0) {
+        dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * d;
+      } else {
+        if (bad_page) {
+          if (lane == 0) atomicOr(a.fault, kFaultPageId);
+          return;
+        }
+        const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+        dst = static_cast<T*>(a.cache) +
+              ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * d;
       }
       float sum_sq = 0.0f;
 #pragma unroll
@@ -151,6 +156,17 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
 #pragma unroll
         for (int i = 0; i < kVec; ++i) dst[at + i] = from_float<T>(v[i]);
       }
+    };
+    // the loads of four heads fly together; their arithmetic follows
+    constexpr int kHeadsInFlight = 4;
+    for (int head0 = head_begin; head0 < head_end; head0 += kHeadsInFlight) {
+      float v[kHeadsInFlight][kVec];
+#pragma unroll
+      for (int j = 0; j < kHeadsInFlight; ++j)
+        if (head0 + j < head_end) load_head(head0 + j, v[j]);
+#pragma unroll
+      for (int j = 0; j < kHeadsInFlight; ++j)
+        if (head0 + j < head_end) finish_head(head0 + j, v[j]);
     }
   } else {
     pdl_wait();
