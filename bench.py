@@ -194,15 +194,31 @@ def prefill_run(llm, warmup: int, seed: int) -> float:
     return min(times)
 
 
-def write_timeline(llm, batch: int, path: str, seed: int) -> dict:
-    """Start, duration and overlap of every kernel of three decode steps (CUPTI through torch.profiler)."""
+def write_timeline(llm, batch: int, path: str, seed: int, step: str = "decode") -> dict:
+    """Start, duration and overlap of every kernel of three decode steps, or of one step over a
+    2,048-token prompt (CUPTI through torch.profiler)."""
     import torch
     from torch.profiler import ProfilerActivity, profile
 
     from rapid_llm_b200 import SamplingParams
+    from rapid_llm_b200.engine.runner import StepEntry
 
     scheduler, runner = llm.scheduler, llm.runner
     vocab = runner.model.spec.vocab_size
+    if step == "prefill":
+        for trial in range(3):
+            tokens = random_prompts(1, PREFILL_TOKENS, vocab, seed + trial)[0]
+            runner.admit("prefill")
+            torch.cuda.synchronize()
+            if trial < 2:
+                runner.step([StepEntry("prefill", tokens, [PREFILL_TOKENS - 1])])
+            else:
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    runner.step([StepEntry("prefill", tokens, [PREFILL_TOKENS - 1])])
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            runner.release("prefill")
+        return dump_timeline(prof, path, {"step": "prefill", "tokens": PREFILL_TOKENS})
     params = SamplingParams.greedy(max_gen_len=64 + -(-batch * PROMPT_LEN // PREFILL_TOKENS))
     requests = [scheduler.add_request(p, params) for p in random_prompts(batch, PROMPT_LEN, vocab, seed)]
     while any(r.num_computed_tokens < len(r.prompt_token_ids) for r in requests):
@@ -214,19 +230,25 @@ def write_timeline(llm, batch: int, path: str, seed: int) -> dict:
         for _ in range(3):
             scheduler.step()
         torch.cuda.synchronize()
+    for request in requests:
+        scheduler.abort(request)
+    return dump_timeline(prof, path, {"step": "decode", "batch": batch})
+
+
+def dump_timeline(prof, path: str, what: dict) -> dict:
+    import torch
+
     events = sorted(
         (e.time_range.start, e.time_range.end - e.time_range.start, e.name)
         for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
     )
-    for request in requests:
-        scheduler.abort(request)
     origin, latest = events[0][0], events[0][0]
     lines = ["start_us  duration_us  gap_to_previous_end_us  kernel"]
     for begin, duration, name in events:
         lines.append(f"{begin - origin:9.1f} {duration:8.1f} {begin - latest:8.1f}  {name[:80]}")
         latest = max(latest, begin + duration)
     Path(path).write_text("\n".join(lines) + "\n")
-    return {"timeline": path, "events": len(events), "batch": batch}
+    return {"timeline": path, "events": len(events), **what}
 
 
 def serve_run(args, config, raw: dict, shape_name: str, layers: int, layers_full: int) -> dict:
@@ -313,7 +335,7 @@ def run_ours(args) -> dict:
     llm = LLM.from_runner(runner)
 
     if args.timeline:
-        return write_timeline(llm, args.batch, args.timeline, seed=args.batch)
+        return write_timeline(llm, args.batch, args.timeline, seed=args.batch, step=args.timeline_step)
     prefill_ms = prefill_run(llm, args.warmup, seed=11) if "prefill" in args.parts else float("nan")
     results = {}
     for batch in batches:
@@ -457,6 +479,8 @@ def main() -> int:
                         "(comma-separated: prefill, points); an empty string leaves only the main run, for profiling")
     parser.add_argument("--timeline", default=None, help="instead of measuring, write the kernel timeline of three "
                         "decode steps at --batch (start, duration, gap; CUPTI through torch.profiler) to this file")
+    parser.add_argument("--timeline-step", choices=["decode", "prefill"], default="decode",
+                        help="what --timeline records: three decode steps or one step over a 2,048-token prompt")
     parser.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = parser.parse_args()
     if args.gpus != 1:
