@@ -52,7 +52,7 @@ struct GemmArgs {
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
-  return gate / (1.0f + __expf(-gate)) * up;
+  return __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16
 }
 
 template <bool kSwiglu, int BN>
