@@ -97,6 +97,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   auto stage_a = [&](int s, int half) { return smem_base + s * Shape::kStageBytes + half * kTileN * kTileK * 2; };
   auto stage_b = [&](int s) { return smem_base + s * Shape::kStageBytes + kHalves * kTileN * kTileK * 2; };
 
+  if (threadIdx.x == 64) {                    // an epilogue warp: idle until the first tile is done
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_addr(&full_bar[s]), 1);
@@ -134,27 +138,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      auto load_a = [&](long long it, int stage) {
-        const int tile = tile_of(static_cast<int>(it / kb_count));
-        const int kb = kb_begin + static_cast<int>(it % kb_count);
-        const int n_tile = tile / args.t_tiles;
+      // (tile index, k-block) of an iteration advance by counting: a division per copy would cost
+      // this one thread more than the copy itself
+      struct Cursor { int index, kb; };
+      auto advance = [&](Cursor& c) { if (++c.kb == kb_count) { c.kb = 0; ++c.index; } };
+      auto load_a = [&](const Cursor& c, int stage) {
+        const int n_tile = tile_of(c.index) / args.t_tiles;
+        const int k = (kb_begin + c.kb) * kTileK;
         const uint32_t bar = smem_addr(&full_bar[stage]);
         mbar_expect_tx(bar, Shape::kStageBytes);
-        tma_load_2d(stage_a(stage, 0), &map_w, bar, kb * kTileK, n_tile * kTileN);
-        if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, kb * kTileK, args.up_offset + n_tile * kTileN);
+        tma_load_2d(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN);
+        if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN);
       };
-      auto load_b = [&](long long it, int stage) {
-        const int tile = tile_of(static_cast<int>(it / kb_count));
-        const int kb = kb_begin + static_cast<int>(it % kb_count);
-        const int t_tile = tile % args.t_tiles;
-        tma_load_2d(stage_b(stage), &map_x, smem_addr(&full_bar[stage]), kb * kTileK, t_tile * BN);
+      auto load_b = [&](const Cursor& c, int stage) {
+        const int t_tile = tile_of(c.index) % args.t_tiles;
+        tma_load_2d(stage_b(stage), &map_x, smem_addr(&full_bar[stage]), (kb_begin + c.kb) * kTileK, t_tile * BN);
       };
       // weights first: nothing in the stream writes them, so they may fly before the
       // previous kernel has finished; the activations only after
       const int prefetch = static_cast<int>(min(static_cast<long long>(kStages), total_iters));
-      for (int it = 0; it < prefetch; ++it) load_a(it, it);
+      Cursor cursor = {0, 0};
+      for (int it = 0; it < prefetch; ++it) { load_a(cursor, it); advance(cursor); }
       if (args.pdl) pdl_wait();
-      for (int it = 0; it < prefetch; ++it) load_b(it, it);
+      Cursor second = {0, 0};
+      for (int it = 0; it < prefetch; ++it) { load_b(second, it); advance(second); }
       int stage = prefetch % kStages;
       uint32_t phase = prefetch == kStages ? 1u : 0u;
       bool ok = true;
@@ -162,8 +169,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       for (long long it = prefetch; it < total_iters; ++it) {
         ok = mbar_wait(smem_addr(&empty_bar[stage]), phase ^ 1u, aborted, args.fault);
         if (!ok) break;
-        load_a(it, stage);
-        load_b(it, stage);
+        load_a(cursor, stage);
+        load_b(cursor, stage);
+        advance(cursor);
         ++filled;
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }

@@ -59,6 +59,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   atomicOr(fault, kFaultWaitLimit | where);
   return false;
 }
+// Brings a tensor map (a kernel parameter) near the TMA unit ahead of the first copy that uses it.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
                                             int y) {
   asm volatile(
