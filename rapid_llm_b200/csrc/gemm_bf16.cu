@@ -92,10 +92,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ int aborted_flag;
   volatile int* aborted = &aborted_flag;
 
+  if (args.pdl && threadIdx.x == 0) pdl_trigger();   // the successor may set itself up beside this kernel
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_addr(gemm_smem_raw) + 1023u) & ~1023u;
   auto stage_a = [&](int s, int half) { return smem_base + s * Shape::kStageBytes + half * kTileN * kTileK * 2; };
   auto stage_b = [&](int s) { return smem_base + s * Shape::kStageBytes + kHalves * kTileN * kTileK * 2; };
+
+  // this CTA's slice of the k-blocks and its tiles
+  const int rank = blockIdx.x;
+  const int k_base = args.k_blocks / args.k_split, k_rem = args.k_blocks - k_base * args.k_split;
+  const int kb_begin = rank * k_base + min(rank, k_rem);
+  const int kb_count = k_base + (rank < k_rem ? 1 : 0);
+  const int tiles = args.n_tiles * args.t_tiles;
+  const int my_tiles = (tiles - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) /
+                       static_cast<int>(gridDim.y);
+  const long long total_iters = static_cast<long long>(my_tiles) * kb_count;
+  auto tile_of = [&](int index) { return static_cast<int>(blockIdx.y) + index * static_cast<int>(gridDim.y); };
+
+  // (tile index, k-block) of an iteration advance by counting: a division per copy would cost
+  // this one thread more than the copy itself
+  struct Cursor { int index, kb; };
+  auto advance = [&](Cursor& c) { if (++c.kb == kb_count) { c.kb = 0; ++c.index; } };
+  auto load_a = [&](const Cursor& c, int stage) {
+    const int n_tile = tile_of(c.index) / args.t_tiles;
+    const int k = (kb_begin + c.kb) * kTileK;
+    const uint32_t bar = smem_addr(&full_bar[stage]);
+    mbar_expect_tx(bar, Shape::kStageBytes);
+    tma_load_2d(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN);
+    if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN);
+  };
+  auto load_b = [&](const Cursor& c, int stage) {
+    const int t_tile = tile_of(c.index) % args.t_tiles;
+    tma_load_2d(stage_b(stage), &map_x, smem_addr(&full_bar[stage]), (kb_begin + c.kb) * kTileK, t_tile * BN);
+  };
+  const int prefetch = static_cast<int>(min(static_cast<long long>(kStages), total_iters));
+  Cursor cursor = {0, 0};
 
   if (threadIdx.x == 64) {                    // an epilogue warp: idle until the first tile is done
     prefetch_tensormap(&map_w);
@@ -113,6 +144,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     mbar_init(smem_addr(&drain_bar), 1);
     aborted_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The first weight tiles leave at once, before the rest of the CTA is set up and before the
+    // kernel upstream has finished: nothing in the stream writes weights.
+    for (int it = 0; it < prefetch; ++it) { load_a(cursor, it); advance(cursor); }
   }
   if (warp == 1) {
     tmem_alloc(smem_addr(&tmem_base_slot), Shape::kTmemColumns);
@@ -122,43 +156,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  if (args.pdl && threadIdx.x == 0) pdl_trigger();
-
-  // this CTA's slice of the k-blocks and its tiles
-  const int rank = blockIdx.x;
-  const int k_base = args.k_blocks / args.k_split, k_rem = args.k_blocks - k_base * args.k_split;
-  const int kb_begin = rank * k_base + min(rank, k_rem);
-  const int kb_count = k_base + (rank < k_rem ? 1 : 0);
-  const int tiles = args.n_tiles * args.t_tiles;
-  const int my_tiles = (tiles - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) /
-                       static_cast<int>(gridDim.y);
-  const long long total_iters = static_cast<long long>(my_tiles) * kb_count;
-  auto tile_of = [&](int index) { return static_cast<int>(blockIdx.y) + index * static_cast<int>(gridDim.y); };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // (tile index, k-block) of an iteration advance by counting: a division per copy would cost
-      // this one thread more than the copy itself
-      struct Cursor { int index, kb; };
-      auto advance = [&](Cursor& c) { if (++c.kb == kb_count) { c.kb = 0; ++c.index; } };
-      auto load_a = [&](const Cursor& c, int stage) {
-        const int n_tile = tile_of(c.index) / args.t_tiles;
-        const int k = (kb_begin + c.kb) * kTileK;
-        const uint32_t bar = smem_addr(&full_bar[stage]);
-        mbar_expect_tx(bar, Shape::kStageBytes);
-        tma_load_2d(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN);
-        if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN);
-      };
-      auto load_b = [&](const Cursor& c, int stage) {
-        const int t_tile = tile_of(c.index) % args.t_tiles;
-        tma_load_2d(stage_b(stage), &map_x, smem_addr(&full_bar[stage]), (kb_begin + c.kb) * kTileK, t_tile * BN);
-      };
-      // weights first: nothing in the stream writes them, so they may fly before the
-      // previous kernel has finished; the activations only after
-      const int prefetch = static_cast<int>(min(static_cast<long long>(kStages), total_iters));
-      Cursor cursor = {0, 0};
-      for (int it = 0; it < prefetch; ++it) { load_a(cursor, it); advance(cursor); }
+      // the weights of the first stages are on their way (set-up above); the activations only
+      // once the kernel upstream has finished
       if (args.pdl) pdl_wait();
       Cursor second = {0, 0};
       for (int it = 0; it < prefetch; ++it) { load_b(second, it); advance(second); }
