@@ -26,6 +26,7 @@ from .base import (
 TARGET_CTAS = 2 * 148     # work items the attention kernels want in flight on a B200
 DECODE_TARGET_CTAS = 148  # ... in a decode-only step, whose kernel keeps a whole SM's shared memory busy
 MAX_SPLITS = 16
+CLUSTER_SPLITS = 8        # the portable size of a thread-block cluster
 MIN_KEYS_PER_SPLIT = 256
 
 
@@ -68,6 +69,10 @@ class AttentionItems(StepPlanner):
             if not shape.decode_only:
                 longest = int((starts + lengths).max())
                 splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
+            elif tensor_core:
+                # the tcgen05 decode kernel merges a tile's key ranges inside one thread-block
+                # cluster: at most 8 CTAs, and a power of two schedules best
+                splits = 1 << (min(splits, CLUSTER_SPLITS).bit_length() - 1)
             if splits == 1 or chunk_rows == kernels.CHUNK_TILE_ROWS or bool(is_decode.all()):
                 break                  # the tcgen05 chunk kernel does not split key ranges
         entry = np.repeat(np.arange(len(lengths), dtype=np.int64), tiles)

@@ -55,6 +55,15 @@ def test_a_decode_only_step_splits_by_the_number_of_entries_alone():
     assert full["splits"] == 1
 
 
+def test_decode_steps_of_the_cluster_kernel_split_into_a_power_of_two_up_to_eight():
+    planner = AttentionItems(4, 8, 128)
+    for entries, want in [(1, 8), (2, 8), (3, 4), (4, 4), (8, 2), (9, 2), (16, 1)]:
+        plan = planner.plan(StepShape(np.ones(entries, np.int32), np.full(entries, 500, np.int32), True, page_size=16))
+        assert plan["splits"] == want, entries
+    other_page = planner.plan(StepShape(np.ones(1, np.int32), np.full(1, 500, np.int32), True, page_size=24))
+    assert other_page["splits"] == MAX_SPLITS            # the mma.sync tiles merge in a kernel of their own
+
+
 def test_short_contexts_are_not_split_in_a_mixed_step():
     planner = AttentionItems(4, 8)
     plan = planner.plan(StepShape(np.array([30, 1], np.int32), np.array([0, 100], np.int32), decode_only=False))
