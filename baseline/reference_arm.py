@@ -111,6 +111,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None)
     parser.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    parser.add_argument("--workload", choices=["decode", "serve"], default="decode")
+    parser.add_argument("--requests", type=int, default=64)
     parser.add_argument("--workdir", default="/tmp/rapid_llm_b200_reference_arm")
     args = parser.parse_args()
     globals()["PROMPT_LEN"] = args.prompt_len
@@ -131,7 +133,8 @@ def main() -> int:
 
     say("building the reference engine")
     scheduler = Scheduler.from_pretrained(
-        str(folder), max_seq_len=CONTEXT, max_num_seqs=max(args.batch, 8), max_num_batched_tokens=8192,
+        str(folder), max_seq_len=CONTEXT, max_num_seqs=max(args.batch, 8, min(args.requests, 64) if args.workload == "serve" else 0),
+        max_num_batched_tokens=PREFILL_TOKENS if args.workload == "serve" else 8192,
         max_chunk_size=PREFILL_TOKENS, use_cuda_graph=True,
     )
     scheduler.stop_token_ids = set()
@@ -144,6 +147,29 @@ def main() -> int:
     def drain() -> None:
         while scheduler.has_unfinished_requests():
             scheduler.step()
+
+    if args.workload == "serve":
+        # the continuous-batching workload of bench.py's serve_run, the same requests in the same order
+        generator = torch.Generator().manual_seed(3)
+        count = args.requests
+        prompt_lengths = torch.randint(128, 4097, (count,), generator=generator).tolist()
+        output_lengths = torch.randint(64, 513, (count,), generator=generator).tolist()
+        prompts = [torch.randint(0, vocab, (n,), generator=generator).tolist() for n in prompt_lengths]
+        for prompt, n in zip(prompts, output_lengths):          # once untimed: loads, graphs, compilation
+            scheduler.add_request("", greedy(n), prompt_token_ids=prompt)
+        drain()
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        requests = [scheduler.add_request("", greedy(n), prompt_token_ids=p) for p, n in zip(prompts, output_lengths)]
+        drain()
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - started
+        print(json.dumps({
+            "seconds": seconds, "generated_tokens": sum(len(r.output_token_ids) for r in requests),
+            "prompt_tokens": sum(prompt_lengths), "wanted_tokens": sum(output_lengths),
+            "layers": config["num_hidden_layers"], "layers_full": layers_full,
+        }))
+        return 0
 
     # prefill of one 2,048-token prompt: submit, step until its first token; best of three
     prefill_ms = []

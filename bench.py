@@ -255,7 +255,7 @@ def serve_run(args, config, raw: dict, shape_name: str, layers: int, layers_full
     """Continuous batching as a user meets it: ``--requests`` prompts of uniform-random length
     (128 to 4,096 tokens) with 64 to 512 tokens to generate each, all handed to ``generate`` at
     once; prompts are cut into portions of 2,048 tokens a step beside the decoding requests.
-    Timed by the wall clock around the call, host token ids in and out."""
+    Run once untimed, then timed by the wall clock around the call, host token ids in and out."""
     import torch
 
     from rapid_llm_b200 import LLM, EngineConfig, SamplingParams
@@ -277,10 +277,9 @@ def serve_run(args, config, raw: dict, shape_name: str, layers: int, layers_full
     llm = LLM.from_runner(ModelRunner.from_random(config, seed=0, config=engine))
     params = [SamplingParams.greedy(max_gen_len=n) for n in output_lengths]
     llm.scheduler.stop_token_ids = set()
-    warm = llm.generate(prompts[:2], [SamplingParams.greedy(max_gen_len=8)] * 2)     # loads, graphs, workspaces
-    assert all(len(o.token_ids) == 8 for o in warm)
+    llm.generate(prompts, params)      # the whole workload once untimed: loads, graphs, workspaces
     torch.cuda.synchronize()
-    before = kernels.LAUNCHES.count
+    before, steps_before = kernels.LAUNCHES.count, llm.runner.steps_run
     with ClockSampler() as clocks:
         begin = time.perf_counter()
         outputs = llm.generate(prompts, params)
@@ -294,7 +293,7 @@ def serve_run(args, config, raw: dict, shape_name: str, layers: int, layers_full
         "dtype": "bf16", "data": "synthetic", "impl": "ours", "seconds": round(seconds, 3),
         "prompt_tokens": sum(prompt_lengths), "generated_tokens": generated,
         "all_tokens_per_second": round((sum(prompt_lengths) + generated) / seconds, 1),
-        "steps": llm.runner.steps_run, "preemptions": llm.scheduler.num_preemptions,
+        "steps": llm.runner.steps_run - steps_before, "preemptions": llm.scheduler.num_preemptions,
         "gpu_launches": kernels.LAUNCHES.count - before,
         "config": {
             "model": f"{shape_name} shape, random weights", "layers": layers, "layers_full": layers_full,
@@ -407,7 +406,10 @@ def run_reference(args) -> dict:
     if not (ROOT / "baseline" / "_ref" / "rapid_llm").is_dir():
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
     command = [sys.executable, str(arm), "--steps", str(args.steps), "--warmup", str(args.warmup),
-               "--batch", str(args.batch), "--prompt-len", str(args.prompt_len)]
+               "--batch", str(args.batch), "--prompt-len", str(args.prompt_len),
+               "--workload", args.workload, "--requests", str(args.requests)]
+    if args.shape != "8b":
+        return {"impl": "reference", "unavailable": "the reference arm is set up for the 8B shape of the benchmark only"}
     if args.layers:
         command += ["--layers", str(args.layers)]
     try:
@@ -420,6 +422,18 @@ def run_reference(args) -> dict:
         tail = " | ".join((done.stderr or done.stdout).strip().splitlines()[-3:])[:400]
         return {"impl": "reference", "unavailable": f"the reference engine failed here (exit {done.returncode}): {tail}"}
     got = json.loads(lines[-1])
+    if args.workload == "serve":
+        return {
+            "metric": f"generated tok/s, continuous batching of {args.requests} requests (Qwen3-8B shape)",
+            "value": round(got["generated_tokens"] / got["seconds"], 1), "unit": "tok/s", "n_gpus": 1,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "seconds": round(got["seconds"], 3), "prompt_tokens": got["prompt_tokens"],
+            "generated_tokens": got["generated_tokens"], "wanted_tokens": got["wanted_tokens"],
+            "all_tokens_per_second": round((got["prompt_tokens"] + got["generated_tokens"]) / got["seconds"], 1),
+            "config": {"model": "Qwen3-8B shape, random weights", "layers": got["layers"], "layers_full": got["layers_full"],
+                       "requests": args.requests, "engine": "rapid_llm.engine.Scheduler (stock path, CUDA graphs on)"},
+            "clocks": clocks.summary(),
+        }
     peaks = measured_peaks()
     raw = dict(QWEN3_8B)
     layers = got["layers"]
