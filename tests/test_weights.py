@@ -56,6 +56,38 @@ def test_every_tensor_lands_where_it_belongs(tiny_dirs):
     assert model.head.weight is not model.embedding.weight
 
 
+def test_a_model_in_several_shards_loads_like_one_file(tiny_dirs, tmp_path):
+    """Shards are read in name order; q, k and v of one layer may lie in different files.  A tensor
+    that two shards hold is reported, not silently taken from one of them."""
+    folder = tiny_dirs["B"]
+    tensors = {}
+    with SafetensorsFile(folder / "model.safetensors") as handle:
+        for name in handle.keys():
+            tensors[name] = handle.tensor(name).clone()
+    names = sorted(tensors)
+    out = tmp_path / "sharded"
+    out.mkdir()
+    (out / "config.json").write_text((folder / "config.json").read_text())
+    for index in range(3):
+        part = {name: tensors[name] for name in names[index::3]}
+        write_safetensors(out / f"model-{index + 1:05d}-of-00003.safetensors", part)
+    whole, sharded = build(folder), build(out)
+    for a, b in zip(whole.layers, sharded.layers):
+        assert torch.equal(a.mixer.qkv, b.mixer.qkv) and torch.equal(a.mixer.o, b.mixer.o)
+        assert torch.equal(a.mixer.q_norm, b.mixer.q_norm) and torch.equal(a.mixer.k_norm, b.mixer.k_norm)
+        assert torch.equal(a.feed_forward.gate_up, b.feed_forward.gate_up)
+        assert torch.equal(a.feed_forward.down, b.feed_forward.down)
+        assert torch.equal(a.mixer_norm.weight, b.mixer_norm.weight)
+        assert torch.equal(a.feed_forward_norm.weight, b.feed_forward_norm.weight)
+    assert torch.equal(whole.embedding.weight, sharded.embedding.weight)
+    assert torch.equal(whole.head.weight, sharded.head.weight)
+    assert torch.equal(whole.final_norm.weight, sharded.final_norm.weight)
+    write_safetensors(out / "model-00004-of-00003.safetensors", {names[0]: tensors[names[0]]})
+    with pytest.raises(WeightLoadError) as caught:
+        build(out)
+    assert names[0] in str(caught.value)
+
+
 def test_tied_head_is_the_embedding_and_a_shipped_head_wins(tiny_dirs, tmp_path):
     model = build(tiny_dirs["A"])
     assert model.head.weight is model.embedding.weight
