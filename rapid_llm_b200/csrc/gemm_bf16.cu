@@ -111,6 +111,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   // (tile index, k-block) of an iteration advance by counting: a division per copy would cost
   // this one thread more than the copy itself
+  const uint64_t weights_once = l2_evict_first_policy();
   struct Cursor { int index, kb; };
   auto advance = [&](Cursor& c) { if (++c.kb == kb_count) { c.kb = 0; ++c.index; } };
   auto load_a = [&](const Cursor& c, int stage) {
@@ -118,8 +119,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int k = (kb_begin + c.kb) * kTileK;
     const uint32_t bar = smem_addr(&full_bar[stage]);
     mbar_expect_tx(bar, Shape::kStageBytes);
-    tma_load_2d(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN);
-    if (kSwiglu) tma_load_2d(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN);
+    tma_load_2d_hint(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN, weights_once);
+    if (kSwiglu) tma_load_2d_hint(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN, weights_once);
   };
   auto load_b = [&](const Cursor& c, int stage) {
     const int t_tile = tile_of(c.index) % args.t_tiles;
