@@ -198,6 +198,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
     uint64_t* empties = is_value ? empty_v : empty_k;
     const int box_rows = min(args.page_size, kTcKeys);
     const int boxes = kTcKeys / box_rows;
+    const uint64_t read_once = l2_evict_first_policy();   // a decode step reads every key and value once
     bool waited = false, ok = true;
     int issued = 0;
     for (int b = 0; b < n_blocks && ok; ++b) {
@@ -238,7 +239,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
         }
         const int row = ((page * 2 + is_value) * args.hkv + kv_head) * args.page_size + in_page;
         const uint32_t dst = (is_value ? v_tile(stage) : k_tile(stage)) + half * kTcHalfBytes + x * box_rows * 128;
-        tma_load_2d(dst, &map_cache, smem_addr(&fulls[stage]), half * 64, row);
+        tma_load_2d_hint(dst, &map_cache, smem_addr(&fulls[stage]), half * 64, row, read_once);
       }
       ++issued;
     }
