@@ -59,10 +59,13 @@ template <bool kSwiglu, int BN>
 struct GemmShape {
   static constexpr int kHalves = kSwiglu ? 2 : 1;
   static constexpr int kStageBytes = kHalves * kTileN * kTileK * 2 + BN * kTileK * 2;
-  // Small token tiles stream weights: three or more stages within 110 KB let two CTAs (or this
-  // kernel's and the next one's) share an SM.  Large token tiles get the whole SM.
+  // Small token tiles stream weights.  Their ring stays within 74 KB, so that three CTAs fit an
+  // SM: while two CTAs of one product stream, a CTA of the next one sets itself up and fetches
+  // its first weight tiles beside them (measured: better than a deeper ring with two per SM, and
+  // than a shallower one with four).  The SwiGLU tiles are twice as large and keep 110 KB, two
+  // per SM.  Large token tiles get the whole SM.
   static constexpr bool kShareSm = BN <= 64 && 3 * kStageBytes <= 110 * 1024;
-  static constexpr int kBudget = kShareSm ? 110 * 1024 : 200 * 1024;
+  static constexpr int kBudget = kShareSm ? (kSwiglu ? 110 : 74) * 1024 : 200 * 1024;
   static constexpr int kStagesFit = kBudget / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kAccColumns = kHalves * BN;          // per accumulator buffer
