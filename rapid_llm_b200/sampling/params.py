@@ -4,8 +4,9 @@
 ``max_gen_len`` ``None`` fills the context; ``repetition_penalty`` > 0 with 1.0 off;
 values are validated at construction.  ``seed`` is an addition: draws come from a
 counter-based generator keyed by (seed, index of the generated token), so a request's
-tokens do not depend on what else is in the batch.  The text-level ``stop_on_repeat``
-breaker and logprob reporting need a tokenizer-bound engine and are not carried over.
+tokens do not depend on what else is in the batch.  Not carried over: the text-level
+``stop_on_repeat`` breaker, which needs a tokenizer-bound engine, and the reporting of
+log-probabilities (``logprobs``, ``prompt_logprobs``), which is not part of sampling.
 """
 
 from __future__ import annotations
