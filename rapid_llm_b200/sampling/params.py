@@ -4,9 +4,10 @@
 ``max_gen_len`` ``None`` fills the context; ``repetition_penalty`` > 0 with 1.0 off;
 values are validated at construction.  ``seed`` is an addition: draws come from a
 counter-based generator keyed by (seed, index of the generated token), so a request's
-tokens do not depend on what else is in the batch.  Not carried over: the text-level
-``stop_on_repeat`` breaker, which needs a tokenizer-bound engine, and the reporting of
-log-probabilities (``logprobs``, ``prompt_logprobs``), which is not part of sampling.
+tokens do not depend on what else is in the batch.  ``stop_on_repeat`` is accepted and
+inert: the reference's breaker looks at decoded text, which token-id requests do not have.
+``logprobs`` and ``prompt_logprobs`` (reporting, not sampling) are accepted only as ``None``;
+any other value is refused at construction rather than ignored.
 """
 
 from __future__ import annotations
@@ -20,6 +21,9 @@ class SamplingParams:
     top_p: float = 0.9
     max_gen_len: int | None = None
     repetition_penalty: float = 1.1
+    stop_on_repeat: bool = True
+    logprobs: int | None = None
+    prompt_logprobs: int | None = None
     seed: int | None = None
 
     def __post_init__(self) -> None:
@@ -31,6 +35,8 @@ class SamplingParams:
             raise ValueError(f"max_gen_len must be >= 1 or None, got {self.max_gen_len}")
         if self.repetition_penalty <= 0:
             raise ValueError(f"repetition_penalty must be > 0, got {self.repetition_penalty}")
+        if self.logprobs is not None or self.prompt_logprobs is not None:
+            raise ValueError("logprobs and prompt_logprobs are not reported by this engine; leave them None")
         if self.seed is not None and not 0 <= self.seed < 2**63:
             raise ValueError(f"seed must be in [0, 2**63), got {self.seed}")
 

@@ -164,6 +164,9 @@ def test_sampling_params_are_validated():
         with pytest.raises(ValueError):
             SamplingParams(**bad)
     assert SamplingParams().temperature == 0.6 and SamplingParams().top_p == 0.9 and SamplingParams().repetition_penalty == 1.1
+    assert SamplingParams(stop_on_repeat=False, logprobs=None).stop_on_repeat is False      # the reference's fields are accepted
+    with pytest.raises(ValueError):
+        SamplingParams(logprobs=5)
     assert SamplingParams(temperature=0).is_greedy
 
 
