@@ -52,6 +52,17 @@ class LLM:
         max_gpu_num_blocks: int | None = None,
         device: str = "cuda",
         use_cuda_graph: bool | None = None,
+        quantization: str | None = None,
+        tensor_parallel_size: int = 1,
+        data_parallel_size: int = 1,
+        enable_expert_parallel: bool = False,
+        prefill_context_parallel_size: int = 1,
+        prefill_context_parallel_strategy: str = "zigzag",
+        decode_context_parallel_size: int = 1,
+        dcp_comm_backend: str = "ag_rs",
+        kv_cache_dtype: str = "auto",
+        cuda_graph_lazy: bool = False,
+        hf_overrides: Mapping[str, Any] | None = None,
         dtype: str | torch.dtype = "bfloat16",
         page_size: int = 16,
         max_num_seqs: int = 32,
@@ -60,10 +71,21 @@ class LLM:
         enable_chunked_prefill: bool = True,
         enable_preemption: bool = True,
         run_ahead: bool = True,
-        hf_overrides: Mapping[str, Any] | None = None,
         stop_token_ids: Sequence[int] | None = None,
         runner: ModelRunner | None = None,
     ) -> None:
+        # The reference's options for what this engine does not do are accepted at their neutral
+        # values (``rapid_llm/engine/llm.py:78-96``) and refused otherwise, never ignored.
+        neutral = {
+            "quantization": (quantization, None), "tensor_parallel_size": (tensor_parallel_size, 1),
+            "data_parallel_size": (data_parallel_size, 1), "enable_expert_parallel": (enable_expert_parallel, False),
+            "prefill_context_parallel_size": (prefill_context_parallel_size, 1),
+            "decode_context_parallel_size": (decode_context_parallel_size, 1), "kv_cache_dtype": (kv_cache_dtype, "auto"),
+        }
+        refused = [f"{name}={value!r}" for name, (value, wanted) in neutral.items() if value != wanted]
+        if refused:
+            raise ValueError("this engine runs unquantised weights and caches on one GPU; not supported: " + ", ".join(refused))
+        del prefill_context_parallel_strategy, dcp_comm_backend, cuda_graph_lazy   # meaningful only with the above
         if device == "cuda":
             device = "cuda:0"
         self.engine_config = EngineConfig(

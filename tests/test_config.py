@@ -110,3 +110,15 @@ def test_schedule_validation():
         dataclasses.replace(spec, schedule=(ScheduleEntry(0, cache_from=1), ScheduleEntry(1))).validate()
     with pytest.raises(ValueError, match="names layer"):
         dataclasses.replace(spec, schedule=(ScheduleEntry(5),)).validate()
+
+
+def test_the_entry_point_refuses_options_of_what_is_not_built():
+    """The reference's constructor options are accepted at their neutral values; anything that asks
+    for quantisation or more than one GPU is refused before any work, never ignored."""
+    from rapid_llm_b200 import LLM
+
+    for option in (dict(quantization="fp8"), dict(tensor_parallel_size=2), dict(data_parallel_size=2),
+                   dict(enable_expert_parallel=True), dict(kv_cache_dtype="fp8")):
+        with pytest.raises(ValueError) as caught:
+            LLM("/nonexistent", **option)
+        assert next(iter(option)) in str(caught.value)
