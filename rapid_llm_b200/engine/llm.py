@@ -140,12 +140,7 @@ class LLM:
     def _decode(self, token_ids: list[int]) -> str:
         return "" if self.tokenizer is None else self.tokenizer.decode(token_ids)
 
-    def generate(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None) -> list[RequestOutput]:
-        """Generate for every prompt; returns one ``RequestOutput`` per prompt, in order.
-
-        ``prompts``: a string, a list of strings, one list of token ids, or a list of them.
-        ``sampling_params``: one set for all prompts, or one per prompt.
-        """
+    def _submit(self, prompts, sampling_params):
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         if sampling_params is None:
@@ -156,9 +151,45 @@ class LLM:
         if len(per_prompt) != len(prompts):
             raise ValueError("one SamplingParams for all prompts, or one per prompt")
         encoded = [self._encode(p) for p in prompts]
-        requests = [
-            self.scheduler.add_request(ids, params) for (_, ids), params in zip(encoded, per_prompt)
-        ]
+        requests = [self.scheduler.add_request(ids, params) for (_, ids), params in zip(encoded, per_prompt)]
+        return encoded, requests
+
+    def stream(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None):
+        """Yield, after every step that brought something, what each prompt gained since the last
+        yield: one entry per prompt, a piece of text when the model folder has a tokenizer, else
+        the list of new token ids (``rapid_llm/engine/llm.py:197-222`` yields text pieces the
+        same way).  Tokens that are still only on the device (the scheduler runs a step ahead)
+        are reported once the host has read them."""
+        _, requests = self._submit(prompts, sampling_params)
+        reported = [0] * len(requests)
+        texts = [""] * len(requests)
+        while True:
+            gained, anything = [], False
+            for index, request in enumerate(requests):
+                tokens = request.output_token_ids
+                known = next((i for i, token in enumerate(tokens) if token < 0), len(tokens))
+                new = list(tokens[reported[index]:known])
+                reported[index] = max(reported[index], known)
+                anything = anything or bool(new)
+                if self.tokenizer is None:
+                    gained.append(new)
+                else:
+                    text = self._decode(list(tokens[:known]))
+                    gained.append(text[len(texts[index]):])
+                    texts[index] = text
+            if anything:
+                yield gained
+            if not self.scheduler.has_unfinished():
+                return
+            self.scheduler.step()
+
+    def generate(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None) -> list[RequestOutput]:
+        """Generate for every prompt; returns one ``RequestOutput`` per prompt, in order.
+
+        ``prompts``: a string, a list of strings, one list of token ids, or a list of them.
+        ``sampling_params``: one set for all prompts, or one per prompt.
+        """
+        encoded, requests = self._submit(prompts, sampling_params)
         self.scheduler.run_to_completion()
         outputs = []
         for (text, ids), request in zip(encoded, requests):

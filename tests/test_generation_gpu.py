@@ -156,3 +156,23 @@ def test_many_requests_under_pressure_equal_plain(tiny_dirs, tiny_plain, name):
     llm.runner.cache.check()
     assert llm.runner.cache.num_free_slots == 4
     assert llm.scheduler.num_preemptions >= 1
+
+
+def test_streaming_yields_the_tokens_of_generate_piece_by_piece(tiny_dirs):
+    from rapid_llm_b200 import SamplingParams
+
+    prompts = random_prompts(256, [9, 40, 3], 8)
+    params = [SamplingParams.greedy(max_gen_len=n) for n in (12, 5, 20)]
+    llm = make_llm(tiny_dirs["A"], "float32", "A")
+    whole = [o.token_ids for o in llm.generate(prompts, params)]
+    pieces = [[] for _ in prompts]
+    yields = 0
+    for gained in llm.stream(prompts, params):
+        assert len(gained) == len(prompts) and any(gained)
+        for mine, new in zip(pieces, gained):
+            mine.extend(new)
+        yields += 1
+    assert pieces == whole and yields >= 12
+    assert all(token >= 0 for mine in pieces for token in mine)
+    llm.runner.cache.check()
+    assert llm.runner.cache.num_free_slots == 4
