@@ -20,7 +20,11 @@ def __getattr__(name):  # the engine imports lazily: configuration and weights w
         from .engine.runner import ModelRunner
 
         return ModelRunner
+    if name == "Scheduler":
+        from .engine.scheduler import Scheduler
+
+        return Scheduler
     raise AttributeError(name)
 
 
-__all__ = ["EngineConfig", "LLM", "ModelRunner", "Qwen3Config", "SamplingParams", "load_config"]
+__all__ = ["EngineConfig", "LLM", "ModelRunner", "Qwen3Config", "SamplingParams", "Scheduler", "load_config"]

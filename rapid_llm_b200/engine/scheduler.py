@@ -145,17 +145,42 @@ class Scheduler:
         self._inflight: Inflight | None = None
         self._can_launch = hasattr(executor, "launch") and hasattr(executor, "collect")
 
+    @classmethod
+    def from_pretrained(cls, model, **options) -> "Scheduler":
+        """A scheduler over a model folder, as the reference builds one
+        (``rapid_llm/engine/scheduler.py:410-440``): the options are those of
+        :class:`~rapid_llm_b200.engine.llm.LLM` (``max_seq_len``, ``max_num_seqs``,
+        ``max_num_batched_tokens``, ``max_chunk_size``, ``max_gpu_num_blocks``, ``use_cuda_graph``,
+        ``enable_preemption``, ``hf_overrides``, ``dtype``, ...).  The entry point it was built
+        through stays reachable as ``scheduler.llm``."""
+        from .llm import LLM
+
+        llm = LLM(model, **options)
+        llm.scheduler.llm = llm
+        return llm.scheduler
+
     # -- submission ------------------------------------------------------------------ #
     def add_request(
         self,
-        prompt_token_ids: Sequence[int],
+        prompt: Sequence[int] | str,
         params: SamplingParams | None = None,
         request_id: Hashable | None = None,
+        prompt_token_ids: Sequence[int] | None = None,
+        sampling_params: SamplingParams | None = None,
     ) -> Request:
         """Queue a request.  An empty prompt, or one that leaves no room to generate, is refused
-        (``rapid_llm/engine/batch_planner.py:403-427``); so is one the pool could never hold."""
-        params = params or SamplingParams()
-        prompt = [int(t) for t in prompt_token_ids]
+        (``rapid_llm/engine/batch_planner.py:403-427``); so is one the pool could never hold.
+
+        ``prompt`` is the list of token ids.  The reference's calling form, text first and the
+        ids in ``prompt_token_ids`` (``rapid_llm/engine/scheduler.py:635-643``), is taken too: the
+        ids win, and text without ids is refused, since the scheduler holds no tokenizer
+        (``LLM.generate`` encodes text).  ``sampling_params`` is the reference's name of ``params``."""
+        params = params or sampling_params or SamplingParams()
+        if prompt_token_ids is not None:
+            prompt = prompt_token_ids
+        elif isinstance(prompt, str):
+            raise ValueError("the scheduler takes token ids: pass prompt_token_ids, or use LLM.generate for text")
+        prompt = [int(t) for t in prompt]
         limit = self.config.max_seq_len
         if not prompt:
             raise ValueError("the prompt is empty")
@@ -180,6 +205,8 @@ class Scheduler:
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running or self._inflight is not None)
+
+    has_unfinished_requests = has_unfinished      # the reference's name
 
     # -- planning -------------------------------------------------------------------- #
     def _chunk(self, request: Request, budget: int) -> int:
@@ -366,7 +393,12 @@ class Scheduler:
         elif request in self.waiting:                    # evicted while its last token was in flight
             self.waiting.remove(request)
 
-    def abort(self, request: Request) -> None:
+    def abort(self, request: Request | Hashable) -> None:
+        """End a request now; takes the handle or, as the reference does, its id."""
+        if not isinstance(request, Request):
+            request = next((r for r in [*self.running, *self.waiting] if r.request_id == request), None)
+            if request is None:
+                return
         if request.status in (RUNNING, WAITING):
             self._finish(request, "abort", time.perf_counter())
 

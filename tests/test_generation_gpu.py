@@ -176,3 +176,20 @@ def test_streaming_yields_the_tokens_of_generate_piece_by_piece(tiny_dirs):
     assert all(token >= 0 for mine in pieces for token in mine)
     llm.runner.cache.check()
     assert llm.runner.cache.num_free_slots == 4
+
+
+def test_a_scheduler_from_a_model_folder_steps_requests_by_hand(tiny_dirs, tiny_plain):
+    """The reference's other way in: ``Scheduler.from_pretrained``, ``add_request``, ``step``."""
+    from rapid_llm_b200.engine import Scheduler
+
+    config, weights = tiny_plain["A"]
+    prompt = random_prompts(256, [21], 12)[0]
+    scheduler = Scheduler.from_pretrained(tiny_dirs["A"], dtype="float32", max_seq_len=128, max_gpu_num_blocks=16,
+                                          page_size=PAGE_SIZES["A"], max_num_seqs=2, max_chunk_size=8)
+    from rapid_llm_b200 import SamplingParams
+    request = scheduler.add_request("", SamplingParams.greedy(max_gen_len=6), prompt_token_ids=prompt)
+    steps = 0
+    while scheduler.has_unfinished_requests():
+        scheduler.step()
+        steps += 1
+    assert request.output_token_ids == greedy_generate(config, weights, prompt, 6) and steps >= 3 + 6

@@ -159,6 +159,25 @@ def test_whole_prompts_only_when_chunking_is_off():
     assert executor.steps[-1] == [("b", 0, 40, True)]
 
 
+def test_the_references_calling_forms_are_taken():
+    """Text first and ids by keyword, ``sampling_params``, ``has_unfinished_requests``, abort by id
+    (``rapid_llm/engine/scheduler.py:635-643``)."""
+    scheduler, executor = make()
+    a = scheduler.add_request("ignored text", sampling_params=greedy(2), request_id="a", prompt_token_ids=list(range(5)))
+    b = scheduler.add_request(list(range(9)), greedy(50), "b")
+    assert a.prompt_token_ids == list(range(5)) and a.params.max_gen_len == 2
+    with pytest.raises(ValueError):
+        scheduler.add_request("text alone")
+    assert scheduler.has_unfinished_requests()
+    scheduler.step()
+    scheduler.abort("b")
+    scheduler.abort("nobody")                           # unknown ids are not an error
+    scheduler.run_to_completion()
+    assert not scheduler.has_unfinished_requests()
+    assert a.output_token_ids == [1000, 1001] and b.finish_reason == "abort"
+    assert executor.cache.num_free_slots == 4
+
+
 def test_sampling_params_are_validated():
     for bad in (dict(temperature=-1), dict(top_p=0), dict(top_p=1.5), dict(max_gen_len=0), dict(repetition_penalty=0)):
         with pytest.raises(ValueError):
