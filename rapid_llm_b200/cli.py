@@ -39,6 +39,15 @@ def _add_engine_options(sub: argparse.ArgumentParser) -> None:
     sub.add_argument("--max-gen-len", type=int, default=None)
     sub.add_argument("--repetition-penalty", type=float, default=1.1,
                      help="Penalise logits of already-generated tokens (1.0 disables it)")
+    # the reference's options for what this engine does not do: taken at their neutral values only
+    sub.add_argument("--quantization", default=None, help="not supported (weights stay bfloat16 or float32)")
+    sub.add_argument("--kv-cache-dtype", default="auto", help='only "auto": the cache has the model\'s dtype')
+    sub.add_argument("--tensor-parallel-size", type=int, default=1, help="only 1: one GPU")
+    sub.add_argument("--enable-expert-parallel", action="store_true", help="not supported")
+    sub.add_argument("--prefill-context-parallel-size", type=int, default=1, help="only 1")
+    sub.add_argument("--prefill-context-parallel-strategy", default="zigzag", help="without meaning on one GPU")
+    sub.add_argument("--decode-context-parallel-size", type=int, default=1, help="only 1")
+    sub.add_argument("--dcp-comm-backend", default="ag_rs", help="without meaning on one GPU")
     sub.add_argument("--seed", type=int, default=None, help="seed of the sampling draws")
     sub.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     sub.add_argument("--page-size", type=int, default=16)
@@ -63,8 +72,6 @@ def _sampling(args):
 
 
 def run_batch(args) -> int:
-    from .engine.llm import LLM
-
     if args.prompt_ids_file:
         lines = [line.strip() for line in Path(args.prompt_ids_file).read_text().splitlines()]
         prompts = [[int(t) for t in line.replace(",", " ").split()] for line in lines if line]
@@ -74,15 +81,32 @@ def run_batch(args) -> int:
         prompts = list(DEMO_PROMPTS)
     if not prompts:
         raise SystemExit("the prompt file contains no prompts")
-    llm = LLM(
+    try:
+        llm = _build_llm(args)
+    except (ValueError, FileNotFoundError) as error:       # a refused option, a folder without a model
+        raise SystemExit(f"rapid-llm-b200: {error}") from None
+    started = time.perf_counter()
+    outputs = llm.generate(prompts, _sampling(args))
+    elapsed = time.perf_counter() - started
+    return _report(args, outputs, started, elapsed)
+
+
+def _build_llm(args):
+    from .engine.llm import LLM
+
+    return LLM(
         _model_dir(args), max_seq_len=args.max_seq_len, max_gpu_num_blocks=args.max_gpu_num_blocks,
         device=args.device, use_cuda_graph=args.cuda_graph, dtype=args.dtype, page_size=args.page_size,
         max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
         max_chunk_size=args.max_chunk_size, run_ahead=args.run_ahead,
+        quantization=args.quantization, kv_cache_dtype=args.kv_cache_dtype,
+        tensor_parallel_size=args.tensor_parallel_size, enable_expert_parallel=args.enable_expert_parallel,
+        prefill_context_parallel_size=args.prefill_context_parallel_size,
+        decode_context_parallel_size=args.decode_context_parallel_size,
     )
-    started = time.perf_counter()
-    outputs = llm.generate(prompts, _sampling(args))
-    elapsed = time.perf_counter() - started
+
+
+def _report(args, outputs, started: float, elapsed: float) -> int:
     for index, output in enumerate(outputs):
         completion = output.outputs[0]
         print(f"--- [{index}] {completion.finish_reason} ---")
