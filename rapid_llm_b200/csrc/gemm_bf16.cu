@@ -375,7 +375,9 @@ static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, GemmA
   }
   args.k_split = split;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(split, split > 1 ? tiles : (tiles < resident ? tiles : resident));
+  // a product that is not split walks its tiles with as many CTAs as fit: three per SM for the small rings
+  const int walkers = Shape::kShareSm && !kSwiglu ? 3 * sm_count() : resident;
+  config.gridDim = dim3(split, split > 1 ? tiles : (tiles < walkers ? tiles : walkers));
   config.blockDim = dim3(kGemmThreads);
   config.dynamicSmemBytes = Shape::kSmemBytes;
   config.stream = stream;
