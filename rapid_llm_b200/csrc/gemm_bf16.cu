@@ -359,7 +359,8 @@ static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, GemmA
     configured = true;
   }
   // how many CTAs the GPU holds at once, and how finely to split k so that they all stream
-  const int resident = sm_count() * (Shape::kShareSm ? 2 : 1);
+  // (three of the smallest tiles' CTAs fit an SM and splitting for three pays there; measured)
+  const int resident = sm_count() * (Shape::kShareSm ? (!kSwiglu && BN <= 16 ? 3 : 2) : 1);
   const int tiles = args.n_tiles * args.t_tiles;
   int split = 1;
   if (Shape::kCanSplit) {
