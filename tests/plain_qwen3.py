@@ -11,7 +11,6 @@ compares this file with them.
 from __future__ import annotations
 
 import json
-import math
 import struct
 from pathlib import Path
 

@@ -3,7 +3,6 @@ under random orders of requests; windows give pages back; slots; groups."""
 
 import random
 
-import numpy as np
 import pytest
 
 from rapid_llm_b200.cache import CacheError, CacheManager, PagePool, plan_groups

@@ -100,7 +100,7 @@ def test_round_trip_through_config_json():
 
 
 def test_schedule_validation():
-    from rapid_llm_b200.config import ModelSpec, ScheduleEntry
+    from rapid_llm_b200.config import ScheduleEntry
     import dataclasses
 
     spec = Qwen3Config.from_dict(TINY_A).to_spec()

@@ -18,7 +18,7 @@ import numpy as np
 import pytest
 import torch
 from plain_qwen3 import forward_logits
-from tiny_configs import CONFIGS, PAGE_SIZES
+from tiny_configs import PAGE_SIZES
 from tolerances import for_dtype
 from trace_tools import collect, mixed, portions, tail_one_by_one, whole
 
