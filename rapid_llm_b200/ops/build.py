@@ -49,9 +49,10 @@ LIBRARIES: dict[str, list[str]] = {
 }
 LIBRARY_FLAGS: dict[str, list[str]] = {}
 
-# head sizes whose attention library `build_all` compiles ahead of time; any other multiple
-# of 16 up to 256 is compiled when a model with that head size is first built
-DEFAULT_HEAD_DIMS = (64, 128)
+# head sizes whose attention library `build_all` compiles ahead of time (the architecture's 128,
+# the common 64 and the tiny configurations of the tests and of the smoke run); any other
+# multiple of 16 up to 256 is compiled when a model with that head size is first built
+DEFAULT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
 
 def attention_library(head_dim: int) -> str:
