@@ -427,6 +427,29 @@ def test_attention_decode_kernels(hq, hkv, page, window, splits, lengths, new_co
     torch.testing.assert_close(got, want, **for_dtype(dtype))
 
 
+@pytest.mark.parametrize("decode_kernel", ["auto", "mma"])
+def test_attention_decode_with_more_pages_than_a_cta_keeps_in_shared_memory(decode_kernel):
+    """A request of 8,300 tokens in pages of 8 has 1,038 pages: beyond the page ids a CTA copies
+    into shared memory (512 and 1,024), so the kernels read the block table as they go."""
+    dtype, hq, hkv, d, page = torch.bfloat16, 2, 1, 128, 8
+    lengths, new_counts = [8300, 9], [1, 1]
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=21)
+    scale = d**-0.5
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, 0, 1, decode_kernel)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, 0)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+def test_attention_prefill_tc_with_more_pages_than_a_cta_keeps_in_shared_memory():
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 1, 128, 8
+    lengths, new_counts = [8300], [100]
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=22)
+    scale = d**-0.5
+    got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, 0, page=page)
+    want = plain_paged(case, dtype, lengths, new_counts, scale, 0)
+    torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
 @pytest.mark.parametrize(
     "hq,hkv,page,window,lengths,new_counts",
     [(32, 8, 16, 0, [2048], [2048]),                                   # one whole prompt
