@@ -70,3 +70,36 @@ def test_one_wide_layer_whole_in_portions_and_decoding(name, tmp_path):
         torch.testing.assert_close(got, torch.stack(wanted), **tolerance)
     runner.check_fault()
     assert at == {"a": 300, "b": 90}
+
+
+def test_a_long_context_with_heads_of_128(tmp_path):
+    """3,300 tokens through two narrow layers with heads of 128: prompt portions whose tiles look
+    back over thousands of cached keys, then single tokens whose key range is split over a
+    cluster, against the plain implementation."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, intermediate_size=512))
+    raw.update(num_hidden_layers=2, vocab_size=500, max_position_embeddings=4096)
+    folder = write_random_model(tmp_path / "long", Qwen3Config.from_dict(raw), 13, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    tokens = torch.randint(0, 500, (3300,), generator=torch.Generator().manual_seed(6)).tolist()
+    plain = forward_logits(config, weights, tokens)
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=4096, page_size=16, num_pages=260, max_num_seqs=2,
+                          max_num_batched_tokens=1024, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    tolerance = at_scale("bfloat16", plain)
+    runner.admit("r")
+    at = 0
+    for size in (1024, 1024, 1000, 246):
+        places = [0, size // 2, size - 1]
+        got = runner.step([StepEntry("r", tokens[at : at + size], places)]).float().cpu()
+        torch.testing.assert_close(got, plain[[at + p for p in places]], **tolerance)
+        at += size
+    for _ in range(6):
+        got = runner.step_decode([StepEntry("r", tokens[at : at + 1], [0])]).float().cpu()
+        torch.testing.assert_close(got, plain[at : at + 1], **tolerance)
+        at += 1
+    runner.check_fault()
+    assert at == 3300
