@@ -103,3 +103,39 @@ def test_a_long_context_with_heads_of_128(tmp_path):
         at += 1
     runner.check_fault()
     assert at == 3300
+
+
+def test_a_window_on_one_layer_with_heads_of_128(tmp_path):
+    """Two layers with heads of 128, the second with a window of 200 keys: the tcgen05 kernels mask
+    the window's edge, the windowed group gives pages back as the window passes them."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, intermediate_size=384))
+    raw.update(num_hidden_layers=2, vocab_size=400, max_position_embeddings=1024,
+               use_sliding_window=True, sliding_window=200, max_window_layers=1)
+    folder = write_random_model(tmp_path / "window", Qwen3Config.from_dict(raw), 14, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    tokens = torch.randint(0, 400, (900,), generator=torch.Generator().manual_seed(7)).tolist()
+    plain = forward_logits(config, weights, tokens)
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=1024, page_size=16, num_pages=70, max_num_seqs=2,
+                          max_num_batched_tokens=512, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    assert len(runner.cache.groups) == 2
+    tolerance = at_scale("bfloat16", plain)
+    runner.admit("r")
+    at = 0
+    for size in (300, 7, 512, 61):
+        places = [0, size - 1]
+        got = runner.step([StepEntry("r", tokens[at : at + size], places)]).float().cpu()
+        torch.testing.assert_close(got, plain[[at + p for p in places]], **tolerance)
+        at += size
+    for _ in range(20):
+        got = runner.step_decode([StepEntry("r", tokens[at : at + 1], [0])]).float().cpu()
+        torch.testing.assert_close(got, plain[at : at + 1], **tolerance)
+        at += 1
+    runner.check_fault()
+    runner.cache.check()
+    held = sorted(sum(1 for p in pages if p) for pages in runner.cache.pages_of("r"))
+    assert held[1] >= 56 and held[0] <= 15               # all keys in one group, a window of them in the other
