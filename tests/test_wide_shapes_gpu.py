@@ -139,3 +139,42 @@ def test_a_window_on_one_layer_with_heads_of_128(tmp_path):
     runner.cache.check()
     held = sorted(sum(1 for p in pages if p) for pages in runner.cache.pages_of("r"))
     assert held[1] >= 56 and held[0] <= 15               # all keys in one group, a window of them in the other
+
+
+def test_graph_decode_of_three_requests_padded_to_a_bucket_of_four(tmp_path):
+    """Heads of 128, three requests decoded together from a captured graph whose batch is padded
+    with a row on the null page; then two of them, after the third has ended."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=1, intermediate_size=384))
+    raw.update(num_hidden_layers=2, vocab_size=400, max_position_embeddings=512)
+    folder = write_random_model(tmp_path / "bucket", Qwen3Config.from_dict(raw), 15, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    generator = torch.Generator().manual_seed(8)
+    tokens = {name: torch.randint(0, 400, (count,), generator=generator).tolist()
+              for name, count in (("a", 48), ("b", 181), ("c", 310))}
+    plain = {name: forward_logits(config, weights, ids) for name, ids in tokens.items()}
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=512, page_size=16, num_pages=48, max_num_seqs=4,
+                          max_num_batched_tokens=512, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    tolerance = at_scale("bfloat16", plain["c"])
+    at = {}
+    for name, ids in tokens.items():
+        runner.admit(name)
+        at[name] = len(ids) - 8
+        runner.step([StepEntry(name, ids[: at[name]], [])])
+    live = ["a", "b", "c"]
+    for step in range(8):
+        if step == 5:
+            runner.release("b")
+            live.remove("b")
+        entries = [StepEntry(name, tokens[name][at[name] : at[name] + 1], [0]) for name in live]
+        got = runner.step_decode(entries).float().cpu()
+        want = torch.stack([plain[name][at[name]] for name in live])
+        torch.testing.assert_close(got, want, **tolerance)
+        for name in live:
+            at[name] += 1
+    runner.check_fault()
+    runner.cache.check()
