@@ -220,12 +220,13 @@ def sample_token(logits, temperature, top_p=1.0, penalty=1.0, generated=(), seed
     if top_p < 1.0:
         order = torch.argsort(weights, descending=True, stable=True)
         sorted_w = weights[order]
-        before = torch.cumsum(sorted_w, 0) - sorted_w
-        # tokens of equal weight share the mass strictly above them
-        strictly_above = torch.tensor([float(weights[weights > w].sum()) for w in sorted_w])
+        before = torch.cumsum(sorted_w.double(), 0) - sorted_w.double()     # mass ranked before each token
+        # tokens of equal weight share the mass strictly above them: that of the first of their run
+        _, run, counts = torch.unique_consecutive(sorted_w, return_inverse=True, return_counts=True)
+        run_start = torch.cumsum(counts, 0) - counts
+        strictly_above = before[run_start[run]]
         keep = torch.zeros_like(keep)
         keep[order[strictly_above <= top_p * total]] = True
-        del before
     kept = torch.where(keep, weights, torch.zeros_like(weights))
     target = philox_uniform(seed, counter) * float(kept.sum())
     running = torch.cumsum(kept.double(), 0)

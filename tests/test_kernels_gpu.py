@@ -534,8 +534,9 @@ def test_greedy_is_first_maximum(dtype, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_sampling_matches_plain(dtype):
-    vocab, rows = 1237, 24
+@pytest.mark.parametrize("vocab", [1237, 151936, 400003])      # a small row; the model's; more than a cluster keeps in shared memory
+def test_sampling_matches_plain(dtype, vocab):
+    rows = 24
     logits = rand((rows, vocab), dtype, scale=2.0, seed=12).to(DEV)
     temperature = torch.tensor([0.0, 0.7, 1.0, 1.3] * 6, dtype=torch.float32)
     top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 0.3, 0.95] * 4, dtype=torch.float32)
