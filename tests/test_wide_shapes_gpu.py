@@ -178,3 +178,38 @@ def test_graph_decode_of_three_requests_padded_to_a_bucket_of_four(tmp_path):
             at[name] += 1
     runner.check_fault()
     runner.cache.check()
+
+
+def test_the_same_steps_give_the_same_bits(tmp_path):
+    """Reduction orders are fixed (cluster sums in rank order, split key ranges merged in order, no
+    atomics on values): two engines fed the same steps return identical logits, bit for bit."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, intermediate_size=2816))
+    raw.update(num_hidden_layers=2, vocab_size=3001, max_position_embeddings=1024)
+    folder = write_random_model(tmp_path / "bits", Qwen3Config.from_dict(raw), 16, dtype=torch.bfloat16)
+    generator = torch.Generator().manual_seed(9)
+    tokens = {name: torch.randint(0, 3001, (count,), generator=generator).tolist() for name, count in (("a", 700), ("b", 90))}
+
+    def run():
+        engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=1024, page_size=16, num_pages=64, max_num_seqs=4,
+                              max_num_batched_tokens=512, use_cuda_graph=True)
+        runner = ModelRunner.from_folder(folder, engine)
+        outputs = []
+        runner.admit("a"), runner.admit("b")
+        outputs.append(runner.step([StepEntry("a", tokens["a"][:400], [399]), StepEntry("b", tokens["b"][:60], [0, 59])]).clone())
+        outputs.append(runner.step([StepEntry("a", tokens["a"][400:690], [0, 289]), StepEntry("b", tokens["b"][60:61], [0])]).clone())
+        at = {"a": 690, "b": 61}
+        for _ in range(6):
+            entries = [StepEntry(name, tokens[name][at[name] : at[name] + 1], [0]) for name in ("a", "b")]
+            outputs.append(runner.step_decode(entries).clone())
+            for name in at:
+                at[name] += 1
+        runner.check_fault()
+        return outputs
+
+    first, second = run(), run()
+    for a, b in zip(first, second):
+        assert torch.equal(a, b)
