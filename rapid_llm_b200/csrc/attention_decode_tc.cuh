@@ -486,15 +486,33 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
     __syncwarp();
     cluster_sync();
     if (softmax_warp && team == 0) {
+      // where the other ranks keep their row statistics and this thread's column of their results
+      uint32_t peer_lse[8], peer_out[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        peer_lse[r] = r < args.splits ? peer_smem(smem_addr(&split_lse[0]), r) : 0u;
+        peer_out[r] = r < args.splits ? peer_smem(smem_addr(&split_out[t]), r) : 0u;
+      }
       for (int n = split; n < n_rows; n += args.splits) {
+        // all remote loads of the row first (each takes hundreds of cycles), the arithmetic after
+        float lse_of[8], out_of[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          lse_of[r] = r < args.splits ? load_peer_f32(peer_lse[r] + n * 4) : -INFINITY;
+          out_of[r] = r < args.splits ? load_peer_f32(peer_out[r] + n * 128 * 4) : 0.0f;
+        }
         float m = -INFINITY;
-        for (int r = 0; r < args.splits; ++r) m = fmaxf(m, load_cluster_f32(smem_addr(&split_lse[n]), r));
+#pragma unroll
+        for (int r = 0; r < 8; ++r) m = fmaxf(m, lse_of[r]);
         const float safe = m == -INFINITY ? 0.0f : m;
         float total = 0.0f, value = 0.0f;
-        for (int r = 0; r < args.splits; ++r) {
-          const float w = fast_exp2(load_cluster_f32(smem_addr(&split_lse[n]), r) - safe);
-          total += w;
-          value += w * load_cluster_f32(smem_addr(&split_out[n * 128 + t]), r);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < args.splits) {
+            const float w = fast_exp2(lse_of[r] - safe);
+            total += w;
+            value += w * out_of[r];
+          }
         }
         const int p = row0 + n, token = p / group;
         const size_t row = static_cast<size_t>(tok_begin + token) * args.hq + kv_head * group + (p - token * group);
