@@ -119,9 +119,11 @@ attention_mma_kernel(const AttentionArgs args) {
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp % kWarpsM, wn = warp / kWarpsM;
-  const int* item = args.items + static_cast<size_t>(blockIdx.x) * 4;
+  // the kv head is the fast grid dimension: CTAs start in the order of the item list (longest
+  // first) over all heads, so the last wave holds the shortest items
+  const int* item = args.items + static_cast<size_t>(blockIdx.y) * 4;
   const int entry = item[0], row0 = item[1], split = item[2];
-  const int kv_head = blockIdx.y;
+  const int kv_head = blockIdx.x;
   const int group = args.hq / args.hkv;
   const int tok_begin = args.cu_seqlens[entry];
   const int n_rows = (args.cu_seqlens[entry + 1] - tok_begin) * group;
@@ -508,7 +510,7 @@ int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStrea
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return launch_kernel(kernel, dim3(n_items, args.hkv), dim3(kThreads), smem, stream, pdl, args);
+  return launch_kernel(kernel, dim3(args.hkv, n_items), dim3(kThreads), smem, stream, pdl, args);
 }
 
 }  // namespace RL_ATTENTION_NS
@@ -544,7 +546,7 @@ static int launch_prefill_tc(const AttentionArgs& a, int n_items, bool pdl, cuda
   t.entry_slot = a.entry_slot; t.block_table = a.block_table; t.hq = a.hq; t.hkv = a.hkv;
   t.page_size = a.page_size; t.num_pages = a.num_pages; t.max_pages = a.max_pages; t.slots = a.slots;
   t.window = a.window; t.scale_log2 = a.scale_log2; t.fault = a.fault;
-  return launch_kernel(attention_prefill_tc_kernel, dim3(n_items, a.hkv), dim3(kPfThreads), kPfSmemBytes, stream, pdl,
+  return launch_kernel(attention_prefill_tc_kernel, dim3(a.hkv, n_items), dim3(kPfThreads), kPfSmemBytes, stream, pdl,
                        map, t);
 }
 
@@ -638,7 +640,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
-      hkv > 65535)
+      hkv > 65535 || n_chunk_items > 65535 || n_decode_items > 65535)      // grid y dimensions
     return static_cast<int>(cudaErrorInvalidValue);
   attn::AttentionArgs args;
   args.q = static_cast<const attn::bf16*>(q);

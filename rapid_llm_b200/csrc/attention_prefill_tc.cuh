@@ -86,9 +86,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
   auto v_tile = [&](int s) { return base + (kPfTiles + kPfStages + s) * kPfTileBytes; };
 
   // ---- the item ------------------------------------------------------------------------
-  const int* item = args.items + static_cast<size_t>(blockIdx.x) * 4;
+  // the kv head is the fast grid dimension: CTAs start in the order of the item list (longest
+  // first) over all heads, so the last wave holds the shortest items
+  const int* item = args.items + static_cast<size_t>(blockIdx.y) * 4;
   const int entry = item[0], row0 = item[1];
-  const int kv_head = blockIdx.y;
+  const int kv_head = blockIdx.x;
   const int group = args.hq / args.hkv;
   const int tok_begin = args.cu_seqlens[entry];
   const int n_rows_entry = (args.cu_seqlens[entry + 1] - tok_begin) * group;
