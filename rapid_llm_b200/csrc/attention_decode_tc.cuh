@@ -108,7 +108,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
   auto p_tile = [&](int team, int b) { return q_tile + (1 + team * 2 + b) * kTcOperandBytes; };
 
   // ---- the item ------------------------------------------------------------------------
-  const int* item = args.items + static_cast<size_t>(blockIdx.x) * 4;
+  const int* item = args.items + (static_cast<size_t>(blockIdx.z) * gridDim.x + blockIdx.x) * 4;
   const int entry = item[0], row0 = item[1], split = item[2];
   const int kv_head = blockIdx.y;
   const int group = args.hq / args.hkv;

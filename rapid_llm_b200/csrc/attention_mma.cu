@@ -561,8 +561,12 @@ static int launch_decode_tc_rows(const CUtensorMap& map, const DecodeTcArgs& t, 
     if (e != cudaSuccess) return static_cast<int>(e);
     *configured = true;
   }
+  // x: the key ranges of one tile (a cluster when they merge among themselves), y: the kv head,
+  // z: the tile.  CTAs start in x, y, z order: the tiles of the item list, longest first, over
+  // all heads, so that the last wave holds the shortest.
+  if (t.splits < 1 || n_items % t.splits != 0 || n_items / t.splits > 65535) return static_cast<int>(cudaErrorInvalidValue);
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(n_items, t.hkv);
+  config.gridDim = dim3(t.splits, t.hkv, n_items / t.splits);
   config.blockDim = dim3(kTcThreads);
   config.dynamicSmemBytes = kTcSmemBytes;
   config.stream = stream;
