@@ -27,6 +27,8 @@ TARGET_CTAS = 2 * 148     # work items the attention kernels want in flight on a
 DECODE_TARGET_CTAS = 148  # ... in a decode-only step, whose kernel keeps a whole SM's shared memory busy
 MAX_SPLITS = 16
 CLUSTER_SPLITS = 8        # the portable size of a thread-block cluster
+TC_CHUNK_MIN_CTAS = 32    # measured: from here on the unsplit tcgen05 chunk kernel beats the split mma.sync tiles
+TC_CHUNK_SHORT_CONTEXT = 1024   # ... and below this context it does so with any number of CTAs
 MIN_KEYS_PER_SPLIT = 256
 
 
@@ -74,7 +76,14 @@ class AttentionItems(StepPlanner):
                 # cluster: at most 8 CTAs, and a power of two schedules best
                 splits = 1 << (min(splits, CLUSTER_SPLITS).bit_length() - 1)
             if splits == 1 or chunk_rows == kernels.CHUNK_TILE_ROWS or bool(is_decode.all()):
-                break                  # the tcgen05 chunk kernel does not split key ranges
+                break
+            # The tcgen05 chunk kernel does not split key ranges, but it is several times faster per
+            # key than the mma.sync tiles: it runs unsplit unless it would leave most of the GPU
+            # idle on a long context (a few dozen prompt tokens behind thousands of cached ones).
+            chunk_ctas = int(tiles[~is_decode].sum()) * self.num_kv_heads
+            if chunk_ctas >= TC_CHUNK_MIN_CTAS or longest <= TC_CHUNK_SHORT_CONTEXT:
+                splits = 1
+                break
         entry = np.repeat(np.arange(len(lengths), dtype=np.int64), tiles)
         first = np.concatenate(([0], np.cumsum(tiles)[:-1]))
         tile_index = np.arange(int(tiles.sum()), dtype=np.int64) - np.repeat(first, tiles)

@@ -84,6 +84,15 @@ def test_chunk_tiles_follow_the_kernel_that_will_run():
     late = StepShape(np.asarray([40], dtype=np.int32), np.asarray([6000], dtype=np.int32), False, page_size=16)
     plan = planner.plan(late)
     assert plan["splits"] > 1 and plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS
+    # medium portions, also deep into a context, stay on the tcgen05 kernel, unsplit; so do short
+    # portions of a short context
+    for count, start in [(512, 0), (1024, 3072), (512, 7000), (100, 500), (32, 600)]:
+        plan = planner.plan(StepShape(np.asarray([count], dtype=np.int32), np.asarray([start], dtype=np.int32), False, page_size=16))
+        assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1, (count, start)
+    # a decode token beside such a portion is not split either (one split count per step)
+    mixed = StepShape(np.asarray([700, 1], dtype=np.int32), np.asarray([0, 3000], dtype=np.int32), False, page_size=16)
+    plan = planner.plan(mixed)
+    assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1 and len(plan["decode_items"]) == 1
     # other head sizes or page sizes: the mma.sync tiles
     assert AttentionItems(4, 8, 64).plan(whole)["chunk_rows"] == kernels.CHUNK_TILE_ROWS
     odd = StepShape(np.asarray([2048], dtype=np.int32), np.asarray([0], dtype=np.int32), False, page_size=4)
