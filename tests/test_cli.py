@@ -1,0 +1,51 @@
+"""The command line without a GPU: its options carry the reference's names
+(``rapid_llm/cli.py:57-165,614-701``), ``random-init`` writes a loadable model folder, and an
+option that asks for what is not built ends with a message."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+from tiny_configs import TINY_B
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def run_cli(*args, check=True):
+    done = subprocess.run([sys.executable, "-m", "rapid_llm_b200.cli", *args], cwd=ROOT, capture_output=True, text=True)
+    if check:
+        assert done.returncode == 0, done.stderr
+    return done
+
+
+def test_batch_takes_the_references_options():
+    text = run_cli("batch", "--help").stdout
+    for flag in ("--model-dir", "--max-seq-len", "--max-gpu-num-blocks", "--device", "--temperature", "--top-p",
+                 "--max-gen-len", "--repetition-penalty", "--quantization", "--kv-cache-dtype", "--tensor-parallel-size",
+                 "--prompts-file", "--max-num-seqs", "--show-stats", "--cuda-graph", "--no-cuda-graph"):
+        assert flag in text, flag
+
+
+def test_random_init_writes_a_model_folder(tmp_path):
+    from rapid_llm_b200.config import load_config
+    from rapid_llm_b200.weights import SafetensorsFile
+
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(TINY_B))
+    out = tmp_path / "model"
+    run_cli("random-init", "--config", str(config), "--out", str(out), "--seed", "3", "--dtype", "bfloat16")
+    assert load_config(out).num_hidden_layers == TINY_B["num_hidden_layers"]
+    with SafetensorsFile(out / "model.safetensors") as handle:
+        names = set(handle.keys())
+    assert "model.embed_tokens.weight" in names and "lm_head.weight" in names
+    again = tmp_path / "again"
+    run_cli("random-init", "--config", str(config), "--out", str(again), "--seed", "3", "--dtype", "bfloat16")
+    assert (out / "model.safetensors").read_bytes() == (again / "model.safetensors").read_bytes()      # seeded
+
+
+def test_an_option_for_what_is_not_built_ends_with_a_message(tmp_path):
+    done = run_cli("batch", "--model-dir", str(tmp_path), "--tensor-parallel-size", "2", check=False)
+    assert done.returncode != 0 and "tensor_parallel_size=2" in done.stderr and "Traceback" not in done.stderr
+    missing = run_cli("batch", check=False)
+    assert missing.returncode != 0 and "model-dir" in missing.stderr
