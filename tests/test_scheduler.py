@@ -312,3 +312,52 @@ def test_abort_while_a_step_is_in_flight():
     scheduler.run_to_completion()
     assert b.output_token_ids == [1000, 1001, 1002]
     assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
+
+
+# ------------------------------------------------------------------ random workloads
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("ahead", [False, True])
+def test_random_arrivals_lengths_stops_and_aborts_lose_nothing(seed, ahead):
+    """Requests of random length arrive at random steps into a pool too small for all of them, some
+    stop early on a stop token, some are aborted: every survivor gets exactly its tokens, the model
+    never sees a stand-in id, and when all is done every page and slot is back."""
+    import random
+
+    rng = random.Random(seed)
+    pages = rng.randint(9, 16)
+    maker = make_ahead if ahead else make
+    scheduler, executor = maker(pages=pages, max_seq_len=96, max_num_seqs=3, max_num_batched_tokens=rng.choice([24, 40, 64]),
+                                max_chunk_size=rng.choice([7, 16, 32]))
+    plan = []                                      # (arrival step, prompt length, tokens wanted, stop after, abort at step)
+    for index in range(12):
+        prompt = rng.randint(1, 60)
+        wanted = rng.randint(1, 95 - prompt)
+        stop = rng.randint(0, wanted) if rng.random() < 0.3 else None
+        abort = rng.randint(0, 40) if rng.random() < 0.2 else None
+        plan.append((rng.randint(0, 30), prompt, wanted, stop, abort))
+    requests = {}
+    step = 0
+    while step < 400 and (len(requests) < len(plan) or scheduler.has_unfinished()):
+        for index, (arrival, prompt, wanted, stop, abort) in enumerate(plan):
+            if arrival == step:
+                if stop is not None:
+                    executor.stop_after[index] = stop
+                requests[index] = scheduler.add_request([rng.randrange(100) + 10 for _ in range(prompt)], greedy(wanted), index)
+            if abort == step and index in requests:
+                scheduler.abort(index)
+        if scheduler.has_unfinished():
+            scheduler.step()
+        executor.cache.check()
+        step += 1
+    assert len(requests) == len(plan) and not scheduler.has_unfinished()
+    for index, (arrival, prompt, wanted, stop, abort) in enumerate(plan):
+        request = requests[index]
+        assert all(token >= 0 for token in request.output_token_ids)
+        if request.finish_reason == "abort":
+            continue
+        count = wanted if stop is None else min(wanted, stop)
+        assert request.output_token_ids == [1000 + i for i in range(count)], (index, request.finish_reason)
+        assert request.finish_reason == ("eos" if stop is not None and stop < wanted else "length")
+    if ahead:
+        assert all(token >= 0 for fed in executor.fed for token in fed)
+    assert executor.cache.num_free_pages() == pages and executor.cache.num_free_slots == 3
