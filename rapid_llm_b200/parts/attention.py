@@ -40,9 +40,13 @@ class AttentionItems(StepPlanner):
     the tiles are too few to fill the GPU, each tile's key range is split into ``splits`` parts
     (the same number for the whole step): a function of the number of entries alone in a
     decode-only step, so that a captured decode graph replays the same item list at every
-    context length; bounded by the longest context otherwise.  Chunk tiles have 256 rows for the
-    tcgen05 kernel, which takes head size 128, the usual page sizes and unsplit key ranges, and
-    64 rows for the mma.sync kernel otherwise; the longest tiles come first in the list.
+    context length (a power of two up to 8 where the tcgen05 decode kernel merges the parts inside
+    a thread-block cluster); bounded by the longest context otherwise.  Chunk tiles have 256 rows
+    for the tcgen05 kernel, which takes head size 128, the usual page sizes and unsplit key
+    ranges, and 64 rows for the mma.sync kernel otherwise.  The tcgen05 kernel is several times
+    faster per key, so it also runs, unsplit, where a split would have been wanted, unless its
+    CTAs are few and the context long (a few dozen prompt tokens behind thousands of cached ones).
+    The longest tiles come first in the list, and the kernels' grids start them in that order.
     The reference picks its split size per launch in the same spirit
     (``rapid_llm/kernels/ops/attention/flashdecoding.py:43-112``).
     """
