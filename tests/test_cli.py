@@ -49,3 +49,8 @@ def test_an_option_for_what_is_not_built_ends_with_a_message(tmp_path):
     assert done.returncode != 0 and "tensor_parallel_size=2" in done.stderr and "Traceback" not in done.stderr
     missing = run_cli("batch", check=False)
     assert missing.returncode != 0 and "model-dir" in missing.stderr
+
+
+def test_bench_refuses_more_than_one_gpu_with_one_line():
+    done = subprocess.run([sys.executable, "bench.py", "--gpus", "2"], cwd=ROOT, capture_output=True, text=True)
+    assert done.returncode == 2 and len(done.stdout.strip().splitlines()) == 1 and "single-GPU" in done.stdout
