@@ -222,6 +222,105 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
   }
 }
 
+// Heads of 128 in bfloat16 at many tokens, the whole head rotated, no bias: half a warp per
+// head (a lane holds 8 consecutive elements, its rotation partner sits 8 lanes further), so every
+// warp instruction works on two heads, and the loads of a warp's eight heads fly together.
+__global__ void qk_norm_rope_write_pairs_kernel(const RopeArgs a) {
+  using T = __nv_bfloat16;
+  constexpr int kHeadsPerWarp = 8, kD = 128;
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_per_token = a.kv_dest ? a.hq + 2 * a.hkv : a.hq;
+  const int warps_per_token = (heads_per_token + kHeadsPerWarp - 1) / kHeadsPerWarp;
+  const long long index = static_cast<long long>(blockIdx.x) * kRopeWarps + warp;
+  if (index >= static_cast<long long>(a.tokens) * warps_per_token) {
+    pdl_wait();
+    return;
+  }
+  const int t = static_cast<int>(index / warps_per_token);
+  const int head_begin = static_cast<int>(index - static_cast<long long>(t) * warps_per_token) * kHeadsPerWarp;
+  const int head_end = min(heads_per_token, head_begin + kHeadsPerWarp);
+  int pos = a.positions[t];
+  if (pos < 0 || pos >= a.max_pos) {
+    if (lane == 0 && head_begin < a.hq + a.hkv) atomicOr(a.fault, kFaultPosition);
+    pos = 0;
+  }
+  int page = 0, offset = 0;
+  bool bad_page = false;
+  if (a.kv_dest) {
+    const int dest = a.kv_dest[t];
+    page = dest / a.page_size;
+    offset = dest - page * a.page_size;
+    bad_page = dest < 0 || page >= a.num_pages;
+  }
+  const int side = lane >> 4, at = (lane & 15) * 8;          // which head of the pair; first element
+  const int angle = at & 63;
+  float c[8], s[8], qw[8], kw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    c[i] = a.cos_table[static_cast<size_t>(pos) * 64 + angle + i];
+    s[i] = a.sin_table[static_cast<size_t>(pos) * 64 + angle + i];
+    qw[i] = a.q_weight ? a.q_weight[at + i] : 1.0f;
+    kw[i] = a.k_weight ? a.k_weight[at + i] : 1.0f;
+  }
+  pdl_wait();
+  const T* row = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width;
+  uint4 raw[kHeadsPerWarp / 2];
+#pragma unroll
+  for (int pair = 0; pair < kHeadsPerWarp / 2; ++pair) {
+    const int head = head_begin + 2 * pair + side;
+    raw[pair] = make_uint4(0, 0, 0, 0);
+    if (head < head_end) raw[pair] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(head) * kD + at);
+  }
+#pragma unroll
+  for (int pair = 0; pair < kHeadsPerWarp / 2; ++pair) {
+    const int head = head_begin + 2 * pair + side;
+    const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // q, k, v
+    const __nv_bfloat162* packed = reinterpret_cast<const __nv_bfloat162*>(&raw[pair]);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 two = __bfloat1622float2(packed[i]);
+      v[2 * i] = two.x;
+      v[2 * i + 1] = two.y;
+    }
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum_sq += v[i] * v[i];
+#pragma unroll
+    for (int step = 8; step > 0; step >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, step);   // within 16 lanes
+    const bool normed = kind == 0 ? a.q_weight != nullptr : (kind == 1 && a.k_weight != nullptr);
+    const float inv_rms = normed ? rsqrtf(sum_sq / static_cast<float>(kD) + a.eps) : 1.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float scaled = v[i] * inv_rms * (kind == 0 ? qw[i] : kw[i]);
+      const float mine = normed ? scaled : v[i];
+      const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+      // first half of the head: x1 * c - x2 * s; second half: x2 * c + x1 * s; values pass through
+      const float turned = (lane & 8) ? mine * c[i] + other * s[i] : mine * c[i] - other * s[i];
+      v[i] = kind == 2 ? v[i] : turned;
+    }
+    if (head >= head_end) continue;
+    T* dst;
+    if (kind == 0) {
+      dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * kD;
+    } else {
+      if (bad_page) {
+        if ((lane & 15) == 0) atomicOr(a.fault, kFaultPageId);
+        continue;
+      }
+      const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+      dst = static_cast<T*>(a.cache) +
+            ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * kD;
+    }
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst + at) = out;
+  }
+}
+
 }  // namespace rl
 
 extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, const float* bias,
@@ -252,6 +351,8 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
     heads_per_warp = 8;
   const long long warps = static_cast<long long>(tokens) * ((heads_per_token + heads_per_warp - 1) / heads_per_warp);
   const dim3 grid(static_cast<unsigned>((warps + rl::kRopeWarps - 1) / rl::kRopeWarps)), block(rl::kRopeWarps * 32);
+  if (heads_per_warp == 8 && d == 128 && vec == 4 && bias == nullptr && dtype == rl::kBF16)
+    return rl::launch_kernel(rl::qk_norm_rope_write_pairs_kernel, grid, block, 0, stream, pdl != 0, a);
   RL_DISPATCH_DTYPE(dtype, {
     if (vec == 8) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 8>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
     if (vec == 4) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 4>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);
