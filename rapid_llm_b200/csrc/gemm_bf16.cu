@@ -21,6 +21,14 @@
 // stores it.  No global scratch, no atomics.  With many tokens the k-range is not split and a
 // CTA walks several tiles, the epilogue of one overlapping the products of the next.
 //
+// A norm between two products can ride on them instead of being a kernel of its own (steps of up
+// to 64 tokens).  The product before it adds its float32 result to the residual row, stores the
+// sum back, writes the sum times the norm's weight as the next product's input and leaves the
+// sums of squares per token and 32 output columns in a small table; the product after it adds
+// the table's row up (in a fixed order) and multiplies its own result by rsqrt(mean + eps): a
+// row's scale commutes with the product.  The residual add, the squares and the scale are float32
+// (formula: rapid_llm/kernels/ops/layernorm/skip_rmsnorm.py:41-48).
+//
 // Launched with programmatic stream serialization, the kernel starts while its predecessor
 // in the stream drains: barriers, tensor memory and the first weight tiles (which no kernel
 // writes) are set up and in flight before griddepcontrol.wait lets it read the activations.
@@ -49,10 +57,29 @@ struct GemmArgs {
   int n_tiles, t_tiles, k_blocks;
   int k_split;             // CTAs (= cluster size) that share one tile's k-range
   int pdl;                 // launched with programmatic stream serialization
+  // a norm that follows this product (plain products of one token tile only; all three or none):
+  // residual[T, N] += result; out = bf16(residual * norm_weight[n]); sumsq_out[t, 4 * n_tiles] gets the
+  // squares of the new residual summed over each tile's four groups of 32 columns
+  float* residual;
+  const float* norm_weight;
+  float* sumsq_out;
+  // a norm that came before it and left its scale open (one token tile only): the result of row t is
+  // multiplied by rsqrt(sum(sumsq_in[t, 0:sumsq_count]) * inv_norm_size + norm_eps)
+  const float* sumsq_in;
+  int sumsq_count;
+  float norm_eps, inv_norm_size;
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
   return __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16
+}
+
+// One element of a product that a norm follows: the residual takes the sum, the output the sum times
+// the norm's weight; returns the sum's square for the row's mean.
+__device__ __forceinline__ float store_for_norm(const GemmArgs& args, size_t at, float norm_w, float sum) {
+  args.residual[at] = sum;
+  args.out[at] = __float2bfloat16_rn(sum * norm_w);
+  return sum * sum;
 }
 
 template <bool kSwiglu, int BN>
@@ -93,6 +120,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full_bar[2], acc_empty_bar[2], drain_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int aborted_flag;
+  __shared__ float row_scale[BN <= 64 ? BN : 1];      // the scale an earlier norm left open, per token
   volatile int* aborted = &aborted_flag;
 
   if (args.pdl && threadIdx.x == 0) pdl_trigger();   // the successor may set itself up beside this kernel
@@ -238,6 +266,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     uint32_t acc_phase[2] = {0, 0};
     bool ok = kb_count > 0;
     if (args.pdl) pdl_wait();                           // the output buffer may still be read upstream
+    if constexpr (BN <= 64) {
+      if (args.sumsq_in != nullptr) {
+        // 128 / BN neighbouring threads add up a token's row of the table (always in the same order)
+        // while the first products run
+        constexpr int kPerToken = 128 / BN;
+        const int token = (static_cast<int>(threadIdx.x) - 64) / kPerToken;
+        const int sub = (static_cast<int>(threadIdx.x) - 64) % kPerToken;
+        float sum = 0.0f;
+        if (token < args.T) {
+          const float4* row = reinterpret_cast<const float4*>(args.sumsq_in + static_cast<size_t>(token) * args.sumsq_count);
+#pragma unroll 8
+          for (int p = sub; p < args.sumsq_count / 4; p += kPerToken) {
+            const float4 four = row[p];
+            sum += (four.x + four.y) + (four.z + four.w);
+          }
+        }
+#pragma unroll
+        for (int offset = kPerToken / 2; offset >= 1; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        if (sub == 0) row_scale[token] = token < args.T ? rsqrtf(sum * args.inv_norm_size + args.norm_eps) : 1.0f;
+        named_barrier(1, 128);
+      }
+    }
+    const bool scaled = BN <= 64 && args.sumsq_in != nullptr;
     for (int index = 0; index < my_tiles && ok; ++index) {
       const int tile = tile_of(index);
       const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
@@ -252,13 +303,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (t0 + c >= args.T) break;
           float v[16];
           tmem_load16(acc + c, v);
+          if (scaled) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= row_scale[c + j];
+          }
           if (kSwiglu) {
             float u[16];
             tmem_load16(acc + BN + c, u);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], u[j]);
+            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], scaled ? u[j] * row_scale[c + j] : u[j]);
           }
-          if (n < args.N) {
+          if (!kSwiglu && args.residual != nullptr) {
+            const float norm_w = n < args.N ? args.norm_weight[n] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;                 // the same for the whole warp
+              if (t < args.T) {
+                const size_t at = static_cast<size_t>(t) * args.N + n;
+                const float sq = warp_sum(n < args.N ? store_for_norm(args, at, norm_w, args.residual[at] + v[j]) : 0.0f);
+                if (lane == 0) args.sumsq_out[static_cast<size_t>(t) * (4 * args.n_tiles) + 4 * n_tile + quarter] = sq;
+              }
+            }
+          } else if (n < args.N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (t0 + c + j < args.T)
@@ -298,10 +364,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       uint32_t peer[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) peer[q] = q < args.k_split ? peer_smem(smem_base + n_local * 4, q) : 0u;
+      const bool scaled = BN <= 64 && args.sumsq_in != nullptr;
+      const bool norm_follows = !kSwiglu && args.residual != nullptr;
+      const float norm_w = norm_follows && n < args.N ? args.norm_weight[n] : 0.0f;
       for (int j = rank; j < BN && t0 + j < args.T; j += args.k_split) {
         // all loads first, the sums (in rank order) after: a remote load takes hundreds of cycles,
         // and a warp that adds each value as it arrives pays that once per rank
         float gate_part[8], up_part[8];
+        const size_t at = static_cast<size_t>(t0 + j) * args.N + n;
+        const float before = norm_follows && n < args.N ? args.residual[at] : 0.0f;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           gate_part[q] = q < args.k_split ? load_peer_f32(peer[q] + j * kTileN * 4) : 0.0f;
@@ -315,9 +386,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             up += up_part[q];
           }
         }
-        if (n < args.N)
-          args.out[static_cast<size_t>(t0 + j) * args.N + n] =
-              __float2bfloat16_rn(kSwiglu ? silu_mul(gate, up) : gate);
+        if (scaled) {
+          gate *= row_scale[j];
+          up *= row_scale[j];
+        }
+        if (norm_follows) {
+          const float sq = warp_sum(n < args.N ? store_for_norm(args, at, norm_w, before + gate) : 0.0f);
+          if (lane == 0)
+            args.sumsq_out[static_cast<size_t>(t0 + j) * (4 * args.n_tiles) + 4 * n_tile + (warp & 3)] = sq;
+        } else if (n < args.N) {
+          args.out[at] = __float2bfloat16_rn(kSwiglu ? silu_mul(gate, up) : gate);
+        }
       }
     }
     __syncwarp();
@@ -418,11 +497,25 @@ extern "C" {
 // programmatic stream serialization (the previous kernel of the stream must then be one that
 // tolerates an early successor; every kernel of this library does).  `k_split` forces the
 // number of CTAs per tile (0 = choose).
-int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
-                 int k_split, int* fault, cudaStream_t stream) {
+//
+// A norm that follows (`residual`, `norm_weight`, `sumsq_out`: all or none; float32; plain products of
+// at most 64 tokens): residual[tokens, n_out] += result, out = residual * norm_weight, and
+// sumsq_out[tokens, rl_gemm_bf16_sumsq_count(n_out)] receives partial sums of the new residual's squares.
+// A norm that came before (`sumsq_in[tokens, sumsq_count]`, at most 64 tokens): row t of the result is
+// multiplied by rsqrt(sum(sumsq_in[t]) / norm_size + norm_eps).
+int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
+                      int k_split, float* residual, const float* norm_weight, float* sumsq_out,
+                      const float* sumsq_in, int sumsq_count, float norm_eps, int norm_size, int* fault,
+                      cudaStream_t stream) {
   if (tokens == 0 || n_out == 0) return 0;
   if (tokens < 0 || n_out < 0 || k <= 0 || k % 8 != 0 || k_split < 0 || k_split > 8 ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  const bool norm_follows = residual != nullptr || norm_weight != nullptr || sumsq_out != nullptr;
+  if (norm_follows && (residual == nullptr || norm_weight == nullptr || sumsq_out == nullptr || swiglu != 0 || tokens > 64))
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (sumsq_in != nullptr && (tokens > 64 || sumsq_count <= 0 || sumsq_count % 4 != 0 || norm_size <= 0 ||
+                              (reinterpret_cast<uintptr_t>(sumsq_in) & 15)))
     return static_cast<int>(cudaErrorInvalidValue);
   const int bn = rl::token_tile(tokens, swiglu != 0);
   CUtensorMap map_w, map_x;
@@ -440,6 +533,13 @@ int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out,
   args.k_blocks = (k + rl::kTileK - 1) / rl::kTileK;
   args.k_split = 1;
   args.pdl = pdl;
+  args.residual = residual;
+  args.norm_weight = norm_weight;
+  args.sumsq_out = sumsq_out;
+  args.sumsq_in = sumsq_in;
+  args.sumsq_count = sumsq_count;
+  args.norm_eps = norm_eps;
+  args.inv_norm_size = norm_size > 0 ? 1.0f / static_cast<float>(norm_size) : 0.0f;
 #define RL_GEMM_CASE(SW, BNV) \
   if ((swiglu != 0) == SW && bn == BNV) return rl::launch_gemm<SW, BNV>(map_w, map_x, args, k_split, stream);
   RL_GEMM_CASE(false, 16) RL_GEMM_CASE(false, 32) RL_GEMM_CASE(false, 64) RL_GEMM_CASE(false, 128)
@@ -448,5 +548,14 @@ int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out,
 #undef RL_GEMM_CASE
   return static_cast<int>(cudaErrorInvalidValue);
 }
+
+int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
+                 int k_split, int* fault, cudaStream_t stream) {
+  return rl_gemm_bf16_norm(x, w, out, tokens, n_out, k, swiglu, pdl, k_split, nullptr, nullptr, nullptr, nullptr, 0,
+                           0.0f, 0, fault, stream);
+}
+
+// columns of the table of partial sums of squares that a product of `n_out` output columns writes per token
+int rl_gemm_bf16_sumsq_count(int n_out) { return 4 * ((n_out + rl::kTileN - 1) / rl::kTileN); }
 
 }  // extern "C"

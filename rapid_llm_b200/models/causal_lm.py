@@ -87,8 +87,11 @@ class CausalLM:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""
         x = self.embedding.forward(batch)
         residual = None
-        for position, entry in enumerate(self.spec.schedule):
-            x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position])
+        schedule = self.spec.schedule
+        for position, entry in enumerate(schedule):
+            # the norm that the next layer starts with may ride on this layer's last product
+            after = self.layers[schedule[position + 1].layer].leading_norm() if position + 1 < len(schedule) else None
+            x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position], then_norm=after)
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=self.dtype, device=self.device)
         if residual is None:

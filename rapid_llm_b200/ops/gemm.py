@@ -7,9 +7,16 @@ the library product (cuBLAS through ``torch.mm``), which is where the reference'
 uses a library as well (``rapid_llm/kernels/ops/gemm/linear.py:17-40``) and is still the
 faster of the two at thousands of tokens.  ``FORCE`` pins one of the two for tests and
 measurements.
+
+A weight-only RMS norm between two tensor-core products rides on them instead of running as a
+kernel of its own (:class:`FollowingNorm` into the product before it, :class:`ScaledRows` out
+of it and into the product after it); ``FUSE_NORMS`` switches that off.
 """
 
 from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
 
 import torch
 
@@ -17,6 +24,45 @@ from . import kernels
 
 TENSOR_CORE_MAX_TOKENS = 64
 FORCE: str | None = None      # "tcgen05", "library" or None (choose by size)
+FUSE_NORMS = True             # let a norm between two tensor-core products ride on them
+
+
+@dataclass
+class FollowingNorm:
+    """A norm ``y = r * rsqrt(mean(r^2) + eps) * weight`` of ``r = residual + (a product's result)``,
+    offered to that product: ``residual`` (float32, updated in place) and the norm's float32 ``weight``;
+    ``workspace`` lends the buffers of the result."""
+
+    residual: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    workspace: Any
+
+
+@dataclass
+class ScaledRows:
+    """Rows of a norm's result that still lack their scale: ``rows[t] = r[t] * weight`` and the true
+    row is ``rows[t] * rsqrt(sum(sumsq[t]) / size + eps)``.  A product of these rows multiplies its
+    own result by the scale instead (float32), which is the same up to rounding."""
+
+    rows: torch.Tensor
+    sumsq: torch.Tensor
+    eps: float
+    size: int
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+
+def _open_scale(x) -> tuple[torch.Tensor, dict]:
+    if isinstance(x, ScaledRows):
+        return x.rows, {"sumsq_in": x.sumsq, "norm_eps": x.eps, "norm_size": x.size}
+    return x, {}
 
 
 def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -27,8 +73,15 @@ def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.shape[0] <= TENSOR_CORE_MAX_TOKENS
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[T, N] = x[T, K] @ weight[N, K]^T``; all three on the GPU, same dtype."""
+def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | None = None, *,
+           then_norm: FollowingNorm | None = None):
+    """``out[T, N] = x[T, K] @ weight[N, K]^T``; all three on the GPU, same dtype.
+
+    ``x`` may be :class:`ScaledRows`.  With ``then_norm`` the product may take the norm along:
+    it then returns :class:`ScaledRows` (the residual is updated, ``out`` is not written);
+    otherwise it returns ``out`` and the caller runs the norm.
+    """
+    x, scale = _open_scale(x)
     if not x.is_cuda:
         raise kernels.KernelError("linear: tensors must live on a CUDA device; there is no CPU path")
     if x.dtype != weight.dtype or out.dtype != x.dtype:
@@ -38,19 +91,32 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, fault: torc
     if x.shape[0] == 0:
         return out
     if fault is not None and use_tensor_core_kernel(x, weight):
-        return kernels.gemm_bf16(x, weight, out, fault)
+        rows, width = out.shape
+        if (then_norm is not None and FUSE_NORMS and rows <= kernels.GEMM_NORM_MAX_TOKENS and width % 8 == 0
+                and rows <= TENSOR_CORE_MAX_TOKENS):
+            normed = then_norm.workspace.get("normed", rows, width, x.dtype)
+            sumsq = then_norm.workspace.get("normed_sumsq", rows, kernels.gemm_bf16_sumsq_count(width), torch.float32)
+            kernels.gemm_bf16(x, weight, normed, fault, residual=then_norm.residual, norm_weight=then_norm.weight,
+                              sumsq_out=sumsq, **scale)
+            return ScaledRows(normed, sumsq, then_norm.eps, width)
+        return kernels.gemm_bf16(x, weight, out, fault, **scale)
+    if scale:
+        raise kernels.KernelError("linear: rows with an open scale need the tensor-core product")
     torch.mm(x, weight.t(), out=out)
     return out
 
 
-def gated_linear(x: torch.Tensor, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor) -> torch.Tensor:
+def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor) -> torch.Tensor:
     """``act = silu(x @ gate^T) * (x @ up^T)`` for a ``[2 I, K]`` weight with the gate rows first.
 
     One fused tensor-core kernel where it applies; otherwise the product into a ``[T, 2 I]``
-    buffer from ``workspace`` followed by the SiLU-multiply kernel.
+    buffer from ``workspace`` followed by the SiLU-multiply kernel.  ``x`` may be :class:`ScaledRows`.
     """
+    x, scale = _open_scale(x)
     if use_tensor_core_kernel(x, gate_up):
-        return kernels.gemm_bf16(x, gate_up, act, fault, swiglu=True)
+        return kernels.gemm_bf16(x, gate_up, act, fault, swiglu=True, **scale)
+    if scale:
+        raise kernels.KernelError("gated_linear: rows with an open scale need the tensor-core product")
     wide = workspace.get("ffn_gate_up", x.shape[0], gate_up.shape[0], x.dtype)
     linear(x, gate_up, wide, fault)
     return kernels.silu_mul(wide, act)

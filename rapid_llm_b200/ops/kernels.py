@@ -459,6 +459,12 @@ def gemm_lib() -> ctypes.CDLL:
         lib.rl_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_void_p, c_void_p]
         lib.rl_gemm_bf16.restype = c_int
+        lib.rl_gemm_bf16_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, ctypes.c_float, c_int,
+                                          c_void_p, c_void_p]
+        lib.rl_gemm_bf16_norm.restype = c_int
+        lib.rl_gemm_bf16_sumsq_count.argtypes = [c_int]
+        lib.rl_gemm_bf16_sumsq_count.restype = c_int
         _GEMM_LIB = lib
     return _GEMM_LIB
 
@@ -468,15 +474,33 @@ def gemm_bf16_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
+GEMM_NORM_MAX_TOKENS = 64   # most rows of a product that carries a norm's add or a norm's open scale
+
+
+def gemm_bf16_sumsq_count(n_out: int) -> int:
+    """Columns of the table of partial sums of squares that a product of ``n_out`` columns writes."""
+    return int(gemm_lib().rl_gemm_bf16_sumsq_count(int(n_out)))
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor, *, swiglu: bool = False,
-              k_split: int = 0) -> torch.Tensor:
+              k_split: int = 0, residual: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+              sumsq_out: torch.Tensor | None = None, sumsq_in: torch.Tensor | None = None,
+              norm_eps: float = 0.0, norm_size: int = 0) -> torch.Tensor:
     """``out[T, N] = x[T, K] @ w[N, K]^T`` in bfloat16 on the tcgen05 tensor cores.
 
     With ``swiglu``, ``w`` is ``[2 N, K]`` (gate rows, then up rows) and
     ``out = silu(x @ gate^T) * (x @ up^T)`` without the ``[T, 2 N]`` intermediate.
     ``k_split`` forces how many CTAs share a tile's inner range (0 = the kernel chooses).
+
+    A norm between two products rides on them (at most :data:`GEMM_NORM_MAX_TOKENS` rows).
+    With ``residual`` (float32 ``[T, N]``), ``norm_weight`` (float32 ``[N]``) and ``sumsq_out``
+    (float32 ``[T, gemm_bf16_sumsq_count(N)]``) the product is added to ``residual`` in place,
+    ``out = residual * norm_weight`` and ``sumsq_out`` receives partial sums of the new
+    residual's squares.  With ``sumsq_in`` (such a table), ``norm_eps`` and ``norm_size``, row
+    ``t`` of the product is multiplied by ``rsqrt(sum(sumsq_in[t]) / norm_size + norm_eps)``
+    (before the SiLU): the scale that the norm before ``x`` left open.
     """
-    _need_cuda(x, w, out, fault)
+    _need_cuda(x, w, out, fault, residual, norm_weight, sumsq_out, sumsq_in)
     for name, tensor in (("x", x), ("w", w), ("out", out)):
         _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
     tokens, k = x.shape
@@ -485,11 +509,30 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
         raise KernelError(f"gemm_bf16: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
     if not gemm_bf16_supports(x, w):
         raise KernelError("gemm_bf16: the inner size must be a multiple of 8 and the operands 16-byte aligned")
+    norm_follows = residual is not None or norm_weight is not None or sumsq_out is not None
+    if norm_follows:
+        if residual is None or norm_weight is None or sumsq_out is None or swiglu:
+            raise KernelError("gemm_bf16: a following norm needs residual, norm_weight and sumsq_out, and no swiglu")
+        for name, tensor in (("residual", residual), ("norm_weight", norm_weight), ("sumsq_out", sumsq_out)):
+            _expect(name, tensor, torch.float32), _contig(name, tensor)
+        if (residual.shape != (tokens, n_out) or norm_weight.shape != (n_out,)
+                or sumsq_out.shape != (tokens, gemm_bf16_sumsq_count(n_out))):
+            raise KernelError("gemm_bf16: residual, norm_weight or sumsq_out do not have the product's shape")
+    if sumsq_in is not None:
+        _expect("sumsq_in", sumsq_in, torch.float32), _contig("sumsq_in", sumsq_in)
+        if sumsq_in.dim() != 2 or sumsq_in.shape[0] != tokens or sumsq_in.shape[1] % 4 or norm_size <= 0:
+            raise KernelError("gemm_bf16: sumsq_in must be [tokens, a multiple of 4] and norm_size positive")
+    if (norm_follows or sumsq_in is not None) and tokens > GEMM_NORM_MAX_TOKENS:
+        raise KernelError(f"gemm_bf16: a norm rides on products of at most {GEMM_NORM_MAX_TOKENS} rows, got {tokens}")
     if tokens == 0:
         return out
     _check(
-        gemm_lib().rl_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL),
-                                int(k_split), _ptr(fault), _stream()),
+        gemm_lib().rl_gemm_bf16_norm(
+            _ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL), int(k_split),
+            _ptr(residual), _ptr(norm_weight), _ptr(sumsq_out),
+            _ptr(sumsq_in), 0 if sumsq_in is None else sumsq_in.shape[1], float(norm_eps), int(norm_size),
+            _ptr(fault), _stream(),
+        ),
         f"gemm_bf16({tokens}x{k} by {n_out})",
     )
     return out

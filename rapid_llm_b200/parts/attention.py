@@ -113,6 +113,8 @@ class AttentionItems(StepPlanner):
 
 @MIXERS.register("gqa_attention")
 class GQAAttention(Mixer):
+    rides_norms = True
+
     def __init__(
         self,
         *,
@@ -200,7 +202,7 @@ class GQAAttention(Mixer):
         return total
 
     # -- forward --------------------------------------------------------------- #
-    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+    def forward(self, x, batch, cache, then_norm=None):
         if cache.group is None or cache.pages is None:
             raise ValueError("attention needs a cache group; the engine did not give this layer one")
         if cache.writes == self.shares_cache:
@@ -223,7 +225,7 @@ class GQAAttention(Mixer):
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
-        return gemm.linear(attended, self.o, out, batch.fault)
+        return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm)
 
     def attend(self, q, pages, out, batch, group) -> None:
         if q.dtype == torch.bfloat16:

@@ -143,6 +143,13 @@ class Part:
 
 
 class Mixer(Part):
+    # A mixer or feed-forward with ``rides_norms`` takes the norm's unscaled result as ``x``
+    # (``ops.gemm.ScaledRows``, which its first product resolves) and an extra keyword
+    # ``then_norm`` (``ops.gemm.FollowingNorm`` or ``None``): the norm after it, which its last
+    # product may take along, returning ``ScaledRows`` instead of a tensor.  Without the flag a
+    # part sees plain tensors only.
+    rides_norms = False
+
     def cache_need(self) -> CacheNeed | None:
         return None
 
@@ -157,6 +164,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    rides_norms = False      # as for a mixer
+
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
         raise NotImplementedError
 
@@ -164,6 +173,11 @@ class FeedForward(Part):
 class Norm(Part):
     def forward(self, x, residual, batch, *, mode: int, write_residual: bool, row_index=None, name="normed"):
         raise NotImplementedError
+
+    def following(self, residual, batch):
+        """This norm of ``residual + (a product's result)`` as an offer to that product
+        (``ops.gemm.FollowingNorm``), or ``None`` if it only runs as a kernel of its own."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -181,7 +195,14 @@ class Block(Part):
     def step_planners(self) -> list[StepPlanner]:
         return []
 
-    def forward(self, x, residual, batch, cache):
+    def leading_norm(self) -> "Norm | None":
+        """The norm this block starts with, if the block takes its unscaled result
+        (``ops.gemm.ScaledRows``) as ``x`` from the block before it."""
+        return None
+
+    def forward(self, x, residual, batch, cache, then_norm=None):
+        """``then_norm``: the next block's :meth:`leading_norm`, which this block's last product may
+        take along (it then returns ``ScaledRows`` as ``x`` and the residual already holds the sum)."""
         raise NotImplementedError
 
 

@@ -4,6 +4,11 @@
 the next norm, so a pair ``(x, residual)`` is threaded through the stack
 (``rapid_llm/models/base.py:231-266,372-375``): ``residual`` is ``None`` entering the first
 layer; the norm kernel forms ``x + residual`` in float32, stores it back and norms it.
+
+Where the parts on both sides of a norm can take it along (``rides_norms``: the product before
+it adds to the residual and applies the norm's weight, the product after it applies the row's
+scale), the norm is offered to them and no norm kernel runs; the parts decide step by step
+whether they accept (small steps in bfloat16 do).
 """
 
 from __future__ import annotations
@@ -11,6 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import LayerSpec
+from ..ops.gemm import ScaledRows
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, TensorSpec
 from .norm import ADD, FIRST
 
@@ -74,13 +80,28 @@ class PreNormBlock(Block):
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for _, part in self._children())
 
-    def forward(self, x, residual, batch, cache):
+    def leading_norm(self):
+        return self.mixer_norm if self.mixer.rides_norms else None
+
+    def forward(self, x, residual, batch, cache, then_norm=None):
         """``(x, residual)`` in, ``(x, residual)`` out; ``residual`` is ``None`` for the first layer."""
-        if residual is None:
+        if isinstance(x, ScaledRows):
+            normed = x          # the block before took this block's first norm along
+        elif residual is None:
             residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
             normed = self.mixer_norm.forward(x, residual, batch, mode=FIRST, write_residual=True)
         else:
             normed = self.mixer_norm.forward(x, residual, batch, mode=ADD, write_residual=True)
-        mixed = self.mixer.forward(normed, batch, cache)
-        normed = self.feed_forward_norm.forward(mixed, residual, batch, mode=ADD, write_residual=True)
+        if self.mixer.rides_norms:
+            offer = self.feed_forward_norm.following(residual, batch) if self.feed_forward.rides_norms else None
+            mixed = self.mixer.forward(normed, batch, cache, then_norm=offer)
+        else:
+            mixed = self.mixer.forward(normed, batch, cache)
+        if isinstance(mixed, ScaledRows):
+            normed = mixed
+        else:
+            normed = self.feed_forward_norm.forward(mixed, residual, batch, mode=ADD, write_residual=True)
+        if self.feed_forward.rides_norms:
+            offer = then_norm.following(residual, batch) if then_norm is not None else None
+            return self.feed_forward.forward(normed, batch, then_norm=offer), residual
         return self.feed_forward.forward(normed, batch), residual

@@ -16,6 +16,8 @@ from .base import FEED_FORWARDS, MATRIX, FeedForward, TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    rides_norms = True
+
     def __init__(self, *, hidden_size: int, intermediate_size: int, dtype, device,
                  gate_name: str = "gate_proj", up_name: str = "up_proj", down_name: str = "down_proj") -> None:
         super().__init__(dtype=dtype, device=device)
@@ -46,9 +48,9 @@ class SwiGLU(FeedForward):
     def parameter_bytes(self) -> int:
         return (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
 
-    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+    def forward(self, x, batch, then_norm=None):
         rows = x.shape[0]
         act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)
         gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault)
         out = batch.workspace.get("ffn_out", rows, self.hidden, x.dtype)
-        return gemm.linear(act, self.down, out, batch.fault)
+        return gemm.linear(act, self.down, out, batch.fault, then_norm=then_norm)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import kernels
+from ..ops import gemm, kernels
 from .base import NORMS, VECTOR, Norm, TensorSpec
 
 FIRST, ADD, PLAIN = 0, 1, 2
@@ -34,6 +34,12 @@ class RMSNorm(Norm):
 
     def parameter_bytes(self) -> int:
         return self.weight.numel() * 4
+
+    def following(self, residual: torch.Tensor, batch) -> gemm.FollowingNorm | None:
+        """This norm of ``residual + (a product's result)``, as an offer to that product."""
+        if self.dtype != torch.bfloat16 or residual is None:
+            return None
+        return gemm.FollowingNorm(residual, self.weight, self.eps, batch.workspace)
 
     def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed"):
         """Norm of ``x`` (``FIRST``/``PLAIN``) or of ``x + residual`` (``ADD``).

@@ -154,6 +154,42 @@ def test_long_decoding(dtype, models):
     compare(rows, {"d": forward_logits(config, weights, tokens)}, dtype)
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_norms_ride_on_the_products_of_small_steps(name, models, monkeypatch):
+    """In bfloat16 steps of up to 64 tokens only the first and the last norm run as kernels; the
+    others are taken along by the products around them.  Both ways give the plain implementation's
+    logits, and larger steps keep the norm kernels."""
+    from rapid_llm_b200.ops import gemm, kernels
+
+    dirs, plains = models["bfloat16"]
+    config, weights = plains[name]
+    layers = config["num_hidden_layers"]
+    tokens = random_tokens(config["vocab_size"], 90, 77)
+    plain = forward_logits(config, weights, tokens)
+    calls = []
+    real = kernels.add_rmsnorm
+    monkeypatch.setattr(kernels, "add_rmsnorm", lambda *a, **k: (calls.append(a[0].shape[0]), real(*a, **k))[1])
+    results = {}
+    for fused in (True, False):
+        monkeypatch.setattr(gemm, "FUSE_NORMS", fused)
+        runner = make_runner(dirs[name], "bfloat16", max_tokens=128, page_size=PAGE_SIZES[name])
+        records = portions("n", tokens, [70, 9, 1, 1, 2, 7])      # a large step, then small ones
+        calls.clear()
+        outputs = replay(runner, records)
+        per_step = 2 * layers + 1
+        large = [rows for rows in calls if rows > 64]
+        assert len(large) == per_step - 1 or len(large) == per_step    # the last norm sees the wanted rows only
+        small_steps = len(records) - 1
+        small = len(calls) - per_step
+        assert small == (2 if fused else per_step) * small_steps, (fused, calls)
+        rows = collect(records, outputs)
+        compare(rows, {"n": plain}, "bfloat16")
+        results[fused] = rows["n"]
+    tolerance = for_dtype("bfloat16")
+    for position, got in results[True].items():
+        torch.testing.assert_close(got, results[False][position], **tolerance)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_steps_that_nobody_waits_for(dtype, models):
     """Portions that want no logits are never read back, so the host prepares several steps

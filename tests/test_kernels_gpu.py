@@ -189,6 +189,61 @@ def test_gemm_bf16_under_programmatic_dependent_launch():
     torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("pdl", [False, True])
+@pytest.mark.parametrize("split", [0, 1, 2, 8])
+@pytest.mark.parametrize("swiglu_after", [False, True])
+@pytest.mark.parametrize("t,k_,width,n_after", [(1, 64, 128, 128), (5, 200, 328, 136), (8, 4096, 1024, 256),
+                                                (33, 1000, 520, 100), (64, 264, 96, 384)])
+def test_gemm_bf16_takes_a_norm_along(t, k_, width, n_after, swiglu_after, split, pdl):
+    """A product that adds to the residual, applies the norm's weight and leaves the squares, then
+    a product that applies the row's scale: together ``norm(residual + x W^T) W2^T``."""
+    kernels = k()
+    eps = 3e-5
+    x = rand((t, k_), torch.bfloat16, seed=30).to(DEV)
+    w = rand((width, k_), torch.bfloat16, scale=0.05, seed=31).to(DEV)
+    w_after = rand(((2 if swiglu_after else 1) * n_after, width), torch.bfloat16, scale=0.05, seed=32).to(DEV)
+    residual = rand((t, width), torch.float32, scale=2.0, seed=33).to(DEV)
+    norm_weight = (1.0 + rand((width,), torch.float32, scale=0.2, seed=34)).to(DEV)
+    # one row far larger than the others: a scale taken from the wrong row shows
+    residual[t // 2] *= 30.0
+    want_residual = residual + x.float() @ w.float().T
+    want_normed = rms_norm(want_residual, norm_weight, eps)
+    want = bf16_product(want_normed, w_after, n_after, swiglu_after)
+
+    fault = fault_word()
+    rows = torch.full((t, width), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sumsq = torch.full((t, kernels.gemm_bf16_sumsq_count(width)), float("nan"), dtype=torch.float32, device=DEV)
+    out = torch.full((t, n_after), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.PDL = pdl
+    try:
+        kernels.gemm_bf16(x, w, rows, fault, k_split=split, residual=residual, norm_weight=norm_weight, sumsq_out=sumsq)
+        kernels.gemm_bf16(rows, w_after, out, fault, swiglu=swiglu_after, k_split=split,
+                          sumsq_in=sumsq, norm_eps=eps, norm_size=width)
+    finally:
+        kernels.PDL = False
+    assert fault.item() == 0
+    torch.testing.assert_close(residual, want_residual, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(sumsq.sum(dim=1), want_residual.square().sum(dim=1), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(rows.float(), want_residual * norm_weight, rtol=1e-2, atol=1e-3)
+    torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
+
+
+def test_gemm_bf16_norm_refusals():
+    kernels = k()
+    x = torch.zeros((65, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((128, 64), dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros((65, 128), dtype=torch.bfloat16, device=DEV)
+    residual = torch.zeros((65, 128), dtype=torch.float32, device=DEV)
+    weight = torch.ones((128,), dtype=torch.float32, device=DEV)
+    sumsq = torch.zeros((65, 4), dtype=torch.float32, device=DEV)
+    with pytest.raises(kernels.KernelError, match="at most 64"):
+        kernels.gemm_bf16(x, w, out, fault_word(), residual=residual, norm_weight=weight, sumsq_out=sumsq)
+    with pytest.raises(kernels.KernelError, match="needs residual"):
+        kernels.gemm_bf16(x[:8], w, out[:8], fault_word(), residual=residual[:8])
+    with pytest.raises(kernels.KernelError, match="sumsq_in"):
+        kernels.gemm_bf16(x[:8], w, out[:8], fault_word(), sumsq_in=sumsq[:8, :3].contiguous(), norm_size=64)
+
+
 def test_gemm_bf16_refuses_rows_that_are_no_multiple_of_16_bytes():
     kernels = k()
     with pytest.raises(kernels.KernelError):
