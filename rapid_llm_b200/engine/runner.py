@@ -397,10 +397,9 @@ class ModelRunner:
             kernels.LAUNCHES.count = before          # recording is not launching
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
+            # The eager run above is this step's result.  Capturing executes nothing, and the graph
+            # is not replayed now: a mixer with state of its own must see every token once.
             self._graphs[bucket] = (graph, static_logits, launches)
-            logits = static_logits
-            graph.replay()   # the eager run above already wrote the same values; keeps one code path
-            kernels.LAUNCHES.add(launches)
         else:
             graph, logits, launches = captured
             graph.replay()

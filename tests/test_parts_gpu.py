@@ -237,3 +237,103 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for name in tokens:
         torch.testing.assert_close(torch.cat(pieces[name]), whole[name], **for_dtype("float32"))
     assert float(whole["a"].abs().max()) > 0
+
+
+def test_state_advances_once_per_token_when_decode_steps_are_captured(tmp_path):
+    """A mixer with state, indexed on the device, decodes through captured graphs: the step in
+    which a batch size is captured must advance the state once, like every other step."""
+    from rapid_llm_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.parts import MIXERS, Mixer, StateNeed, TensorSpec
+    from rapid_llm_b200.weights import write_random_model
+
+    hidden, vocab, decay = 32, 89, 0.75
+
+    @MIXERS.register("toy_running_sum")
+    class ToyRunningSum(Mixer):
+        """s_t = decay * s_{t-1} + x_t per request; y_t = s_t @ W^T."""
+
+        def __init__(self, *, hidden_size, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.weight = self.new_storage((hidden_size, hidden_size), "matrix")
+
+        def state_need(self):
+            return StateNeed((self.weight.shape[0],), torch.float32)
+
+        def tensor_specs(self):
+            return {"proj.weight": TensorSpec(tuple(self.weight.shape))}
+
+        def load_tensor(self, name, tensor):
+            self.weight.copy_(tensor)
+
+        def forward(self, x, batch, cache):
+            if batch.decode_only:          # one token per entry: slots come from the device, no host decision
+                slots = batch.entry_slot.long()
+                state = cache.state[slots] * decay + x.float()
+                cache.state[slots] = state
+                return (state @ self.weight.float().T).to(x.dtype)
+            out = torch.empty_like(x)
+            for index in range(batch.num_entries):
+                state = cache.state[int(batch.h_entry_slot[index])]
+                for row in range(int(batch.h_cu_seqlens[index]), int(batch.h_cu_seqlens[index + 1])):
+                    state.mul_(decay).add_(x[row].float())
+                    out[row] = (state @ self.weight.float().T).to(x.dtype)
+            return out
+
+    @dataclasses.dataclass(frozen=True)
+    class RunningSumConfig:
+        vocab_size: int
+        architecture = "ToyRunningSumForCausalLM"
+        model_type = "toy_running_sum"
+
+        @classmethod
+        def from_dict(cls, raw, overrides=None):
+            return cls(dict(raw, **(overrides or {}))["vocab_size"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "model_type": self.model_type, "vocab_size": self.vocab_size}
+
+        def to_spec(self):
+            norm = PartSpec("rmsnorm", {"size": hidden, "eps": 1e-5})
+            toy = PartSpec("toy_running_sum", {"hidden_size": hidden})
+            attention = PartSpec("gqa_attention", {
+                "hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                "position": PartSpec("rope", {"head_dim": 16, "rotary_dim": 16, "theta": 10000.0, "max_positions": 64}),
+            })
+            ffn = PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48})
+            layers = tuple(LayerSpec("prenorm", mixer, ffn, norm, f"model.layers.{i}.") for i, mixer in enumerate((toy, attention)))
+            return ModelSpec(
+                architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=hidden, max_positions=64,
+                embedding=PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": hidden}),
+                layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(2)), final_norm=norm,
+                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": hidden, "tied": True}),
+            )
+
+    register_architecture(RunningSumConfig)
+    folder = write_random_model(tmp_path / "running_sum", RunningSumConfig(vocab), seed=11)
+    engine = EngineConfig(dtype=torch.float32, max_seq_len=64, page_size=8, num_pages=24, max_num_seqs=4,
+                          max_num_batched_tokens=64, use_cuda_graph=True, use_dependent_launch=False)
+    runner = ModelRunner.from_folder(folder, engine)
+    generator = torch.Generator().manual_seed(4)
+    tokens = {name: torch.randint(0, vocab, (count,), generator=generator).tolist()
+              for name, count in (("a", 19), ("b", 12), ("c", 26))}
+    tail = 7
+    whole = {}
+    for name, ids in tokens.items():
+        runner.admit(name)
+        whole[name] = runner.step([StepEntry(name, ids, list(range(len(ids) - tail, len(ids))))]).cpu().clone()
+        runner.release(name)
+
+    for name, ids in tokens.items():
+        runner.admit(name)
+        runner.step([StepEntry(name, ids[:-tail], [])])
+    decoded = {name: [] for name in tokens}
+    for step in range(tail):        # three rows padded to a batch of four; the first of these steps captures it
+        entries = [StepEntry(name, [ids[len(ids) - tail + step]], [0]) for name, ids in tokens.items()]
+        logits = runner.step_decode(entries).cpu()
+        for row, name in enumerate(tokens):
+            decoded[name].append(logits[row].clone())
+    runner.check_fault()
+    assert list(runner._graphs) == [4]
+    for name in tokens:
+        torch.testing.assert_close(torch.stack(decoded[name]), whole[name], **for_dtype("float32"))
