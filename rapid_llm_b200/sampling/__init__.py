@@ -1,3 +1,3 @@
-from .params import SamplingParams
+from .params import PositionLogprobs, SamplingParams
 
-__all__ = ["SamplingParams"]
+__all__ = ["PositionLogprobs", "SamplingParams"]
