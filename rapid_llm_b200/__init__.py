@@ -8,7 +8,7 @@ is the command line.
 __version__ = "0.1.0"
 
 from .config import EngineConfig, Qwen3Config, load_config
-from .sampling.params import PositionLogprobs, SamplingParams
+from .sampling.params import SamplingParams
 
 
 def __getattr__(name):  # the engine imports lazily: configuration and weights work without a GPU
@@ -27,4 +27,4 @@ def __getattr__(name):  # the engine imports lazily: configuration and weights w
     raise AttributeError(name)
 
 
-__all__ = ["EngineConfig", "LLM", "ModelRunner", "PositionLogprobs", "Qwen3Config", "SamplingParams", "Scheduler", "load_config"]
+__all__ = ["EngineConfig", "LLM", "ModelRunner", "Qwen3Config", "SamplingParams", "Scheduler", "load_config"]

@@ -525,100 +525,6 @@ sample_cluster_kernel(const T* __restrict__ logits, int vocab, long long row_str
   sample_cluster_sync();                                         // nobody leaves while its shared memory may be read
 }
 
-// ------------------------------------------------------------------------------------------
-// Log-probabilities for reporting (rapid_llm/engine/sampler.py:345-369): per row, the
-// distribution is log_softmax(adjusted logits / T) in float32, with the repetition penalty
-// applied as above and T = 1 for rows without a temperature (greedy rows, prompt positions).
-// Written per row: the log-probability of the given token, and the k most likely tokens with
-// theirs, descending, equal values in rising index order.  Each rank of the top k is one sweep
-// over the row ("the largest that comes after the previous one"), which is simple and exact
-// and costs k reads of a row that lies in L2.
-template <typename T>
-__global__ void __launch_bounds__(1024)
-logprobs_kernel(const T* __restrict__ logits, int vocab, long long row_stride,
-                const float* __restrict__ temperature,   // [rows] or null = 1; values <= 0 count as 1
-                const float* __restrict__ penalty,       // [rows] or null = 1
-                const int* __restrict__ seen_tokens, const int* __restrict__ seen_offsets,
-                const int* __restrict__ ids,             // [rows] the token whose log-probability is wanted
-                int k, float* __restrict__ chosen, float* __restrict__ top_values, int* __restrict__ top_ids) {
-  extern __shared__ unsigned seen_bits[];  // ceil(vocab / 32) words when a penalty applies
-  __shared__ float fscratch[32];
-  __shared__ int iscratch[32];
-  pdl_trigger();
-  const int row = blockIdx.x;
-  const T* x = logits + static_cast<size_t>(row) * row_stride;
-  pdl_wait();
-  const float temp = temperature ? temperature[row] : 0.0f;
-  const float divisor = temp > 0.0f ? temp : 1.0f;     // a true division, as the reference divides
-  const float pen = penalty ? penalty[row] : 1.0f;
-  const int seen_begin = seen_offsets ? seen_offsets[row] : 0;
-  const int seen_end = seen_offsets ? seen_offsets[row + 1] : 0;
-  const bool has_pen = pen != 1.0f && seen_tokens != nullptr && seen_end > seen_begin;
-  if (has_pen) {
-    const int words = (vocab + 31) >> 5;
-    for (int i = threadIdx.x; i < words; i += blockDim.x) seen_bits[i] = 0u;
-    __syncthreads();
-    for (int i = seen_begin + threadIdx.x; i < seen_end; i += blockDim.x) {
-      const int id = seen_tokens[i];
-      if (id >= 0 && id < vocab) atomicOr(&seen_bits[id >> 5], 1u << (id & 31));
-    }
-    __syncthreads();
-  }
-  auto scaled = [&](float v, int i) -> float {
-    if (has_pen && ((seen_bits[i >> 5] >> (i & 31)) & 1u)) v = v < 0.0f ? v * pen : v / pen;
-    return v / divisor;
-  };
-  // fn(index, scaled value) sees each element once; a thread meets its indices in rising order
-  const bool vector = (reinterpret_cast<uintptr_t>(x) & (sizeof(T) == 2 ? 15 : 31)) == 0;
-  const int vector_end = vector ? (vocab & ~7) : 0;
-  auto sweep = [&](auto&& fn) {
-    for (int c = threadIdx.x * 8; c < vector_end; c += blockDim.x * 8) {
-      float v[8];
-      load8(x + c, v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) fn(c + j, scaled(v[j], c + j));
-    }
-    for (int i = vector_end + threadIdx.x; i < vocab; i += blockDim.x) fn(i, scaled(to_float(x[i]), i));
-  };
-
-  MaxIndex best{-INFINITY, 0x7fffffff};
-  sweep([&](int i, float v) {
-    if (v > best.value) {
-      best.value = v;
-      best.index = i;
-    }
-  });
-  best = block_argmax(best, fscratch, iscratch);
-  float z = 0.0f;
-  sweep([&](int, float v) { z += expf(v - best.value); });
-  z = block_sum(z, fscratch);
-  const float log_z = best.value + logf(z);
-  if (threadIdx.x == 0) {
-    const int id = ids[row];
-    chosen[row] = (id >= 0 && id < vocab) ? scaled(to_float(x[id]), id) - log_z : NAN;
-  }
-
-  MaxIndex last = best;
-  for (int rank = 0; rank < k; ++rank) {
-    if (rank > 0) {
-      MaxIndex next{-INFINITY, 0x7fffffff};
-      sweep([&](int i, float v) {
-        const bool after = v < last.value || (v == last.value && i > last.index);
-        if (after && v > next.value) {
-          next.value = v;
-          next.index = i;
-        }
-      });
-      last = block_argmax(next, fscratch, iscratch);
-    }
-    if (threadIdx.x == 0) {
-      const bool found = last.index >= 0 && last.index < vocab;     // false once the row is used up
-      top_values[static_cast<size_t>(row) * k + rank] = found ? last.value - log_z : -INFINITY;
-      top_ids[static_cast<size_t>(row) * k + rank] = found ? last.index : -1;
-    }
-  }
-}
-
 }  // namespace rl
 
 // logits: [rows, vocab] of `dtype` with `row_stride` elements between rows.  Null
@@ -677,34 +583,6 @@ extern "C" int rl_sample(int dtype, const void* logits, int rows, int vocab, lon
     return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, pdl != 0,
                              static_cast<const scalar_t*>(logits), vocab, row_stride, temperature, top_p,
                              penalty, seeds, counters, seen_tokens, seen_offsets, out);
-  });
-  return 0;
-}
-
-// Log-probabilities of `ids[r]` under row r's distribution, and its `k` most likely tokens
-// (`top_values`, `top_ids`: [rows, k]; may be null when k is 0).  `temperature`, `penalty` and
-// the seen-token lists mean what they mean to rl_sample and may be null.
-extern "C" int rl_logprobs(int dtype, const void* logits, int rows, int vocab, long long row_stride,
-                           const float* temperature, const float* penalty, const int* seen_tokens,
-                           const int* seen_offsets, const int* ids, int k, float* chosen,
-                           float* top_values, int* top_ids, cudaStream_t stream) {
-  if (rows == 0) return 0;
-  if (vocab <= 0 || k < 0 || ids == nullptr || chosen == nullptr ||
-      (k > 0 && (top_values == nullptr || top_ids == nullptr)))
-    return static_cast<int>(cudaErrorInvalidValue);
-  const size_t smem = (penalty && seen_tokens) ? static_cast<size_t>((vocab + 31) / 32) * 4 : 0;
-  if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
-  const int threads = vocab >= 8192 ? 1024 : 256;
-  RL_DISPATCH_DTYPE(dtype, {
-    auto kernel = rl::logprobs_kernel<scalar_t>;
-    if (smem > 40 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem));
-      if (e != cudaSuccess) return static_cast<int>(e);
-    }
-    return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, false,
-                             static_cast<const scalar_t*>(logits), vocab, row_stride, temperature, penalty,
-                             seen_tokens, seen_offsets, ids, k, chosen, top_values, top_ids);
   });
   return 0;
 }

@@ -193,15 +193,11 @@ class LLM:
         self.scheduler.run_to_completion()
         outputs = []
         for (text, ids), request in zip(encoded, requests):
-            completion = CompletionOutput(
-                0, self._decode(request.output_token_ids), list(request.output_token_ids), request.finish_reason,
-                None if request.output_logprobs is None else list(request.output_logprobs),
-            )
+            completion = CompletionOutput(0, self._decode(request.output_token_ids), list(request.output_token_ids), request.finish_reason)
             metrics = {
                 "arrival": request.arrival_time, "first_scheduled": request.first_scheduled_time,
                 "first_token": request.first_token_time, "finished": request.finish_time,
                 "preemptions": request.num_preemptions,
             }
-            prompt_logprobs = None if request.prompt_logprobs is None else list(request.prompt_logprobs)
-            outputs.append(RequestOutput(text, ids, [completion], metrics, prompt_logprobs))
+            outputs.append(RequestOutput(text, ids, [completion], metrics))
         return outputs

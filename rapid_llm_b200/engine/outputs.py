@@ -1,15 +1,12 @@
 """Result records of a generation call, shaped like the reference's
 (``rapid_llm/engine/outputs.py:22-59``): one ``RequestOutput`` per prompt holding its
-completions; token ids ride along because random-weight models have no tokenizer.
-``logprobs`` (one record per generated token) and ``prompt_logprobs`` (one per prompt position,
-``None`` at position 0) are filled when the request's ``SamplingParams`` ask for them and are
-``None`` otherwise."""
+completions; token ids ride along because random-weight models have no tokenizer.  The
+reference's ``logprobs`` and ``prompt_logprobs`` attributes exist and are always ``None``
+(log-probabilities are not reported)."""
 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-
-from ..sampling.params import PositionLogprobs
 
 
 @dataclass
@@ -18,7 +15,7 @@ class CompletionOutput:
     text: str
     token_ids: list[int]
     finish_reason: str | None
-    logprobs: list[PositionLogprobs] | None = None
+    logprobs: None = None
 
 
 @dataclass
@@ -27,7 +24,7 @@ class RequestOutput:
     prompt_token_ids: list[int]
     outputs: list[CompletionOutput] = field(default_factory=list)
     metrics: dict = field(default_factory=dict)
-    prompt_logprobs: list[PositionLogprobs | None] | None = None
+    prompt_logprobs: None = None
 
     @property
     def text(self) -> str:

@@ -41,15 +41,11 @@ class StepEntry:
         request_id: Key of a request admitted with :meth:`ModelRunner.admit`.
         tokens: Its next tokens (a portion of the prompt, or one decoded token).
         want: Places among ``tokens`` whose logits are asked for; may be empty.
-        score: More such places, whose rows come after the ``want`` rows of ALL entries: the
-            executor asks for prompt positions to score this way, so that the rows it samples
-            from stay one contiguous block.
     """
 
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
-    score: Sequence[int] = ()
 
 
 def require_cuda(device: torch.device) -> None:
@@ -209,8 +205,7 @@ class ModelRunner:
             assert reserved
 
         g = len(cache.groups)
-        wanted = sum(len(entry.want) for entry in entries) + pad
-        rows = wanted + sum(len(entry.score) for entry in entries)
+        rows = sum(len(entry.want) for entry in entries) + pad
         flip = self._meta_flip
         host = self._meta_host[flip]
         self._meta_flip ^= 1
@@ -248,7 +243,7 @@ class ModelRunner:
         if cursor > self._meta_capacity:
             raise ValueError("the step's metadata does not fit its buffer")
 
-        at, row_at, score_at = 0, 0, wanted
+        at, row_at = 0, 0
         cu_seqlens[0] = 0
         for i, (entry, start, length) in enumerate(zip(entries, starts, lengths)):
             slot = cache.slot_of(entry.request_id)
@@ -263,11 +258,6 @@ class ModelRunner:
                     raise ValueError(f"want index {place} outside the entry's {length} tokens")
                 logit_rows[row_at] = at + place
                 row_at += 1
-            for place in entry.score:
-                if not 0 <= place < length:
-                    raise ValueError(f"score index {place} outside the entry's {length} tokens")
-                logit_rows[score_at] = at + place
-                score_at += 1
             at += length
             cu_seqlens[i + 1] = at
         for i in range(len(entries), n):  # padding rows of a captured decode batch
@@ -356,8 +346,7 @@ class ModelRunner:
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Run the entries as one batch; logits ``[wanted, vocab]`` in entry and ``want`` order
-        (followed by the rows of the entries' ``score`` places, in the same order)."""
+        """Run the entries as one batch; logits ``[wanted, vocab]`` in entry and ``want`` order."""
         batch = self.prepare(entries)
         logits = self._forward(batch, self.layer_caches())
         for entry in entries:
@@ -390,7 +379,7 @@ class ModelRunner:
         first step of a bucket runs eagerly and is then captured.  The reference captures
         decode graphs per batch size and length bucket (``rapid_llm/executor/cuda_graph.py:45-46,317``).
         """
-        if any(len(entry.tokens) != 1 or list(entry.want) != [0] or len(entry.score) for entry in entries):
+        if any(len(entry.tokens) != 1 or list(entry.want) != [0] for entry in entries):
             raise ValueError("step_decode takes single tokens that all want their logits")
         count = len(entries)
         bucket = self.decode_bucket(count)

@@ -66,8 +66,6 @@ class Request:
     finish_reason: str | None = None
     num_preemptions: int = 0
     exhausted: bool = False        # its last token is sampled (perhaps still on the device): nothing more to feed
-    output_logprobs: list | None = None      # per generated token its record, when ``params.logprobs`` asks
-    prompt_logprobs: list | None = None      # per prompt position its record (``None`` at position 0)
     arrival_time: float = 0.0
     first_scheduled_time: float | None = None
     first_token_time: float | None = None
@@ -130,9 +128,7 @@ class Executor(Protocol):
 
         An executor that can run ahead also has ``launch(entries) -> handle`` (enqueue only) and
         ``collect(handle) -> list[int]`` (wait for that step's tokens); a token id ``-(row + 1)``
-        among the entries' tokens then means row ``row`` of the previously launched step's result.
-        One that reports log-probabilities has ``records(handle) -> (per sampled row a record or
-        None, [(request, prompt position, record), ...])`` as well."""
+        among the entries' tokens then means row ``row`` of the previously launched step's result."""
 
 
 class Scheduler:
@@ -148,7 +144,6 @@ class Scheduler:
         self.num_preemptions = 0
         self._inflight: Inflight | None = None
         self._can_launch = hasattr(executor, "launch") and hasattr(executor, "collect")
-        self._has_records = self._can_launch and hasattr(executor, "records")
 
     @classmethod
     def from_pretrained(cls, model, **options) -> "Scheduler":
@@ -205,10 +200,6 @@ class Scheduler:
             request_id = f"req-{next(self._ids)}"
         seed = params.seed if params.seed is not None else zlib.crc32(repr(request_id).encode())
         request = Request(request_id, prompt, params, max_new, seed, arrival_time=time.perf_counter())
-        if params.logprobs is not None:
-            request.output_logprobs = []
-        if params.prompt_logprobs is not None:
-            request.prompt_logprobs = [None] * len(prompt)
         self.waiting.append(request)
         return request
 
@@ -345,13 +336,9 @@ class Scheduler:
     def _harvest(self, inflight: Inflight) -> list[Request]:
         """Read a launched step's tokens; put them in place of their stand-ins, finish and free."""
         sampled = self.executor.collect(inflight.handle) if self._can_launch else inflight.handle
-        records, prompt_records = self.executor.records(inflight.handle) if self._has_records else ([], [])
-        for request, position, record in prompt_records:
-            if request.prompt_logprobs is not None:
-                request.prompt_logprobs[position] = record
         now = time.perf_counter()
         finished: list[Request] = []
-        for row, ((request, index), token) in enumerate(zip(inflight.slots, sampled)):
+        for (request, index), token in zip(inflight.slots, sampled):
             if request.finished:
                 continue                                  # a step it ran ahead into: the token is dropped
             token = int(token)
@@ -362,8 +349,6 @@ class Scheduler:
                 self._finish(request, "eos", now)
             else:
                 request.output_token_ids[index] = token
-                if request.output_logprobs is not None and row < len(records):
-                    request.output_logprobs[index:] = [records[row]]      # kept in step with the tokens
                 if request.exhausted and index == len(request.output_token_ids) - 1:
                     self._finish(request, "length", now)
             if request.finished:
@@ -402,8 +387,6 @@ class Scheduler:
         request.finish_time = now
         while request.output_token_ids and request.output_token_ids[-1] < 0:
             request.output_token_ids.pop()               # stand-ins of steps it ran ahead into
-        if request.output_logprobs is not None:
-            del request.output_logprobs[len(request.output_token_ids):]
         if was_running:
             self.running.remove(request)
             self.executor.release(request.request_id)

@@ -123,13 +123,9 @@ def core() -> ctypes.CDLL:
             c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
         ]
-        lib.rl_logprobs.argtypes = [
-            c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-        ]
         for name in (
             "rl_embedding", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float",
-            "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample", "rl_logprobs",
+            "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
             getattr(lib, name).restype = c_int
         _SIGNATURES_SET = True
@@ -572,57 +568,6 @@ def sample(
         f"sample(vocab={logits.shape[1]})",
     )
     return out
-
-
-def logprobs(
-    logits: torch.Tensor,
-    ids: torch.Tensor,
-    chosen: torch.Tensor,
-    *,
-    top_values: torch.Tensor | None = None,
-    top_ids: torch.Tensor | None = None,
-    temperature: torch.Tensor | None = None,
-    penalty: torch.Tensor | None = None,
-    seen_tokens: torch.Tensor | None = None,
-    seen_offsets: torch.Tensor | None = None,
-) -> torch.Tensor:
-    """``chosen[r]`` = log-probability of token ``ids[r]`` under row ``r`` of ``logits``.
-
-    The distribution is ``log_softmax(logits / T)`` in float32, after the repetition penalty
-    of :func:`sample`; rows without a temperature (none given, or 0 = greedy) use ``T = 1``.
-    ``top_values`` / ``top_ids`` (float32 / int32 ``[rows, k]``) receive the ``k`` most likely
-    tokens, descending, equal values in rising id order; entries beyond the vocabulary are
-    ``-inf`` / ``-1``.
-    """
-    _need_cuda(logits, ids, chosen, top_values, top_ids, temperature, penalty, seen_tokens, seen_offsets)
-    _expect("ids", ids, torch.int32), _expect("chosen", chosen, torch.float32)
-    _expect("top_values", top_values, torch.float32), _expect("top_ids", top_ids, torch.int32)
-    _expect("temperature", temperature, torch.float32), _expect("penalty", penalty, torch.float32)
-    _expect("seen_tokens", seen_tokens, torch.int32), _expect("seen_offsets", seen_offsets, torch.int32)
-    for name, tensor in (("ids", ids), ("chosen", chosen), ("top_values", top_values), ("top_ids", top_ids)):
-        _contig(name, tensor)
-    if logits.dim() != 2 or logits.stride(1) != 1:
-        raise KernelError("logprobs: logits must be [rows, vocab] with contiguous rows")
-    rows = logits.shape[0]
-    if ids.numel() != rows or chosen.numel() != rows:
-        raise KernelError("logprobs: ids and chosen must hold one entry per row")
-    width = 0
-    if top_values is not None or top_ids is not None:
-        if top_values is None or top_ids is None or top_values.shape != top_ids.shape or top_values.dim() != 2 \
-                or top_values.shape[0] != rows:
-            raise KernelError("logprobs: top_values and top_ids must both be [rows, k]")
-        width = top_values.shape[1]
-    if rows == 0:
-        return chosen
-    _check(
-        core().rl_logprobs(
-            dtype_tag(logits.dtype), _ptr(logits), rows, logits.shape[1], logits.stride(0) if rows else 0,
-            _ptr(temperature), _ptr(penalty), _ptr(seen_tokens), _ptr(seen_offsets), _ptr(ids), width,
-            _ptr(chosen), _ptr(top_values) if width else c_void_p(0), _ptr(top_ids) if width else c_void_p(0), _stream(),
-        ),
-        f"logprobs(vocab={logits.shape[1]}, k={width})",
-    )
-    return chosen
 
 
 def describe_fault(word: int) -> str:

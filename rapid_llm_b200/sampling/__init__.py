@@ -1,3 +1,3 @@
-from .params import PositionLogprobs, SamplingParams
+from .params import SamplingParams
 
-__all__ = ["PositionLogprobs", "SamplingParams"]
+__all__ = ["SamplingParams"]

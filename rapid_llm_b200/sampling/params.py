@@ -6,35 +6,13 @@ values are validated at construction.  ``seed`` is an addition: draws come from 
 counter-based generator keyed by (seed, index of the generated token), so a request's
 tokens do not depend on what else is in the batch.  ``stop_on_repeat`` is accepted and
 inert: the reference's breaker looks at decoded text, which token-id requests do not have.
-``logprobs`` and ``prompt_logprobs`` ask for log-probability records (``:60-70,114-131``): the
-``k`` most likely tokens per generated token or prompt position, with the log-probability of
-the token that is actually there always included (``0`` reports it alone, ``None`` skips the
-work).  Generated tokens are scored under the distribution they were drawn from (penalty
-applied, temperature divided through; a greedy row at temperature 1), prompt positions under
-the raw logits; position 0 of a prompt has no predictor and reports ``None``.
+``logprobs`` and ``prompt_logprobs`` (reporting, not sampling) are accepted only as ``None``;
+any other value is refused at construction rather than ignored.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
-
-
-@dataclass(frozen=True)
-class PositionLogprobs:
-    """One position's record (``rapid_llm/engine/sampler.py:114-131``).
-
-    Attributes:
-        token_id: The token at this position (the sampled one, or the prompt's own).
-        logprob: Its log-probability under the distribution the position produced; it need not
-            be among the ``k`` most likely.
-        top_token_ids: The ``k`` most likely token ids, descending.
-        top_logprobs: Their log-probabilities, in the same order.
-    """
-
-    token_id: int
-    logprob: float
-    top_token_ids: tuple[int, ...] = ()
-    top_logprobs: tuple[float, ...] = ()
 
 
 @dataclass
@@ -57,9 +35,8 @@ class SamplingParams:
             raise ValueError(f"max_gen_len must be >= 1 or None, got {self.max_gen_len}")
         if self.repetition_penalty <= 0:
             raise ValueError(f"repetition_penalty must be > 0, got {self.repetition_penalty}")
-        for name, value in (("logprobs", self.logprobs), ("prompt_logprobs", self.prompt_logprobs)):
-            if value is not None and value < 0:
-                raise ValueError(f"{name} must be >= 0, got {value}")
+        if self.logprobs is not None or self.prompt_logprobs is not None:
+            raise ValueError("logprobs and prompt_logprobs are not reported by this engine; leave them None")
         if self.seed is not None and not 0 <= self.seed < 2**63:
             raise ValueError(f"seed must be in [0, 2**63), got {self.seed}")
 

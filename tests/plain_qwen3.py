@@ -234,17 +234,6 @@ def sample_token(logits, temperature, top_p=1.0, penalty=1.0, generated=(), seed
     return int(picks[0]) if len(picks) else int(torch.argmax(values))
 
 
-def position_logprobs(logits, token: int, k: int, temperature=0.0, penalty=1.0, generated=()):
-    """Log-probability of ``token`` and the ``k`` most likely tokens with theirs, descending, under
-    log_softmax(penalised logits / T) in float32; T = 1 for a greedy row or a prompt position
-    (rapid_llm/engine/sampler.py:345-369,708-718)."""
-    values = penalised(torch.as_tensor(logits), generated, penalty)
-    scaled = values / (temperature if temperature > 0 else 1.0)
-    logprobs = scaled - torch.logsumexp(scaled, dim=-1)
-    order = sorted(range(len(logprobs)), key=lambda i: (-float(logprobs[i]), i))[:k]
-    return float(logprobs[token]), order, [float(logprobs[i]) for i in order]
-
-
 def greedy_generate(config, weights, prompt, steps: int, dtype=torch.float32) -> list[int]:
     tokens = list(prompt)
     for _ in range(steps):

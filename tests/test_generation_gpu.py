@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import pytest
 import torch
-from plain_qwen3 import forward_logits, greedy_generate, position_logprobs, sample_token
+from plain_qwen3 import forward_logits, greedy_generate, sample_token
 from tiny_configs import PAGE_SIZES
 
 pytestmark = pytest.mark.gpu
@@ -84,46 +84,6 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_dirs, 
             agree += int(want == token)
             total += 1
     assert agree >= total - 2, (agree, total)
-
-
-@pytest.mark.parametrize("run_ahead", [True, False])
-def test_logprobs_of_generated_tokens_and_of_prompt_positions(tiny_dirs, tiny_plain, run_ahead):
-    """Records against the plain log-softmax: generated tokens under the distribution they were
-    drawn from, prompt positions (cut into portions of 13) under the raw logits."""
-    from rapid_llm_b200 import SamplingParams
-
-    config, weights = tiny_plain["B"]
-    prompts = random_prompts(config["vocab_size"], [5, 37, 30, 2], 6)
-    params = [
-        SamplingParams(temperature=0.7, top_p=0.9, repetition_penalty=1.2, max_gen_len=6, seed=3, logprobs=3, prompt_logprobs=2),
-        SamplingParams(temperature=0.0, top_p=1.0, repetition_penalty=1.0, max_gen_len=9, logprobs=0, prompt_logprobs=4),
-        SamplingParams(temperature=1.1, top_p=1.0, repetition_penalty=1.0, max_gen_len=7, seed=9, logprobs=5),
-        SamplingParams.greedy(max_gen_len=5),
-    ]
-    llm = make_llm(tiny_dirs["B"], "float32", "B", run_ahead=run_ahead)
-    outputs = llm.generate(prompts, params)
-    assert outputs[3].outputs[0].logprobs is None and outputs[3].prompt_logprobs is None and outputs[2].prompt_logprobs is None
-    for prompt, output, sp in zip(prompts[:3], outputs[:3], params[:3]):
-        tokens, records = output.token_ids, output.outputs[0].logprobs
-        assert len(records) == len(tokens) == sp.max_gen_len
-        logits = forward_logits(config, weights, prompt + tokens)
-        for index, (token, record) in enumerate(zip(tokens, records)):
-            want, order, values = position_logprobs(logits[len(prompt) - 1 + index], token, sp.logprobs, sp.temperature,
-                                                    sp.repetition_penalty, tokens[:index])
-            assert record.token_id == token and abs(record.logprob - want) < 1e-3
-            assert list(record.top_token_ids) == order
-            assert max((abs(a - b) for a, b in zip(record.top_logprobs, values)), default=0.0) < 1e-3
-        if sp.prompt_logprobs is None:
-            continue
-        scored = output.prompt_logprobs
-        assert len(scored) == len(prompt) and scored[0] is None
-        for position in range(1, len(prompt)):
-            want, order, values = position_logprobs(logits[position - 1], prompt[position], sp.prompt_logprobs)
-            record = scored[position]
-            assert record.token_id == prompt[position] and abs(record.logprob - want) < 1e-3
-            assert list(record.top_token_ids) == order
-            assert max(abs(a - b) for a, b in zip(record.top_logprobs, values)) < 1e-3
-    llm.runner.cache.check()
 
 
 def test_eviction_under_a_small_pool_does_not_change_tokens(tiny_dirs):

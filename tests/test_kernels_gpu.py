@@ -8,7 +8,7 @@ import math
 
 import pytest
 import torch
-from plain_qwen3 import apply_rope, causal_attention, position_logprobs, rms_norm, rope_angles, sample_token
+from plain_qwen3 import apply_rope, causal_attention, rms_norm, rope_angles, sample_token
 from tolerances import for_dtype
 
 pytestmark = pytest.mark.gpu
@@ -614,45 +614,6 @@ def test_sampling_matches_plain(dtype, vocab):
     ]
     agree = sum(int(a == b) for a, b in zip(out.tolist(), want))
     assert agree >= rows - 1, (out.tolist(), want)   # a draw on a float32 rounding edge may differ
-
-
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("vocab,width", [(331, 5), (8193, 0), (151936, 20), (40, 64)])
-def test_logprobs_match_plain(dtype, vocab, width):
-    """Log-probability of a given token and the most likely tokens, under each row's own
-    temperature and penalty; ties in rising id order; a width beyond the vocabulary is padded."""
-    rows = 8
-    logits = rand((rows, vocab), dtype, scale=2.0, seed=21).to(DEV)
-    logits[3, 5] = logits[3, 9] = logits[3].max() + 1          # a tie at the top
-    temperature = torch.tensor([0.0, 0.7, 1.0, 1.3] * 2, dtype=torch.float32)
-    penalty = torch.tensor([1.0, 1.1, 1.0, 2.0] * 2, dtype=torch.float32)
-    generated = [torch.randint(0, vocab, (row % 3 * 7,)).tolist() for row in range(rows)]
-    offsets = torch.tensor([0] + [len(g) for g in generated], dtype=torch.int32).cumsum(0).to(torch.int32)
-    flat = torch.tensor([t for g in generated for t in g] or [0], dtype=torch.int32)
-    ids = torch.randint(0, vocab, (rows,), dtype=torch.int32)
-    chosen = torch.empty(rows, dtype=torch.float32, device=DEV)
-    top_values = torch.empty((rows, width), dtype=torch.float32, device=DEV) if width else None
-    top_ids = torch.empty((rows, width), dtype=torch.int32, device=DEV) if width else None
-    k().logprobs(logits, ids.to(DEV), chosen, top_values=top_values, top_ids=top_ids, temperature=temperature.to(DEV),
-                 penalty=penalty.to(DEV), seen_tokens=flat.to(DEV), seen_offsets=offsets.to(DEV))
-    host = logits.float().cpu()
-    for row in range(rows):
-        want, order, values = position_logprobs(host[row], int(ids[row]), width, float(temperature[row]),
-                                                float(penalty[row]), generated[row])
-        assert abs(float(chosen[row]) - want) < 2e-4
-        if width:
-            real = min(width, vocab)
-            assert top_ids[row, :real].tolist() == order
-            torch.testing.assert_close(top_values[row, :real].cpu(), torch.tensor(values), rtol=0, atol=2e-4)
-            assert top_ids[row, real:].tolist() == [-1] * (width - real)
-    if width:
-        assert top_ids[3, :2].tolist() == [5, 9]
-    # raw rows (a prompt's positions): no temperature, no penalty, rows taken from the middle of a buffer
-    part = logits[2:5]
-    k().logprobs(part, ids[2:5].to(DEV), chosen[:3])
-    for row in range(3):
-        want, _, _ = position_logprobs(host[2 + row], int(ids[2 + row]), 0)
-        assert abs(float(chosen[row]) - want) < 2e-4
 
 
 def test_sampling_follows_the_distribution():

@@ -184,10 +184,8 @@ def test_sampling_params_are_validated():
             SamplingParams(**bad)
     assert SamplingParams().temperature == 0.6 and SamplingParams().top_p == 0.9 and SamplingParams().repetition_penalty == 1.1
     assert SamplingParams(stop_on_repeat=False, logprobs=None).stop_on_repeat is False      # the reference's fields are accepted
-    for bad in (dict(logprobs=-1), dict(prompt_logprobs=-2)):
-        with pytest.raises(ValueError):
-            SamplingParams(**bad)
-    assert SamplingParams(logprobs=0, prompt_logprobs=5).prompt_logprobs == 5
+    with pytest.raises(ValueError):
+        SamplingParams(logprobs=5)
     assert SamplingParams(temperature=0).is_greedy
 
 
@@ -363,50 +361,3 @@ def test_random_arrivals_lengths_stops_and_aborts_lose_nothing(seed, ahead):
     if ahead:
         assert all(token >= 0 for fed in executor.fed for token in fed)
     assert executor.cache.num_free_pages() == pages and executor.cache.num_free_slots == 3
-
-
-# ------------------------------------------------------------------ log-probability records
-class RecordingExecutor(RunAheadExecutor):
-    """Adds ``records``: a record names the row it was made for, so the test can see where it lands."""
-
-    def launch(self, entries):
-        number, sampled = super().launch(entries)
-        prompt_rows = []
-        for entry in entries:
-            request = entry.request
-            if request.params.prompt_logprobs is not None:
-                for place in range(len(entry.tokens)):
-                    target = entry.start + place + 1
-                    if target < len(request.prompt_token_ids):
-                        prompt_rows.append((request, target, ("prompt", request.request_id, target)))
-        widths = [entry.request.params.logprobs for entry in entries if entry.samples]
-        return (number, sampled, widths, prompt_rows)
-
-    def collect(self, ticket):
-        return super().collect(ticket[:2]) if ticket[0] > self.collected else ticket[1]
-
-    def records(self, ticket):
-        _, sampled, widths, prompt_rows = ticket
-        return [None if width is None else ("generated", token) for token, width in zip(sampled, widths)], prompt_rows
-
-
-@pytest.mark.parametrize("ahead", [False, True])
-def test_records_stay_in_step_with_tokens_through_stops_and_eviction(ahead):
-    config = EngineConfig(max_seq_len=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=64, max_chunk_size=16,
-                          run_ahead=ahead)
-    executor = RecordingExecutor(config, 5)
-    scheduler = Scheduler(executor, config, stop_token_ids=[7])
-    executor.stop_after["b"] = 10
-    asks = SamplingParams(temperature=0.0, top_p=1.0, repetition_penalty=1.0, max_gen_len=20, logprobs=2, prompt_logprobs=1)
-    a = scheduler.add_request(list(range(40)), asks, "a")
-    b = scheduler.add_request(list(range(100, 130)), asks, "b")
-    c = scheduler.add_request(list(range(5)), greedy(4), "c")
-    scheduler.run_to_completion()
-    assert scheduler.num_preemptions >= 1                      # five pages: the two long requests cannot both grow
-    for request in (a, b):
-        assert request.output_logprobs == [("generated", token) for token in request.output_token_ids]
-        assert request.prompt_logprobs[0] is None
-        assert request.prompt_logprobs[1:] == [("prompt", request.request_id, p) for p in range(1, len(request.prompt_token_ids))]
-    assert b.finish_reason == "eos" and len(b.output_token_ids) == 10      # the stop token and its record are dropped
-    assert c.output_logprobs is None and c.prompt_logprobs is None and len(c.output_token_ids) == 4
-    executor.cache.check()
