@@ -17,6 +17,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import subprocess
 import sys
 import time
 from pathlib import Path
@@ -136,6 +137,14 @@ def run_random_init(args) -> int:
     return 0
 
 
+def run_bench(argv: list[str]) -> int:
+    """``bench.py`` of the source checkout, as a child process with the same interpreter."""
+    script = Path(__file__).resolve().parent.parent / "bench.py"
+    if not script.is_file():
+        raise SystemExit(f"rapid-llm-b200: {script} is missing; the benchmark ships with the source checkout")
+    return subprocess.call([sys.executable, str(script), *argv])
+
+
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="rapid-llm-b200", description=__doc__.splitlines()[0])
     subs = parser.add_subparsers(dest="command", required=True)
@@ -163,6 +172,8 @@ def build_parser() -> argparse.ArgumentParser:
 
     replay = subs.add_parser("replay", help="Feed token ids step by step and write logits (bin/trace_run)", add_help=False)
     replay.set_defaults(handler=None)
+    bench = subs.add_parser("bench", help="Decode and prefill throughput of the 8B shape (bench.py)", add_help=False)
+    bench.set_defaults(handler=None)
     return parser
 
 
@@ -172,6 +183,8 @@ def main(argv: list[str] | None = None) -> int:
         from .replay import main as replay_main
 
         return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        return run_bench(argv[1:])
     args = build_parser().parse_args(argv)
     return args.handler(args)
 

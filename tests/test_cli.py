@@ -54,3 +54,8 @@ def test_an_option_for_what_is_not_built_ends_with_a_message(tmp_path):
 def test_bench_refuses_more_than_one_gpu_with_one_line():
     done = subprocess.run([sys.executable, "bench.py", "--gpus", "2"], cwd=ROOT, capture_output=True, text=True)
     assert done.returncode == 2 and len(done.stdout.strip().splitlines()) == 1 and "single-GPU" in done.stdout
+
+
+def test_the_bench_command_is_the_checkouts_bench_program():
+    done = run_cli("bench", "--gpus", "2", check=False)
+    assert done.returncode == 2 and "single-GPU" in done.stdout
