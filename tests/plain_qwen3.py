@@ -206,18 +206,12 @@ def penalised(logits: torch.Tensor, generated, penalty: float) -> torch.Tensor:
     return out
 
 
-def sample_token(logits, temperature, top_p=1.0, penalty=1.0, generated=(), seed=0, counter=0) -> int:
-    """Greedy = first index of the maximum (rapid_llm/engine/sampler.py:266-283).  Otherwise
-    softmax(logits / T) (:669-672); keep tokens while the mass ranked before them is <= top_p (:223-244);
-    draw by inverse CDF in index order over the kept mass with u = philox(seed, counter)."""
-    values = penalised(torch.as_tensor(logits), generated, penalty)
-    if temperature <= 0:
-        return int(torch.argmax(values))
-    scaled = values / temperature
-    weights = torch.exp(scaled - scaled.max())
-    total = float(weights.sum())
+def nucleus(weights: torch.Tensor, top_p: float) -> torch.Tensor:
+    """Which tokens the nucleus keeps: those for which the mass ranked before them does not exceed
+    ``top_p`` of the whole (rapid_llm/engine/sampler.py:223-244); ``weights`` need not be normalised."""
     keep = torch.ones_like(weights, dtype=torch.bool)
     if top_p < 1.0:
+        total = float(weights.sum())
         order = torch.argsort(weights, descending=True, stable=True)
         sorted_w = weights[order]
         before = torch.cumsum(sorted_w.double(), 0) - sorted_w.double()     # mass ranked before each token
@@ -227,6 +221,19 @@ def sample_token(logits, temperature, top_p=1.0, penalty=1.0, generated=(), seed
         strictly_above = before[run_start[run]]
         keep = torch.zeros_like(keep)
         keep[order[strictly_above <= top_p * total]] = True
+    return keep
+
+
+def sample_token(logits, temperature, top_p=1.0, penalty=1.0, generated=(), seed=0, counter=0) -> int:
+    """Greedy = first index of the maximum (rapid_llm/engine/sampler.py:266-283).  Otherwise
+    softmax(logits / T) (:669-672); keep tokens while the mass ranked before them is <= top_p (:223-244);
+    draw by inverse CDF in index order over the kept mass with u = philox(seed, counter)."""
+    values = penalised(torch.as_tensor(logits), generated, penalty)
+    if temperature <= 0:
+        return int(torch.argmax(values))
+    scaled = values / temperature
+    weights = torch.exp(scaled - scaled.max())
+    keep = nucleus(weights, top_p)
     kept = torch.where(keep, weights, torch.zeros_like(weights))
     target = philox_uniform(seed, counter) * float(kept.sum())
     running = torch.cumsum(kept.double(), 0)

@@ -2,7 +2,8 @@
 
 ``tests/golden/tiny_{A,B}.npz`` hold logits the reference produced on the CPU in float32
 for the tiny random models (see ``tests/golden/make_golden.py``); the folders are rebuilt
-here from the same seeds.
+here from the same seeds.  ``tests/golden/sampling.npz`` holds what the reference's sampler
+code makes of rows of random logits (``tests/golden/make_sampling_golden.py``).
 """
 
 from pathlib import Path
@@ -10,7 +11,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 import torch
-from plain_qwen3 import forward_logits
+from plain_qwen3 import forward_logits, nucleus, penalised, sample_token
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -47,3 +48,25 @@ def test_window_changes_logits_only_past_the_window(tiny_plain):
     window = config["sliding_window"]
     torch.testing.assert_close(windowed[:window], full[:window], rtol=1e-5, atol=1e-6)
     assert (windowed[window + 8 :] - full[window + 8 :]).abs().max() > 1e-4
+
+
+def test_plain_sampler_pieces_match_the_reference():
+    """The repetition penalty, the greedy pick and the set of tokens the nucleus keeps, row by row."""
+    data = np.load(GOLDEN / "sampling.npz")
+    rows = data["logits"].shape[0]
+    assert rows >= 20
+    for row in range(rows):
+        logits = torch.from_numpy(data["logits"][row])
+        generated = data["generated"][row, : data["generated_count"][row]].tolist()
+        temperature, top_p, penalty = float(data["temperature"][row]), float(data["top_p"][row]), float(data["penalty"][row])
+        values = penalised(logits, generated, penalty)
+        torch.testing.assert_close(values, torch.from_numpy(data["penalised"][row]), rtol=0, atol=0)
+        assert sample_token(logits, 0.0, penalty=penalty, generated=generated) == int(data["greedy"][row])
+        scaled = values / temperature
+        kept = nucleus(torch.exp(scaled - scaled.max()), top_p)
+        want = torch.from_numpy(data["kept"][row])
+        # a token whose mass-before lies within rounding of top_p may fall on either side
+        assert int((kept != want).sum()) <= 1, (row, int(kept.sum()), int(want.sum()))
+        # every draw of the plain sampler lands inside the reference's nucleus
+        for counter in range(6):
+            assert want[sample_token(logits, temperature, top_p, penalty, generated, seed=row, counter=counter)] or (kept != want).any()
