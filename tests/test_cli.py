@@ -7,6 +7,7 @@ import subprocess
 import sys
 from pathlib import Path
 
+import pytest
 from tiny_configs import TINY_B
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -59,3 +60,26 @@ def test_bench_refuses_more_than_one_gpu_with_one_line():
 def test_the_bench_command_is_the_checkouts_bench_program():
     done = run_cli("bench", "--gpus", "2", check=False)
     assert done.returncode == 2 and "single-GPU" in done.stdout
+
+
+def test_replay_sizes_the_pool_from_max_tokens():
+    """``--max-tokens`` is what live requests hold at most: whole pages, the context bounded by the
+    model's positions and by the pool, steps as large as the pool so that a whole prompt is one step."""
+    import torch
+    from tiny_configs import TINY_A, TINY_B
+
+    from rapid_llm_b200.config import Qwen3Config
+    from rapid_llm_b200.replay import build_parser, engine_config_for
+
+    engine = engine_config_for(Qwen3Config.from_dict(TINY_B), "float32", 130, page_size=8, max_live=4)
+    assert engine.num_pages == 17 and engine.page_size == 8 and engine.max_num_seqs == 4
+    assert engine.max_seq_len == 136 and engine.max_num_batched_tokens == 136 and engine.dtype == torch.float32
+    assert not engine.use_cuda_graph
+    small = engine_config_for(Qwen3Config.from_dict(TINY_A), "bfloat16", 1024)
+    assert small.max_seq_len == 128 and small.num_pages == 64 and small.dtype == torch.bfloat16     # 128 positions in the model
+    tiny = engine_config_for(Qwen3Config.from_dict(TINY_A), "float32", 3)
+    assert tiny.num_pages == 1 and tiny.max_seq_len == 16 and tiny.max_num_batched_tokens == 64
+    args = build_parser().parse_args(["--model", "m", "--dtype", "float32", "--out", "o", "--max-tokens", "256"])
+    assert (args.page_size, args.max_live, args.device) == (16, 8, "cuda:0")
+    with pytest.raises(SystemExit):
+        build_parser().parse_args(["--model", "m", "--dtype", "float16", "--out", "o", "--max-tokens", "1"])
