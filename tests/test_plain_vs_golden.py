@@ -3,7 +3,9 @@
 ``tests/golden/tiny_{A,B}.npz`` hold logits the reference produced on the CPU in float32
 for the tiny random models (see ``tests/golden/make_golden.py``); the folders are rebuilt
 here from the same seeds.  ``tests/golden/sampling.npz`` holds what the reference's sampler
-code makes of rows of random logits (``tests/golden/make_sampling_golden.py``).
+code makes of rows of random logits (``tests/golden/make_sampling_golden.py``), and
+``tests/golden/greedy.npz`` the token ids the reference's continuous-batching engine generated
+greedily, prompt portions of 13 tokens beside decode steps (``tests/golden/make_greedy_golden.py``).
 """
 
 from pathlib import Path
@@ -11,7 +13,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 import torch
-from plain_qwen3 import forward_logits, nucleus, penalised, sample_token
+from plain_qwen3 import forward_logits, greedy_generate, nucleus, penalised, sample_token
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -70,3 +72,15 @@ def test_plain_sampler_pieces_match_the_reference():
         # every draw of the plain sampler lands inside the reference's nucleus
         for counter in range(6):
             assert want[sample_token(logits, temperature, top_p, penalty, generated, seed=row, counter=counter)] or (kept != want).any()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_plain_greedy_tokens_match_the_references_engine(name, tiny_plain):
+    config, weights = tiny_plain[name]
+    data = np.load(GOLDEN / "greedy.npz")
+    index = 0
+    while f"{name}_prompt{index}" in data:
+        want = data[f"{name}_tokens{index}"].tolist()
+        assert greedy_generate(config, weights, data[f"{name}_prompt{index}"].tolist(), len(want)) == want
+        index += 1
+    assert index >= 3
