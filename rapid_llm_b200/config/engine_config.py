@@ -44,8 +44,11 @@ class EngineConfig:
             ``None`` sizes the pool from free device memory.
         max_num_seqs: Requests live at a time (= rows of the block tables).
         max_num_batched_tokens: Tokens one step may carry.
-        max_chunk_size: Largest portion of one prompt in a step.
-        enable_chunked_prefill: Cut prompts into portions; off = whole prompts only.
+        max_chunk_size: Largest portion of one prompt in a step; 0 is the reference's older way
+            of switching chunked prefill off and is folded into ``enable_chunked_prefill``.
+        enable_chunked_prefill: Cut prompts into portions; off = whole prompts only, and a step
+            must then be able to carry the longest prompt (``max_num_batched_tokens >=
+            max_seq_len``), or such a prompt would wait for ever.
         enable_preemption: Let a request that cannot grow evict the youngest one.
         memory_fraction: Share of the device's memory the cache may claim when
             ``num_pages`` is ``None``.
@@ -72,9 +75,21 @@ class EngineConfig:
 
     def __post_init__(self) -> None:
         parse_dtype(self.dtype)
-        for name in ("max_seq_len", "page_size", "max_num_seqs", "max_num_batched_tokens", "max_chunk_size"):
+        if self.max_seq_len < 2:
+            raise ValueError(f"max_seq_len must be >= 2 (a prompt token and a generated one), got {self.max_seq_len}")
+        for name in ("page_size", "max_num_seqs", "max_num_batched_tokens"):
             if getattr(self, name) < 1:
                 raise ValueError(f"{name} must be >= 1, got {getattr(self, name)}")
+        if self.max_chunk_size < 0:
+            raise ValueError(f"max_chunk_size must be >= 0, got {self.max_chunk_size}")
+        if self.max_chunk_size == 0:
+            object.__setattr__(self, "enable_chunked_prefill", False)
+        if not self.enable_chunked_prefill and self.max_num_batched_tokens < self.max_seq_len:
+            raise ValueError(
+                f"max_num_batched_tokens ({self.max_num_batched_tokens}) is smaller than max_seq_len "
+                f"({self.max_seq_len}) with chunked prefill off: a whole prompt must fit one step. Raise "
+                "max_num_batched_tokens, lower max_seq_len, or leave chunked prefill on."
+            )
         if self.num_pages is not None and self.num_pages < 1:
             raise ValueError(f"num_pages must be >= 1, got {self.num_pages}")
         if not 0.0 < self.memory_fraction <= 1.0:

@@ -150,13 +150,28 @@ def test_submission_checks():
 
 
 def test_whole_prompts_only_when_chunking_is_off():
-    scheduler, executor = make(enable_chunked_prefill=False, max_num_batched_tokens=64)
+    scheduler, executor = make(enable_chunked_prefill=False, max_seq_len=64, max_num_batched_tokens=64)
     scheduler.add_request(list(range(50)), greedy(1), "a")
     scheduler.add_request(list(range(40)), greedy(1), "b")
     scheduler.step()
     assert executor.steps[-1] == [("a", 0, 50, True)]                 # b does not fit the budget whole
     scheduler.step()
     assert executor.steps[-1] == [("b", 0, 40, True)]
+
+
+def test_limits_that_would_leave_a_prompt_waiting_for_ever_are_refused():
+    """With chunking off a step must hold the longest prompt; a chunk size of 0 is the older
+    switch for the same (``rapid_llm/engine/batch_planner.py:212-233``)."""
+    with pytest.raises(ValueError, match="chunked prefill off"):
+        EngineConfig(max_seq_len=256, max_num_batched_tokens=64, enable_chunked_prefill=False)
+    with pytest.raises(ValueError, match="chunked prefill off"):
+        EngineConfig(max_seq_len=256, max_num_batched_tokens=64, max_chunk_size=0)
+    folded = EngineConfig(max_seq_len=256, max_num_batched_tokens=256, max_chunk_size=0)
+    assert folded.enable_chunked_prefill is False
+    with pytest.raises(ValueError, match="max_seq_len"):
+        EngineConfig(max_seq_len=1)
+    with pytest.raises(ValueError, match="max_chunk_size"):
+        EngineConfig(max_chunk_size=-1)
 
 
 def test_the_references_calling_forms_are_taken():
