@@ -151,7 +151,14 @@ class LLM:
         if len(per_prompt) != len(prompts):
             raise ValueError("one SamplingParams for all prompts, or one per prompt")
         encoded = [self._encode(p) for p in prompts]
-        requests = [self.scheduler.add_request(ids, params) for (_, ids), params in zip(encoded, per_prompt)]
+        requests = []
+        try:
+            for (_, ids), params in zip(encoded, per_prompt):
+                requests.append(self.scheduler.add_request(ids, params))
+        except Exception:
+            for request in requests:          # a refused prompt takes the call's earlier ones with it
+                self.scheduler.abort(request)
+            raise
         return encoded, requests
 
     def stream(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None):

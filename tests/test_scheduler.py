@@ -174,6 +174,22 @@ def test_limits_that_would_leave_a_prompt_waiting_for_ever_are_refused():
         EngineConfig(max_chunk_size=-1)
 
 
+def test_a_refused_prompt_leaves_nothing_of_its_call_in_the_queue():
+    """``LLM.generate`` submits its prompts one by one; when one is refused, those before it must not
+    stay queued for the next call to run."""
+    from rapid_llm_b200.engine.llm import LLM
+
+    scheduler, executor = make()
+    llm = object.__new__(LLM)                          # the submission path alone: no device, no model
+    llm.scheduler, llm.tokenizer = scheduler, None
+    with pytest.raises(ValueError, match="empty"):
+        llm._submit([list(range(5)), list(range(9)), []], greedy(2))
+    assert not scheduler.has_unfinished() and not scheduler.waiting
+    _, requests = llm._submit([list(range(5))], greedy(2))
+    scheduler.run_to_completion()
+    assert requests[0].output_token_ids == [1000, 1001] and len(executor.steps) == 2
+
+
 def test_the_references_calling_forms_are_taken():
     """Text first and ids by keyword, ``sampling_params``, ``has_unfinished_requests``, abort by id
     (``rapid_llm/engine/scheduler.py:635-643``)."""
