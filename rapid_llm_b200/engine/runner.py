@@ -182,6 +182,10 @@ class ModelRunner:
             raise ValueError(f"step of {t} tokens exceeds max_num_batched_tokens {config.max_num_batched_tokens}")
         if len({entry.request_id for entry in entries}) != len(entries):
             raise ValueError("a request appears twice in one step")
+        for entry, length in zip(entries, lengths):      # refuse before any page is taken
+            for place in entry.want:
+                if not 0 <= place < length:
+                    raise ValueError(f"want index {place} outside the entry's {length} tokens")
 
         starts = [cache.num_tokens(entry.request_id) for entry in entries]
         short = [
@@ -254,8 +258,6 @@ class ModelRunner:
             for index in range(g):
                 kv_dest[index][at : at + length] = cache.kv_destinations(index, slot, start, length)
             for place in entry.want:
-                if not 0 <= place < length:
-                    raise ValueError(f"want index {place} outside the entry's {length} tokens")
                 logit_rows[row_at] = at + place
                 row_at += 1
             at += length
