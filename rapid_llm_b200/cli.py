@@ -87,7 +87,10 @@ def run_batch(args) -> int:
     except (ValueError, FileNotFoundError) as error:       # a refused option, a folder without a model
         raise SystemExit(f"rapid-llm-b200: {error}") from None
     started = time.perf_counter()
-    outputs = llm.generate(prompts, _sampling(args))
+    try:
+        outputs = llm.generate(prompts, _sampling(args))
+    except ValueError as error:                            # a refused prompt or sampling option
+        raise SystemExit(f"rapid-llm-b200: {error}") from None
     elapsed = time.perf_counter() - started
     return _report(args, outputs, started, elapsed)
 
