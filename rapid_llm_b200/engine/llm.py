@@ -115,7 +115,10 @@ class LLM:
         self.stop_token_ids = stops
         self.tokenizer = self._load_tokenizer(tokenizer or self.model_dir)
         self.executor = DeviceExecutor(self.runner)
-        self.scheduler = Scheduler(self.executor, self.engine_config, self.stop_token_ids)
+        self.scheduler = Scheduler(
+            self.executor, self.engine_config, self.stop_token_ids,
+            detokenize=self._decode if self.tokenizer is not None else None,
+        )
 
     @classmethod
     def from_runner(cls, runner: ModelRunner, stop_token_ids: Sequence[int] | None = None) -> "LLM":

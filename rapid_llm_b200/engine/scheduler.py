@@ -18,6 +18,11 @@ When pages run out:
   :class:`CacheExhausted` is raised rather than spinning;
 * a request that could never fit the pool even alone is refused when it is submitted.
 
+A request ends with ``"eos"`` (a stop token, which is not appended), ``"length"``, ``"abort"`` or,
+when the scheduler was given a detokenizer, ``"repeat"``: every eighth step the text of a request
+with ``stop_on_repeat`` is checked for a loop (``engine/repetition.py``), as the reference does
+(``rapid_llm/engine/scheduler.py:1398-1455``).
+
 Running ahead.  A step's sampled tokens stay on the device, where the next step's embedding
 can pick them up, so the next step can be planned and enqueued before the host has seen them:
 everything else a step needs (positions, pages, which rows to sample) follows from counts.
@@ -38,11 +43,12 @@ import time
 import zlib
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Hashable, Protocol, Sequence
+from typing import Callable, Hashable, Protocol, Sequence
 
 from ..cache import CacheManager
 from ..config import EngineConfig
 from ..sampling.params import SamplingParams
+from .repetition import CHECK_EVERY, text_repeats
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
@@ -132,8 +138,12 @@ class Executor(Protocol):
 
 
 class Scheduler:
-    def __init__(self, executor: Executor, config: EngineConfig, stop_token_ids: Sequence[int] = ()) -> None:
+    def __init__(self, executor: Executor, config: EngineConfig, stop_token_ids: Sequence[int] = (),
+                 detokenize: Callable[[list[int]], str] | None = None) -> None:
+        """``detokenize`` (token ids to text) switches the repeat breaker on for requests with
+        ``stop_on_repeat``; without it no request ends with the reason ``"repeat"``."""
         self.executor = executor
+        self.detokenize = detokenize
         self.cache = executor.cache
         self.config = config
         self.stop_token_ids = set(int(t) for t in stop_token_ids)
@@ -337,6 +347,7 @@ class Scheduler:
         """Read a launched step's tokens; put them in place of their stand-ins, finish and free."""
         sampled = self.executor.collect(inflight.handle) if self._can_launch else inflight.handle
         now = time.perf_counter()
+        look_for_loops = self.detokenize is not None and self.num_steps % CHECK_EVERY == 0
         finished: list[Request] = []
         for (request, index), token in zip(inflight.slots, sampled):
             if request.finished:
@@ -351,6 +362,10 @@ class Scheduler:
                 request.output_token_ids[index] = token
                 if request.exhausted and index == len(request.output_token_ids) - 1:
                     self._finish(request, "length", now)
+                elif look_for_loops and request.params.stop_on_repeat and text_repeats(
+                    self.detokenize(request.output_token_ids[: index + 1])
+                ):
+                    self._finish(request, "repeat", now)      # stand-ins of steps run ahead are dropped
             if request.finished:
                 finished.append(request)
         return finished

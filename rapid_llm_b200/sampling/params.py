@@ -4,8 +4,9 @@
 ``max_gen_len`` ``None`` fills the context; ``repetition_penalty`` > 0 with 1.0 off;
 values are validated at construction.  ``seed`` is an addition: draws come from a
 counter-based generator keyed by (seed, index of the generated token), so a request's
-tokens do not depend on what else is in the batch.  ``stop_on_repeat`` is accepted and
-inert: the reference's breaker looks at decoded text, which token-id requests do not have.
+tokens do not depend on what else is in the batch.  ``stop_on_repeat`` ends a request whose
+generated text loops (finish reason ``"repeat"``); the test is on decoded text, so it acts only
+when the model folder has a tokenizer, and requests of token ids alone are never ended by it.
 ``logprobs`` and ``prompt_logprobs`` (reporting, not sampling) are accepted only as ``None``;
 any other value is refused at construction rather than ignored.
 """

@@ -392,3 +392,52 @@ def test_random_arrivals_lengths_stops_and_aborts_lose_nothing(seed, ahead):
     if ahead:
         assert all(token >= 0 for fed in executor.fed for token in fed)
     assert executor.cache.num_free_pages() == pages and executor.cache.num_free_slots == 3
+
+
+# ------------------------------------------------------------------ the repeat breaker
+def test_the_repeat_breaker_agrees_with_the_references_own():
+    """``tests/golden/repetition.json`` holds the verdicts of the reference's ``detect_repetition``
+    (``rapid_llm/engine/stop_criteria.py:63-79``) on texts made by ``tests/golden/make_repetition_golden.py``."""
+    import json
+    from pathlib import Path
+
+    from rapid_llm_b200.engine.repetition import text_repeats
+
+    cases = json.loads((Path(__file__).parent / "golden" / "repetition.json").read_text())
+    assert len(cases) >= 50 and 5 <= sum(case["repeats"] for case in cases) <= len(cases) - 5
+    for number, case in enumerate(cases):
+        assert text_repeats(case["text"]) == case["repeats"], number
+
+
+def looping_text(token_ids):
+    """A stand-in tokenizer: 16 characters per token, the same again every 8 tokens, so the text
+    is a loop of 128 characters whatever the (all different) token ids are."""
+    return "".join(f"<piece {'abcdefgh'[token % 8]} of h>. " for token in token_ids)
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_a_request_whose_text_loops_ends_with_the_reason_repeat(ahead):
+    config = EngineConfig(max_seq_len=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=64,
+                          max_chunk_size=32, run_ahead=ahead)
+    executor = RunAheadExecutor(config, 64)
+    scheduler = Scheduler(executor, config, stop_token_ids=[7], detokenize=looping_text)
+    assert len(looping_text([1000])) == 16
+    looping = scheduler.add_request(list(range(5)), greedy(200), "loops")
+    deaf = scheduler.add_request(list(range(5)), SamplingParams(temperature=0.0, repetition_penalty=1.0,
+                                                                stop_on_repeat=False, max_gen_len=60), "deaf")
+    scheduler.run_to_completion()
+    # 512 characters (32 tokens) are the least the breaker looks at, and it looks every eighth step;
+    # running ahead, a step's tokens are read one step later
+    assert looping.finish_reason == "repeat"
+    assert len(looping.output_token_ids) == (39 if ahead else 32)
+    assert all(token >= 0 for token in looping.output_token_ids)
+    assert deaf.finish_reason == "length" and len(deaf.output_token_ids) == 60
+    assert executor.cache.num_free_pages() == 64 and executor.cache.num_free_slots == 4
+    executor.cache.check()
+
+
+def test_without_a_detokenizer_no_request_ends_for_repeating():
+    scheduler, executor = make()
+    request = scheduler.add_request(list(range(5)), greedy(80), "a")
+    scheduler.run_to_completion()
+    assert request.finish_reason == "length" and len(request.output_token_ids) == 80
