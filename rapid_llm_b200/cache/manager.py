@@ -65,15 +65,17 @@ class PagePool:
 
     def free(self, pages: Sequence[int]) -> None:
         """Give pages back; they are the next to be handed out."""
-        for page in pages:
-            if page == NULL_PAGE:
-                continue
+        real = [page for page in pages if page != NULL_PAGE]
+        for page in real:                       # check everything before anything changes
             if not 1 <= page <= self.num_pages:
                 raise CacheError(f"page {page} does not belong to this pool")
             if not self._held[page]:
                 raise CacheError(f"page {page} freed twice")
+        if len(set(real)) != len(real):
+            raise CacheError("a page is named twice in one free")
+        for page in real:
             self._held[page] = False
-        for page in reversed([p for p in pages if p != NULL_PAGE]):
+        for page in reversed(real):
             self._free.appendleft(page)
 
     def check(self) -> None:

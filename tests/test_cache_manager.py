@@ -31,6 +31,18 @@ def test_pool_all_or_nothing_and_double_free():
     pool.check()
 
 
+def test_a_refused_free_changes_nothing():
+    pool = PagePool(4)
+    pages = pool.allocate(3)
+    for bad in ([pages[0], pages[0]], [pages[1], 9], [pages[2], 4]):      # twice in one call, foreign, not held
+        with pytest.raises(CacheError):
+            pool.free(bad)
+        assert pool.num_free == 1
+        pool.check()
+    pool.free(pages)
+    assert pool.num_free == 4
+
+
 def test_groups_by_need():
     groups, entry_group = plan_groups([FULL, WIN, None, FULL, WIN, CacheNeed("full", 1, 32)])
     assert [g.entries for g in groups] == [(0, 3), (1, 4), (5,)]
