@@ -85,6 +85,8 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     final_norm_prefix: str = "model.norm."
+    embedding_prefix: str = "model.embed_tokens."
+    head_prefix: str = "lm_head."
 
     def validate(self) -> None:
         if not self.layers:

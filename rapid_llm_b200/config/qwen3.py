@@ -199,10 +199,12 @@ class Qwen3Config:
             unknown = sorted(set(self.layer_types) - {FULL_ATTENTION, SLIDING_ATTENTION})
             if unknown:
                 raise ValueError(f"unknown layer_types entries: {unknown}")
-        if self.layer_types:
+        if not self.use_sliding_window:
+            wants_window = False
+        elif self.layer_types:
             wants_window = SLIDING_ATTENTION in self.layer_types
         else:
-            wants_window = self.use_sliding_window and (self.max_window_layers or 0) < self.num_hidden_layers
+            wants_window = (self.max_window_layers or 0) < self.num_hidden_layers
         if wants_window and (self.sliding_window is None or self.sliding_window < 1):
             raise ValueError(
                 "sliding-window layers are configured but sliding_window is "
@@ -217,21 +219,21 @@ class Qwen3Config:
     def layer_windows(self) -> tuple[int, ...]:
         """Window of each layer in positions, the query's own included; 0 = all keys.
 
-        ``layer_types`` decides when present.  Otherwise windows exist only
-        under ``use_sliding_window`` and then on the layers from
-        ``max_window_layers`` upwards, which is how the architecture's own
-        configuration defines these keys.  The reference never reads them for
-        this model and always attends over everything
-        (``rapid_llm/engine/kv_cache_spec.py:383-387``), which is what every
+        Windows exist only under ``use_sliding_window`` with a ``sliding_window`` size: the switch is
+        the architecture's own, and with it off the size has no meaning whatever else is written.
+        Where they exist, ``layer_types`` names the layers that have one; without that key they are
+        the layers from ``max_window_layers`` upwards, which is how the architecture's own
+        configuration defines these keys.  The reference never reads them for this model and always
+        attends over everything (``rapid_llm/engine/kv_cache_spec.py:383-387``), which is what every
         published Qwen3 dense configuration (``use_sliding_window: false``) asks for.
         """
         window = self.sliding_window or 0
+        if not self.use_sliding_window or not window:
+            return (0,) * self.num_hidden_layers
         if self.layer_types:
             return tuple(
                 window if kind == SLIDING_ATTENTION else 0 for kind in self.layer_types
             )
-        if not self.use_sliding_window or not window:
-            return (0,) * self.num_hidden_layers
         first = self.max_window_layers if self.max_window_layers is not None else 0
         return tuple(window if index >= first else 0 for index in range(self.num_hidden_layers))
 
@@ -304,6 +306,9 @@ class Qwen3Config:
                     "tied": self.tie_word_embeddings,
                 },
             ),
+            final_norm_prefix="model.norm.",
+            embedding_prefix="model.embed_tokens.",
+            head_prefix="lm_head.",
         )
         spec.validate()
         return spec

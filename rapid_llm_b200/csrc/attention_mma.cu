@@ -485,8 +485,11 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_out,
   const float inv = total > 0.0f ? 1.0f / total : 0.0f;
   for (int c = lane; c < kD; c += 32) {
     float value = 0.0f;
-    for (int s = 0; s < splits; ++s)
+    for (int s = 0; s < splits; ++s) {
+      // a part without keys is not read: nothing wrote it, and 0 * (a NaN left there) would be NaN
+      if (lse[s] == -INFINITY) continue;
       value += exp2f(lse[s] - safe) * part_out[(row * splits + s) * kD + c];
+    }
     out[row * kD + c] = __float2bfloat16_rn(value * inv);
   }
 }
@@ -730,8 +733,8 @@ static int static_scratch_address(float** address) {
   return 0;
 }
 
-// lse[i] = -inf: a (row, split) slot that no work item of this call writes then weighs
-// nothing in the merge, whatever an earlier call left there.
+// lse[i] = -inf: the merge does not read the part of a (row, split) slot that no work item of this
+// call writes, so what an earlier call left there (finite or not) cannot reach the output.
 __global__ void static_scratch_reset_kernel(float* __restrict__ lse, long long count) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) lse[i] = -INFINITY;

@@ -23,7 +23,8 @@
 // refused with rl_attention_static_scratch_too_large (see the ..._strerror function) when
 // that exceeds the array; nothing is launched then.  All calls on a device use the same
 // array and it keeps whatever the previous call left, so the log-sum-exp slots the call
-// will read are reset on the stream before the attention kernels run.  Two calls that may
+// will read are reset on the stream before the attention kernels run, and the merge skips a
+// part whose slot stayed reset (leftovers that are not numbers do no harm either).  Two calls that may
 // execute at the same time on one GPU (different streams, no ordering between them) race
 // on the array: order them yourself.
 #pragma once

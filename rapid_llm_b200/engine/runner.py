@@ -48,6 +48,19 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+def decode_bucket(count: int, max_num_seqs: int, max_num_batched_tokens: int) -> int:
+    """The next power of two from ``count`` up, but never more rows than a step may carry: the padding
+    rows are tokens of the step like any other, so the bucket stays within both limits (a limit that
+    is no power of two is then a bucket of its own)."""
+    limit = min(max_num_seqs, max_num_batched_tokens)
+    if count > limit:
+        return count
+    bucket = 1
+    while bucket < count:
+        bucket *= 2
+    return min(bucket, limit)
+
+
 def require_cuda(device: torch.device) -> None:
     if device.type != "cuda" or not torch.cuda.is_available():
         raise RuntimeError(
@@ -367,10 +380,7 @@ class ModelRunner:
 
     def decode_bucket(self, count: int) -> int:
         """Batch size a decode-only step of ``count`` rows is padded to for graph replay."""
-        bucket = 1
-        while bucket < count:
-            bucket *= 2
-        return min(bucket, self.config.max_num_seqs) if count <= self.config.max_num_seqs else count
+        return decode_bucket(count, self.config.max_num_seqs, self.config.max_num_batched_tokens)
 
     @torch.no_grad()
     def step_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -34,11 +34,11 @@ class CausalLM:
     # -- weights ----------------------------------------------------------------- #
     def _owners(self):
         """``(prefix, part)`` for every part that owns checkpoint tensors."""
-        yield "model.embed_tokens.", self.embedding
+        yield self.spec.embedding_prefix, self.embedding
         for layer_spec, layer in zip(self.spec.layers, self.layers):
             yield layer_spec.prefix, layer
         yield self.spec.final_norm_prefix, self.final_norm
-        yield "lm_head.", self.head
+        yield self.spec.head_prefix, self.head
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Every checkpoint tensor by full name, in a fixed order."""

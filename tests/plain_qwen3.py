@@ -136,14 +136,15 @@ def decoder_layer(h, weights, prefix, cfg, positions, window):
 
 
 def layer_windows(config: dict) -> list[int]:
-    """Window per layer from the architecture's own keys: ``layer_types`` if present, else layers from
-    ``max_window_layers`` up when ``use_sliding_window``; 0 = attend to everything."""
+    """Window per layer from the architecture's own keys; 0 = attend to everything.  No windows unless
+    ``use_sliding_window`` is on and ``sliding_window`` gives a size; then on the layers that ``layer_types``
+    calls ``sliding_attention``, or without that key on the layers from ``max_window_layers`` up."""
     layers = config["num_hidden_layers"]
     window = config.get("sliding_window") or 0
-    if config.get("layer_types"):
-        return [window if kind == "sliding_attention" else 0 for kind in config["layer_types"]]
     if not config.get("use_sliding_window") or not window:
         return [0] * layers
+    if config.get("layer_types"):
+        return [window if kind == "sliding_attention" else 0 for kind in config["layer_types"]]
     first = config.get("max_window_layers") or 0
     return [window if index >= first else 0 for index in range(layers)]
 
@@ -162,23 +163,37 @@ def geometry(config: dict) -> dict:
 
 
 @torch.no_grad()
-def forward_logits(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=torch.float32) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence: embed, layers, final norm, head (rapid_llm/models/base.py:556-631);
-    a tied head uses the embedding matrix unless ``lm_head.weight`` is shipped (rapid_llm/models/weights.py:197-214)."""
-    weights = {name: value.to(dtype) if value.is_floating_point() else value for name, value in weights.items()}
+def forward_hidden(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=torch.float32) -> torch.Tensor:
+    """The residual stream [T, H] of one whole sequence after the last layer, before the final norm:
+    embed, then the layers in order (rapid_llm/models/base.py:556-631)."""
     cfg = geometry(config)
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.numel())
-    h = embed(ids, weights["model.embed_tokens.weight"])
+    h = embed(ids, weights["model.embed_tokens.weight"]).to(dtype)
     for index, window in enumerate(layer_windows(config)):
-        h = decoder_layer(h, weights, f"model.layers.{index}.", cfg, positions, window)
-    h = rms_norm(h, weights["model.norm.weight"], cfg["eps"])
+        prefix = f"model.layers.{index}."
+        layer = {name: value.to(dtype) for name, value in weights.items() if name.startswith(prefix)}
+        h = decoder_layer(h, layer, prefix, cfg, positions, window)
+    return h
+
+
+@torch.no_grad()
+def head_logits(config: dict, weights: dict[str, torch.Tensor], hidden: torch.Tensor) -> torch.Tensor:
+    """Final norm and output head over the given rows of the residual stream; a tied head uses the embedding
+    matrix unless ``lm_head.weight`` is shipped (rapid_llm/models/base.py:619-631, rapid_llm/models/weights.py:197-214)."""
+    h = rms_norm(hidden, weights["model.norm.weight"].to(hidden.dtype), config["rms_norm_eps"])
     head = weights.get("lm_head.weight")
     if head is None:
         if not config.get("tie_word_embeddings", False):
             raise KeyError("lm_head.weight is absent and the embeddings are not tied")
         head = weights["model.embed_tokens.weight"]
-    return h @ head.T
+    return h @ head.to(hidden.dtype).T
+
+
+def forward_logits(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=torch.float32, rows=None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence, or of its positions ``rows`` only."""
+    hidden = forward_hidden(config, weights, token_ids, dtype)
+    return head_logits(config, weights, hidden if rows is None else hidden[list(rows)])
 
 
 # ------------------------------------------------------------------------ sampling

@@ -48,6 +48,8 @@ def test_windows_per_layer():
     raw = dict(TINY_C, layer_types=None)
     assert Qwen3Config.from_dict(raw).layer_windows() == (0, 0, 40, 40)     # from max_window_layers upward
     assert Qwen3Config.from_dict(dict(raw, use_sliding_window=False)).layer_windows() == (0, 0, 0, 0)
+    # the switch decides: layer_types may name sliding layers, with the switch off nothing has a window
+    assert Qwen3Config.from_dict(dict(TINY_C, use_sliding_window=False)).layer_windows() == (0, 0, 0, 0)
     spec = Qwen3Config.from_dict(TINY_C).to_spec()
     assert [layer.mixer.params["window"] for layer in spec.layers] == [0, 40, 0, 40]
 

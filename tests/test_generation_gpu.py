@@ -64,6 +64,21 @@ def test_graph_and_eager_decode_agree(tiny_dirs):
     assert [o.token_ids for o in eager] == [o.token_ids for o in graph]
 
 
+def test_a_token_budget_below_the_number_of_slots(tiny_dirs, tiny_plain):
+    """Six tokens a step and eight slots: five requests decoding from a graph pad to six rows, within the
+    budget (the next power of two would not fit)."""
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain["A"]
+    prompts = random_prompts(config["vocab_size"], [2, 3, 2, 2, 3], 8)
+    llm = make_llm(tiny_dirs["A"], "float32", "A", max_num_seqs=8, max_num_batched_tokens=6, max_chunk_size=6,
+                   use_cuda_graph=True)
+    outputs = llm.generate(prompts, SamplingParams.greedy(max_gen_len=24))
+    for prompt, output in zip(prompts, outputs):
+        assert output.token_ids == greedy_generate(config, weights, prompt, 24)
+    assert 6 in llm.runner._graphs and 8 not in llm.runner._graphs
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_dirs, tiny_plain):
     from rapid_llm_b200 import SamplingParams
 

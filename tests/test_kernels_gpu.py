@@ -156,6 +156,64 @@ def test_gemm_bf16_inner_range_split_over_a_cluster(t, n, k_, swiglu, split):
     torch.testing.assert_close(outs[0].float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
 
 
+def device_rand(shape, scale, seed):
+    """Large operands are drawn on the device: a billion normal draws take the CPU tens of seconds."""
+    generator = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(shape, generator=generator, device=DEV) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("t,n,k_,swiglu", [
+    (1, 151936, 4096, False), (8, 151936, 4096, False), (64, 151936, 4096, False),     # the output head: 1,187 tiles
+    (33, 75000, 512, False),                       # 586 tiles of 64 tokens over fewer CTAs, short inner range
+    (2048, 6144, 4096, False),                     # 48 x 8 tiles of 256 tokens, one CTA per SM
+    (2048, 12288, 4096, True), (700, 9000, 1000, True),   # the fused SwiGLU's 128-token tiles, ragged edges
+    (300, 40000, 520, False),
+])
+def test_gemm_bf16_when_a_cta_walks_several_tiles(t, n, k_, swiglu):
+    """More tiles than CTAs: every CTA takes tile after tile, the accumulators alternate between two
+    tensor-memory buffers and the barriers' phases flip.  Each output is compared with the float32
+    product; an element's bound is the rounding of its bfloat16 store plus that of a float32 sum."""
+    x = device_rand((t, k_), 1.0, seed=40)
+    w = device_rand(((2 if swiglu else 1) * n, k_), 0.05, seed=41)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16(x, w, out, fault, swiglu=swiglu)
+    assert fault.item() == 0
+    step = 8192                                    # the float32 reference in slabs of output columns
+    for begin in range(0, n, step):
+        end = min(n, begin + step)
+        want = x.float() @ w[begin:end].float().T
+        if swiglu:
+            want = torch.nn.functional.silu(want) * (x.float() @ w[n + begin : n + end].float().T)
+        torch.testing.assert_close(out[:, begin:end].float(), want, rtol=6e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("t,n,k_,swiglu", [(16, 300, 1024, False), (64, 256, 4096, False), (40, 57100, 640, False),
+                                           (64, 200, 4096, True), (128, 260, 2048, False), (256, 300, 1024, False)])
+def test_gemm_bf16_every_block_of_the_inner_range_counts(t, n, k_, swiglu, split):
+    """Row ``r`` of the input is zero outside the 64 inner elements of block ``r mod blocks``: a block that
+    a CTA skips, reads twice or reads from the wrong stage changes a whole output row by its full size,
+    at every edge between the ranks of a split and in the last, partial, block."""
+    if t > 64 and split not in (0, 1):
+        pytest.skip("token tiles above 64 do not split the inner range")
+    blocks = -(-k_ // 64)
+    x = rand((t, k_), torch.bfloat16, seed=42)
+    keep = torch.zeros((t, k_), dtype=torch.bool)
+    for row in range(t):
+        block = row % blocks
+        keep[row, block * 64 : (block + 1) * 64] = True
+    x = torch.where(keep, x, torch.zeros_like(x)).to(DEV)
+    w = device_rand(((2 if swiglu else 1) * n, k_), 0.3, seed=43)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16(x, w, out, fault, swiglu=swiglu, k_split=split)
+    assert fault.item() == 0
+    want = bf16_product(x, w, n, swiglu)
+    assert float(want.abs().mean()) > 0.5          # a lost block is far outside the bound
+    torch.testing.assert_close(out.float(), want, rtol=6e-3, atol=2e-3)
+
+
 def test_gemm_bf16_rows_do_not_depend_on_the_batch_beyond_rounding():
     x = rand((40, 512), torch.bfloat16, seed=24).to(DEV)
     w = rand((300, 512), torch.bfloat16, scale=0.05, seed=25).to(DEV)

@@ -441,3 +441,17 @@ def test_without_a_detokenizer_no_request_ends_for_repeating():
     request = scheduler.add_request(list(range(5)), greedy(80), "a")
     scheduler.run_to_completion()
     assert request.finish_reason == "length" and len(request.output_token_ids) == 80
+
+
+def test_a_decode_bucket_stays_within_what_a_step_may_carry():
+    """Padding rows of a graph-replayed decode step count as tokens: the bucket never exceeds the token
+    budget (40 requests under a budget of 48 tokens pad to 48, not to 64) nor the number of slots."""
+    from rapid_llm_b200.engine.runner import decode_bucket
+
+    assert decode_bucket(40, 64, 48) == 48
+    assert decode_bucket(33, 64, 8192) == 64
+    assert decode_bucket(3, 64, 8192) == 4
+    assert decode_bucket(5, 6, 8192) == 6
+    assert decode_bucket(1, 64, 48) == 1
+    for count in range(1, 49):
+        assert count <= decode_bucket(count, 64, 48) <= 48

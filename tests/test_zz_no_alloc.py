@@ -85,8 +85,16 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row():
         ([1, 15, 129, 200, 700, 333], [1, 15, 40, 1, 1, 70], 3, 0, 5),
         ([900, 64, 257, 31], [1, 1, 1, 1], 4, 300, 6),       # decode only, other sizes, a window
     ]
-    for lengths, new_counts, splits, window, seed in runs:
+    for index, (lengths, new_counts, splits, window, seed) in enumerate(runs):
         case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=seed)
+        if index == 1:
+            # what the array holds from before is not always finite: a call on cached values that are not
+            # numbers leaves NaN in every part it writes, and the next call must not pick any of it up
+            first = runs[0]
+            poisoned = paged_case(dtype, hq, hkv, d, page, first[0], first[1], seed=first[4])
+            poisoned["cache"][:, 1] = float("nan")
+            code, got, _ = call_static(entry, poisoned, first[0], first[1], hq, hkv, d, scale, first[3], first[2])
+            assert code == 0 and torch.isnan(got).any()
         code, got, fault = call_static(entry, case, lengths, new_counts, hq, hkv, d, scale, window, splits)
         assert code == 0, lib.rl_attention_static_scratch_strerror(code).decode()
         assert fault == 0

@@ -3,33 +3,39 @@
 from __future__ import annotations
 
 import random
-from typing import Iterable
+from typing import Callable, Iterable
+
+Wanted = Callable[[int], bool] | None      # which positions of a sequence are asked for; None = all
 
 
-def whole(request_id: str, tokens: list[int], step: int = 0) -> list[dict]:
-    return [{"step": step, "entries": [{"id": request_id, "tokens": tokens, "want": list(range(len(tokens)))}],
+def _want(start: int, size: int, wanted: Wanted) -> list[int]:
+    return [place for place in range(size) if wanted is None or wanted(start + place)]
+
+
+def whole(request_id: str, tokens: list[int], step: int = 0, wanted: Wanted = None) -> list[dict]:
+    return [{"step": step, "entries": [{"id": request_id, "tokens": tokens, "want": _want(0, len(tokens), wanted)}],
              "end": [request_id]}]
 
 
-def tail_one_by_one(request_id: str, tokens: list[int], tail: int = 32, step: int = 0) -> list[dict]:
+def tail_one_by_one(request_id: str, tokens: list[int], tail: int = 32, step: int = 0, wanted: Wanted = None) -> list[dict]:
     """Most of the sequence in one step, the last ``tail`` tokens one by one."""
     tail = min(tail, len(tokens) - 1)
     head = tokens[: len(tokens) - tail]
-    records = [{"step": step, "entries": [{"id": request_id, "tokens": head, "want": list(range(len(head)))}], "end": []}]
+    records = [{"step": step, "entries": [{"id": request_id, "tokens": head, "want": _want(0, len(head), wanted)}], "end": []}]
     for offset, token in enumerate(tokens[len(head):]):
         records.append({"step": step + 1 + offset, "entries": [{"id": request_id, "tokens": [token], "want": [0]}], "end": []})
     records[-1]["end"] = [request_id]
     return records
 
 
-def portions(request_id: str, tokens: list[int], sizes: Iterable[int], step: int = 0) -> list[dict]:
-    """The sequence in portions of the given sizes (cycled), every position wanted."""
+def portions(request_id: str, tokens: list[int], sizes: Iterable[int], step: int = 0, wanted: Wanted = None) -> list[dict]:
+    """The sequence in portions of the given sizes (cycled)."""
     records, at, sizes = [], 0, list(sizes)
     index = 0
     while at < len(tokens):
         size = min(sizes[index % len(sizes)], len(tokens) - at)
         chunk = tokens[at : at + size]
-        records.append({"step": step + index, "entries": [{"id": request_id, "tokens": chunk, "want": list(range(size))}], "end": []})
+        records.append({"step": step + index, "entries": [{"id": request_id, "tokens": chunk, "want": _want(at, size, wanted)}], "end": []})
         at += size
         index += 1
     records[-1]["end"] = [request_id]
@@ -37,7 +43,7 @@ def portions(request_id: str, tokens: list[int], sizes: Iterable[int], step: int
 
 
 def mixed(sequences: dict[str, list[int]], seed: int, max_live: int = 4, page: int = 16,
-          prompt_fraction: float = 0.6) -> tuple[list[dict], int]:
+          prompt_fraction: float = 0.6, wanted: Wanted = None) -> tuple[list[dict], int]:
     """Up to ``max_live`` requests at a time: portions of some beside single tokens of others.
 
     Each request feeds the first ``prompt_fraction`` of its tokens in portions of random size
@@ -66,7 +72,7 @@ def mixed(sequences: dict[str, list[int]], seed: int, max_live: int = 4, page: i
                 size = 1
             size = min(size, len(tokens) - fed)
             chunk = tokens[fed : fed + size]
-            entries.append({"id": request_id, "tokens": chunk, "want": list(range(size))})
+            entries.append({"id": request_id, "tokens": chunk, "want": _want(fed, size, wanted)})
             live[request_id] = fed + size
             if live[request_id] == len(tokens):
                 ended.append(request_id)
