@@ -116,6 +116,8 @@ def plan_groups(needs: Sequence[CacheNeed | None]) -> tuple[list[GroupSpec], lis
             raise ValueError(f"unknown cache kind {need.kind!r}")
         if need.kind == "window" and need.window < 1:
             raise ValueError("a windowed cache needs window >= 1")
+        if need.elements_per_token() < 1:
+            raise ValueError("a cache need must give kv heads and a head size, or the shape of a token's row")
         key = need.group_key()
         if key not in keys:
             keys.append(key)
@@ -310,8 +312,3 @@ class CacheManager:
             raise CacheError("a slot is held twice or both held and free")
         if len(slots) + len(self._free_slots) != self.max_num_seqs:
             raise CacheError("a slot was lost")
-
-
-def state_layout(needs: Sequence[StateNeed | None]) -> list[StateNeed | None]:
-    """The per-request state each entry of the run order keeps (``None`` = none)."""
-    return list(needs)

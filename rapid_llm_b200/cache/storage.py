@@ -1,7 +1,9 @@
 """Device side of the cache: page tensors, block tables, per-request state tensors.
 
-Per group one tensor ``[entries, pages + 1, 2, kv_heads, page_size, head_dim]`` (page 0
-is the null page that padding and released table entries point at), one int32 block table
+Per group one tensor ``[entries, pages + 1, *page]`` where ``page`` is what the group's mixers
+asked for (``CacheNeed.page_shape``: a key and a value per kv head, ``[2, kv_heads, page_size, head_dim]``,
+unless the mixer names a row per token of its own); page 0
+is the null page that padding and released table entries point at, one int32 block table
 ``[slots, max_pages]`` mirrored from the host bookkeeping (the step function uploads the rows that changed with its metadata), and
 per run-order entry that asks for it one state tensor ``[slots, *shape]``, zeroed when a
 slot is handed to a new request.  The reference stores one row per token,
@@ -34,7 +36,7 @@ class CacheStorage:
         self.pages: list[torch.Tensor] = []
         for group, pool in zip(manager.groups, manager.pools):
             need = group.need
-            shape = (len(group.entries), pool.num_pages + 1, 2, need.num_kv_heads, manager.page_size, need.head_dim)
+            shape = (len(group.entries), pool.num_pages + 1, *need.page_shape(manager.page_size))
             self.pages.append(torch.zeros(shape, dtype=dtype, device=device))
         self.num_rows = manager.block_tables[0].shape[0] if manager.block_tables else manager.max_num_seqs
         self.block_tables = [

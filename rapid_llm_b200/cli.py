@@ -7,7 +7,9 @@ option names and defaults: ``--model-dir`` (or ``$RAPID_LLM_MODEL_DIR``), ``--ma
 ``--cuda-graph/--no-cuda-graph`` (on for ``batch``), ``--prompts-file``, ``--show-stats``.
 Added here: ``--prompt-ids-file`` (one prompt per line as token ids, for models without a
 tokenizer), ``--seed``, ``--dtype``, ``--page-size``, ``--max-num-batched-tokens``,
-``--max-chunk-size``.  ``random-init`` writes a seeded random model folder and ``replay``
+``--max-chunk-size``, ``--stop-token-ids`` (ids that end a request, added to those of the folder's
+``generation_config.json`` as the reference unions its sources, ``rapid_llm/engine/stop_criteria.py:29-54``;
+a folder of random weights has no such file).  ``random-init`` writes a seeded random model folder and ``replay``
 is ``bin/trace_run``.  The reference's ``chat``, ``vl-chat``, ``serve`` and
 ``acc.divergence`` commands (a REPL, vision, a server, a transformers diff) are not built.
 """
@@ -54,6 +56,8 @@ def _add_engine_options(sub: argparse.ArgumentParser) -> None:
     sub.add_argument("--page-size", type=int, default=16)
     sub.add_argument("--max-num-batched-tokens", type=int, default=8192)
     sub.add_argument("--max-chunk-size", type=int, default=512)
+    sub.add_argument("--stop-token-ids", default="", help="token ids that end a request, separated by commas or "
+                     "spaces; added to the eos ids of the folder's generation_config.json")
 
 
 def _model_dir(args) -> str:
@@ -95,6 +99,13 @@ def run_batch(args) -> int:
     return _report(args, outputs, started, elapsed)
 
 
+def _stop_token_ids(text: str) -> list[int]:
+    try:
+        return [int(token) for token in text.replace(",", " ").split()]
+    except ValueError:
+        raise SystemExit(f"rapid-llm-b200: --stop-token-ids takes integers, got {text!r}") from None
+
+
 def _build_llm(args):
     from .engine.llm import LLM
 
@@ -107,6 +118,7 @@ def _build_llm(args):
         tensor_parallel_size=args.tensor_parallel_size, enable_expert_parallel=args.enable_expert_parallel,
         prefill_context_parallel_size=args.prefill_context_parallel_size,
         decode_context_parallel_size=args.decode_context_parallel_size,
+        stop_token_ids=_stop_token_ids(args.stop_token_ids),
     )
 
 

@@ -68,6 +68,9 @@ struct GemmArgs {
   const float* sumsq_in;
   int sumsq_count;
   float norm_eps, inv_norm_size;
+  // added to every row of the result (after the open scale, before the SiLU or the residual add);
+  // [N], for SwiGLU [2 N] with the gate's part first; may be null
+  const float* bias;
 };
 
 __device__ __forceinline__ float silu_mul(float gate, float up) {
@@ -297,6 +300,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * Shape::kAccColumns + (static_cast<uint32_t>(quarter * 32) << 16);
+      const float bias_gate = args.bias != nullptr && n < args.N ? args.bias[n] : 0.0f;
+      const float bias_up = kSwiglu && args.bias != nullptr && n < args.N ? args.bias[args.up_offset + n] : 0.0f;
       if (args.k_split == 1) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
@@ -307,11 +312,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] *= row_scale[c + j];
           }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += bias_gate;
           if (kSwiglu) {
             float u[16];
             tmem_load16(acc + BN + c, u);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], scaled ? u[j] * row_scale[c + j] : u[j]);
+            for (int j = 0; j < 16; ++j) v[j] = silu_mul(v[j], (scaled ? u[j] * row_scale[c + j] : u[j]) + bias_up);
           }
           if (!kSwiglu && args.residual != nullptr) {
             const float norm_w = n < args.N ? args.norm_weight[n] : 0.0f;
@@ -367,6 +374,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const bool scaled = BN <= 64 && args.sumsq_in != nullptr;
       const bool norm_follows = !kSwiglu && args.residual != nullptr;
       const float norm_w = norm_follows && n < args.N ? args.norm_weight[n] : 0.0f;
+      const float bias_gate = args.bias != nullptr && n < args.N ? args.bias[n] : 0.0f;
+      const float bias_up = kSwiglu && args.bias != nullptr && n < args.N ? args.bias[args.up_offset + n] : 0.0f;
       for (int j = rank; j < BN && t0 + j < args.T; j += args.k_split) {
         // all loads first, the sums (in rank order) after: a remote load takes hundreds of cycles,
         // and a warp that adds each value as it arrives pays that once per rank
@@ -390,6 +399,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           gate *= row_scale[j];
           up *= row_scale[j];
         }
+        gate += bias_gate;
+        up += bias_up;
         if (norm_follows) {
           const float sq = warp_sum(n < args.N ? store_for_norm(args, at, norm_w, before + gate) : 0.0f);
           if (lane == 0)
@@ -503,10 +514,11 @@ extern "C" {
 // sumsq_out[tokens, rl_gemm_bf16_sumsq_count(n_out)] receives partial sums of the new residual's squares.
 // A norm that came before (`sumsq_in[tokens, sumsq_count]`, at most 64 tokens): row t of the result is
 // multiplied by rsqrt(sum(sumsq_in[t]) / norm_size + norm_eps).
+// `bias` (float32 [n_out], SwiGLU [2 n_out]; may be null) is added to every row after that scale.
 int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
                       int k_split, float* residual, const float* norm_weight, float* sumsq_out,
-                      const float* sumsq_in, int sumsq_count, float norm_eps, int norm_size, int* fault,
-                      cudaStream_t stream) {
+                      const float* sumsq_in, int sumsq_count, float norm_eps, int norm_size, const float* bias,
+                      int* fault, cudaStream_t stream) {
   if (tokens == 0 || n_out == 0) return 0;
   if (tokens < 0 || n_out < 0 || k <= 0 || k % 8 != 0 || k_split < 0 || k_split > 8 ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -540,6 +552,7 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
   args.sumsq_count = sumsq_count;
   args.norm_eps = norm_eps;
   args.inv_norm_size = norm_size > 0 ? 1.0f / static_cast<float>(norm_size) : 0.0f;
+  args.bias = bias;
 #define RL_GEMM_CASE(SW, BNV) \
   if ((swiglu != 0) == SW && bn == BNV) return rl::launch_gemm<SW, BNV>(map_w, map_x, args, k_split, stream);
   RL_GEMM_CASE(false, 16) RL_GEMM_CASE(false, 32) RL_GEMM_CASE(false, 64) RL_GEMM_CASE(false, 128)
@@ -552,7 +565,7 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
 int rl_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int swiglu, int pdl,
                  int k_split, int* fault, cudaStream_t stream) {
   return rl_gemm_bf16_norm(x, w, out, tokens, n_out, k, swiglu, pdl, k_split, nullptr, nullptr, nullptr, nullptr, 0,
-                           0.0f, 0, fault, stream);
+                           0.0f, 0, nullptr, fault, stream);
 }
 
 // columns of the table of partial sums of squares that a product of `n_out` output columns writes per token

@@ -61,6 +61,15 @@ def decode_bucket(count: int, max_num_seqs: int, max_num_batched_tokens: int) ->
     return min(bucket, limit)
 
 
+def pages_that_fit(free_bytes: int, fraction: float, page_bytes: int, reserve: int, cap: int) -> int:
+    """Cache pages for ``fraction`` of the free memory after ``reserve`` bytes are set aside for the
+    largest step's activations and logits; never more than ``cap`` (what the slots can hold at full
+    length), never fewer than one."""
+    usable = int(free_bytes * fraction) - int(reserve)
+    pages = usable // page_bytes if page_bytes > 0 else cap
+    return int(max(1, min(pages, cap)))
+
+
 def require_cuda(device: torch.device) -> None:
     if device.type != "cuda" or not torch.cuda.is_available():
         raise RuntimeError(
@@ -152,16 +161,13 @@ class ModelRunner:
     def _pages_from_free_memory(self, groups) -> int:
         free, _total = torch.cuda.mem_get_info(self.device)
         element = torch.empty((), dtype=self.dtype).element_size()
-        per_page = sum(
-            len(g.entries) * 2 * g.need.num_kv_heads * g.need.head_dim * self.config.page_size * element
-            for g in groups
+        per_page = sum(len(g.entries) * g.need.elements_per_token() * self.config.page_size * element for g in groups)
+        return pages_that_fit(
+            free, self.config.memory_fraction, per_page,
+            reserve=self.config.max_num_batched_tokens * self.model.activation_bytes_per_token()
+            + self.config.max_num_seqs * self.model.spec.vocab_size * (element + 4),
+            cap=self.config.max_num_seqs * self.config.max_pages_per_seq,
         )
-        # activations of the largest step: a rough bound, two wide buffers per token
-        reserve = self.config.max_num_batched_tokens * self.model.spec.hidden_size * element * 64
-        usable = int(free * self.config.memory_fraction) - reserve
-        pages = usable // max(per_page, 1) if per_page else 1
-        cap = self.config.max_num_seqs * self.config.max_pages_per_seq
-        return int(max(1, min(pages, cap)))
 
     # -- life of a request -------------------------------------------------------------- #
     def admit(self, request_id: Hashable) -> bool:

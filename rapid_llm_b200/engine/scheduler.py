@@ -200,10 +200,17 @@ class Scheduler:
         max_new = min(params.max_gen_len or room, room)
         page = self.cache.page_size
         most = len(prompt) + max_new - 1          # tokens cached when the last one is sampled
+        # the largest portion of it a step can carry; a windowed group holds at most its window, that
+        # portion and the ragged page at either end at a time, since passed pages are given back
+        portion = min(self.config.max_chunk_size, self.config.max_num_batched_tokens) if self.config.enable_chunked_prefill else len(prompt)
         for index, pool in enumerate(self.cache.pools):
-            if -(-most // page) > pool.num_pages:
+            window = self.cache.groups[index].window
+            pages = -(-most // page)
+            if window:
+                pages = min(pages, -(-(window + portion) // page) + 1)
+            if pages > pool.num_pages:
                 raise ValueError(
-                    f"the request needs {-(-most // page)} pages of cache group {index} by itself, "
+                    f"the request needs {pages} pages of cache group {index} by itself, "
                     f"the pool has {pool.num_pages}"
                 )
         if request_id is None:
@@ -285,7 +292,9 @@ class Scheduler:
         while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
             request = self.waiting[0]
             if request in plan.preempted:
-                break                               # evicted this very step: let it wait one
+                # evicted this very step: it waits one step, and so does everyone behind it, since it
+                # stands at the head of the queue and the queue never skips ahead
+                break
             size = self._chunk(request, budget)
             if size <= 0 or self.cache.num_free_slots == 0:
                 break

@@ -62,6 +62,13 @@ class CausalLM:
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for _, part in self._owners())
 
+    def activation_bytes_per_token(self) -> int:
+        """Bytes of activation buffers one token of a step needs: the widest layer's buffers (the layers
+        share them), the embedding's output and the float32 residual stream."""
+        element = torch.empty((), dtype=self.dtype).element_size()
+        widest = max(layer.workspace_elements_per_token() for layer in self.layers)
+        return (widest + 2 * self.spec.hidden_size) * element + 4 * self.spec.hidden_size
+
     # -- what the cache manager has to provide -------------------------------------- #
     def cache_needs(self) -> list[CacheNeed | None]:
         """One entry per position of the run order; ``None`` = no pages of its own."""

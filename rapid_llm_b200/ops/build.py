@@ -49,10 +49,10 @@ LIBRARIES: dict[str, list[str]] = {
 }
 LIBRARY_FLAGS: dict[str, list[str]] = {}
 
-# head sizes whose attention library `build_all` compiles ahead of time (the architecture's 128,
-# the common 64 and the tiny configurations of the tests and of the smoke run); any other
-# multiple of 16 up to 256 is compiled when a model with that head size is first built
-DEFAULT_HEAD_DIMS = (16, 32, 48, 64, 128)
+# head sizes whose attention library `build_all` compiles ahead of time unless told otherwise (the
+# architecture's 128 and the common 64); any other multiple of 16 up to 256 is compiled when a model
+# with that head size is first built
+DEFAULT_HEAD_DIMS = (64, 128)
 
 
 def attention_library(head_dim: int) -> str:
@@ -189,6 +189,9 @@ def build_library(name: str, extra_flags: list[str] | None = None) -> Path:
             raise BuildError(f"linking {target.name} failed:\n{proc.stdout}\n{proc.stderr}")
         os.replace(staged, target)  # atomic: a concurrent builder sees all or nothing
         _say(f"built {target.name}")
+        for older in out_dir.glob(f"librapid_llm_b200_{name}_*.so"):
+            if older != target:         # of sources that no longer exist; a process that has it loaded keeps it
+                older.unlink(missing_ok=True)
     finally:
         shutil.rmtree(work, ignore_errors=True)
     return target
@@ -206,8 +209,10 @@ def load_library(name: str) -> ctypes.CDLL:
         return _LOADED[name]
 
 
-def build_all() -> list[Path]:
-    """Compile every library (what ``__graft_entry__.build`` calls)."""
-    for head_dim in DEFAULT_HEAD_DIMS:
+def build_all(head_dims=None) -> list[Path]:
+    """Compile every library, the attention library for each of ``head_dims`` (default
+    :data:`DEFAULT_HEAD_DIMS`); several at a time."""
+    for head_dim in (DEFAULT_HEAD_DIMS if head_dims is None else head_dims):
         attention_library(head_dim)
-    return [build_library(name) for name in list(LIBRARIES)]
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        return list(pool.map(build_library, list(LIBRARIES)))

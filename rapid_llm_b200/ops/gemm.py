@@ -73,9 +73,20 @@ def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return x.shape[0] <= TENSOR_CORE_MAX_TOKENS
 
 
+_BIAS_IN_DTYPE: dict[tuple[int, torch.dtype], torch.Tensor] = {}
+
+
+def _bias_as(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 bias in the product's dtype for the library call (made once per vector)."""
+    key = (bias.data_ptr(), dtype)
+    if key not in _BIAS_IN_DTYPE:
+        _BIAS_IN_DTYPE[key] = bias.to(dtype)
+    return _BIAS_IN_DTYPE[key]
+
+
 def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | None = None, *,
-           then_norm: FollowingNorm | None = None):
-    """``out[T, N] = x[T, K] @ weight[N, K]^T``; all three on the GPU, same dtype.
+           then_norm: FollowingNorm | None = None, bias: torch.Tensor | None = None):
+    """``out[T, N] = x[T, K] @ weight[N, K]^T (+ bias[N], float32)``; all on the GPU, same dtype.
 
     ``x`` may be :class:`ScaledRows`.  With ``then_norm`` the product may take the norm along:
     it then returns :class:`ScaledRows` (the residual is updated, ``out`` is not written);
@@ -87,7 +98,7 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
     if x.dtype != weight.dtype or out.dtype != x.dtype:
         raise kernels.KernelError(f"linear: dtypes differ ({x.dtype}, {weight.dtype}, {out.dtype})")
     if x.dtype == torch.float32:
-        return kernels.gemm_f32(x, weight, out)
+        return kernels.gemm_f32(x, weight, out, bias)
     if x.shape[0] == 0:
         return out
     if fault is not None and use_tensor_core_kernel(x, weight):
@@ -97,12 +108,15 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
             normed = then_norm.workspace.get("normed", rows, width, x.dtype)
             sumsq = then_norm.workspace.get("normed_sumsq", rows, kernels.gemm_bf16_sumsq_count(width), torch.float32)
             kernels.gemm_bf16(x, weight, normed, fault, residual=then_norm.residual, norm_weight=then_norm.weight,
-                              sumsq_out=sumsq, **scale)
+                              sumsq_out=sumsq, bias=bias, **scale)
             return ScaledRows(normed, sumsq, then_norm.eps, width)
-        return kernels.gemm_bf16(x, weight, out, fault, **scale)
+        return kernels.gemm_bf16(x, weight, out, fault, bias=bias, **scale)
     if scale:
         raise kernels.KernelError("linear: rows with an open scale need the tensor-core product")
-    torch.mm(x, weight.t(), out=out)
+    if bias is None:
+        torch.mm(x, weight.t(), out=out)
+    else:
+        torch.addmm(_bias_as(bias, x.dtype), x, weight.t(), out=out)
     return out
 
 

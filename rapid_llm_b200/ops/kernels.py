@@ -461,7 +461,7 @@ def gemm_lib() -> ctypes.CDLL:
         lib.rl_gemm_bf16.restype = c_int
         lib.rl_gemm_bf16_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, ctypes.c_float, c_int,
-                                          c_void_p, c_void_p]
+                                          c_void_p, c_void_p, c_void_p]
         lib.rl_gemm_bf16_norm.restype = c_int
         lib.rl_gemm_bf16_sumsq_count.argtypes = [c_int]
         lib.rl_gemm_bf16_sumsq_count.restype = c_int
@@ -485,7 +485,7 @@ def gemm_bf16_sumsq_count(n_out: int) -> int:
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor, *, swiglu: bool = False,
               k_split: int = 0, residual: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
               sumsq_out: torch.Tensor | None = None, sumsq_in: torch.Tensor | None = None,
-              norm_eps: float = 0.0, norm_size: int = 0) -> torch.Tensor:
+              norm_eps: float = 0.0, norm_size: int = 0, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``out[T, N] = x[T, K] @ w[N, K]^T`` in bfloat16 on the tcgen05 tensor cores.
 
     With ``swiglu``, ``w`` is ``[2 N, K]`` (gate rows, then up rows) and
@@ -498,9 +498,14 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
     ``out = residual * norm_weight`` and ``sumsq_out`` receives partial sums of the new
     residual's squares.  With ``sumsq_in`` (such a table), ``norm_eps`` and ``norm_size``, row
     ``t`` of the product is multiplied by ``rsqrt(sum(sumsq_in[t]) / norm_size + norm_eps)``
-    (before the SiLU): the scale that the norm before ``x`` left open.
+    (before the SiLU): the scale that the norm before ``x`` left open.  ``bias`` (float32 ``[N]``, with
+    ``swiglu`` ``[2 N]``) is added to every row after that scale.
     """
-    _need_cuda(x, w, out, fault, residual, norm_weight, sumsq_out, sumsq_in)
+    _need_cuda(x, w, out, fault, residual, norm_weight, sumsq_out, sumsq_in, bias)
+    if bias is not None:
+        _expect("bias", bias, torch.float32), _contig("bias", bias)
+        if bias.shape != (w.shape[0],):
+            raise KernelError(f"gemm_bf16: bias of shape {tuple(bias.shape)} for a weight of {w.shape[0]} rows")
     for name, tensor in (("x", x), ("w", w), ("out", out)):
         _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
     tokens, k = x.shape
@@ -531,7 +536,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
             _ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL), int(k_split),
             _ptr(residual), _ptr(norm_weight), _ptr(sumsq_out),
             _ptr(sumsq_in), 0 if sumsq_in is None else sumsq_in.shape[1], float(norm_eps), int(norm_size),
-            _ptr(fault), _stream(),
+            _ptr(bias), _ptr(fault), _stream(),
         ),
         f"gemm_bf16({tokens}x{k} by {n_out})",
     )

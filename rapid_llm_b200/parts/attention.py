@@ -8,7 +8,9 @@ every query over its request's cached keys with ``kv_head = q_head // group`` an
 ``head_dim ** -0.5`` (``:62``), output projection without bias.
 
 Every size is a constructor parameter; the window (0 = all keys) and whether q/k are
-normed differ per layer if the specification says so.  A layer that reads another entry's
+normed differ per layer if the specification says so, and so does ``qkv_bias`` (a bias on the
+q, k and v projections, which this architecture does not have and its predecessor has; added in
+float32 in the product's epilogue).  A layer that reads another entry's
 cache (``cache.writes`` false) projects queries only.
 """
 
@@ -23,8 +25,7 @@ from .base import (
     MATRIX, MIXERS, POSITION_ENCODINGS, VECTOR, CacheNeed, Mixer, StepPlanner, StepShape, TensorSpec,
 )
 
-TARGET_CTAS = 2 * 148     # work items the attention kernels want in flight on a B200
-DECODE_TARGET_CTAS = 148  # ... in a decode-only step, whose kernel keeps a whole SM's shared memory busy
+DEFAULT_SMS = 148         # a B200's; planning on the host without a device (tests) assumes it
 MAX_SPLITS = 16
 CLUSTER_SPLITS = 8        # the portable size of a thread-block cluster
 TC_CHUNK_MIN_CTAS = 32    # measured: from here on the unsplit tcgen05 chunk kernel beats the split mma.sync tiles
@@ -51,14 +52,17 @@ class AttentionItems(StepPlanner):
     (``rapid_llm/kernels/ops/attention/flashdecoding.py:43-112``).
     """
 
-    def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0) -> None:
+    def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0, sms: int = DEFAULT_SMS) -> None:
         self.group, self.num_kv_heads, self.head_dim = int(group), int(num_kv_heads), int(head_dim)
-        self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim)
+        # work items the kernels want in flight: two CTAs per multiprocessor, one in a decode-only
+        # step, whose kernel keeps a whole multiprocessor's shared memory busy
+        self.target_ctas, self.decode_target_ctas = 2 * int(sms), int(sms)
+        self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim, int(sms))
 
     def capacity(self, max_tokens: int, max_entries: int) -> int:
         chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
         decode_tiles = max_entries * -(-self.group // kernels.DECODE_TILE_ROWS)
-        return 4 * (chunk_tiles + decode_tiles + 2 * TARGET_CTAS)
+        return 4 * (chunk_tiles + decode_tiles + 2 * self.target_ctas)
 
     def plan(self, shape: StepShape) -> dict:
         lengths = np.asarray(shape.lengths, dtype=np.int64)
@@ -70,7 +74,7 @@ class AttentionItems(StepPlanner):
             tile_rows = np.where(is_decode, kernels.DECODE_TILE_ROWS, chunk_rows)
             tiles = -(-rows // tile_rows)
             ctas = int(tiles.sum()) * self.num_kv_heads
-            target = DECODE_TARGET_CTAS if shape.decode_only else TARGET_CTAS
+            target = self.decode_target_ctas if shape.decode_only else self.target_ctas
             splits = max(1, min(MAX_SPLITS, target // max(ctas, 1)))
             if not shape.decode_only:
                 longest = int((starts + lengths).max())
@@ -128,6 +132,7 @@ class GQAAttention(Mixer):
         window: int = 0,
         scale: float | None = None,
         shares_cache: bool = False,
+        qkv_bias: bool = False,
         dtype,
         device,
     ) -> None:
@@ -142,13 +147,16 @@ class GQAAttention(Mixer):
         self.window = int(window)
         self.scale = float(scale) if scale is not None else self.d**-0.5
         self.shares_cache = bool(shares_cache)
-        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d)
+        device = torch.device(device)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count if device.type == "cuda" else DEFAULT_SMS
+        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", self.d))
 
         kv_rows = 0 if self.shares_cache else 2 * self.hkv * self.d
         self.qkv = self.new_storage((self.hq * self.d + kv_rows, self.hidden), MATRIX)
         self.o = self.new_storage((self.hidden, self.hq * self.d), MATRIX)
+        self.qkv_bias = self.new_storage((self.qkv.shape[0],), VECTOR) if qkv_bias else None
         self.q_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm else None
         self.k_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm and not self.shares_cache else None
 
@@ -171,6 +179,9 @@ class GQAAttention(Mixer):
         if not self.shares_cache:
             specs["k_proj.weight"] = TensorSpec((self.hkv * self.d, self.hidden))
             specs["v_proj.weight"] = TensorSpec((self.hkv * self.d, self.hidden))
+        if self.qkv_bias is not None:
+            for name in ("q_proj", "k_proj", "v_proj")[: 1 if self.shares_cache else 3]:
+                specs[f"{name}.bias"] = TensorSpec((specs[f"{name}.weight"].shape[0],), VECTOR)
         if self.qk_norm:
             specs["q_norm.weight"] = TensorSpec((self.d,), VECTOR, init="ones_normal")
             if not self.shares_cache:
@@ -187,6 +198,12 @@ class GQAAttention(Mixer):
             self.qkv[q_rows + kv_rows :].copy_(tensor)
         elif name == "o_proj.weight":
             self.o.copy_(tensor)
+        elif name == "q_proj.bias":
+            self.qkv_bias[:q_rows].copy_(tensor.to(torch.float32))
+        elif name == "k_proj.bias":
+            self.qkv_bias[q_rows : q_rows + kv_rows].copy_(tensor.to(torch.float32))
+        elif name == "v_proj.bias":
+            self.qkv_bias[q_rows + kv_rows :].copy_(tensor.to(torch.float32))
         elif name == "q_norm.weight":
             self.q_norm.copy_(tensor.to(torch.float32))
         elif name == "k_norm.weight":
@@ -196,10 +213,13 @@ class GQAAttention(Mixer):
 
     def parameter_bytes(self) -> int:
         total = (self.qkv.numel() + self.o.numel()) * self.qkv.element_size()
-        for vector in (self.q_norm, self.k_norm):
+        for vector in (self.q_norm, self.k_norm, self.qkv_bias):
             if vector is not None:
                 total += vector.numel() * 4
         return total
+
+    def workspace_elements_per_token(self) -> int:
+        return self.qkv.shape[0] + 2 * self.hq * self.d + self.hidden      # qkv, q, attended, projected
 
     # -- forward --------------------------------------------------------------- #
     def forward(self, x, batch, cache, then_norm=None):
@@ -210,7 +230,7 @@ class GQAAttention(Mixer):
         group = batch.groups[cache.group]
         rows = x.shape[0]
         qkv = batch.workspace.get("attn_qkv", rows, self.qkv.shape[0], x.dtype)
-        gemm.linear(x, self.qkv, qkv, batch.fault)
+        gemm.linear(x, self.qkv, qkv, batch.fault, bias=self.qkv_bias)
         q = batch.workspace.get("attn_q", rows, self.hq * self.d, x.dtype)
         cos, sin = self.position.tables()
         kernels.qk_norm_rope_write(

@@ -55,15 +55,36 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Pages a mixer wants: ``kind`` is ``"full"`` (all keys) or ``"window"``."""
+    """Pages a mixer wants.
+
+    ``kind`` says which positions are kept: ``"full"`` (all of them) or ``"window"`` (the last
+    ``window``).  What a page holds is the mixer's business: by default a key and a value per kv
+    head, ``[2, num_kv_heads, page_size, head_dim]``; a mixer that caches something else (one
+    latent row per token, keys without values) names the shape of one token's row in
+    ``token_shape`` and gets pages ``[page_size, *token_shape]``.
+    """
 
     kind: str
-    num_kv_heads: int
-    head_dim: int
+    num_kv_heads: int = 0
+    head_dim: int = 0
     window: int = 0
+    token_shape: tuple[int, ...] | None = None
 
     def group_key(self) -> tuple:
-        return (self.kind, self.window, self.num_kv_heads, self.head_dim)
+        return (self.kind, self.window, self.num_kv_heads, self.head_dim, self.token_shape)
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        if self.token_shape is not None:
+            return (page_size, *self.token_shape)
+        return (2, self.num_kv_heads, page_size, self.head_dim)
+
+    def elements_per_token(self) -> int:
+        if self.token_shape is not None:
+            count = 1
+            for extent in self.token_shape:
+                count *= int(extent)
+            return count
+        return 2 * self.num_kv_heads * self.head_dim
 
 
 @dataclass(frozen=True)
@@ -126,6 +147,11 @@ class Part:
         """Called once after loading, with the names that were present."""
 
     def parameter_bytes(self) -> int:
+        return 0
+
+    def workspace_elements_per_token(self) -> int:
+        """Elements of the engine dtype this part's activation buffers hold per token of a step
+        (for sizing the cache pool from free memory; 0 = negligible or unknown)."""
         return 0
 
     # -- helpers ------------------------------------------------------------ #

@@ -80,6 +80,9 @@ class PreNormBlock(Block):
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for _, part in self._children())
 
+    def workspace_elements_per_token(self) -> int:
+        return sum(part.workspace_elements_per_token() for _, part in self._children())
+
     def leading_norm(self):
         return self.mixer_norm if self.mixer.rides_norms else None
 

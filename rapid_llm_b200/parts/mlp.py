@@ -48,6 +48,9 @@ class SwiGLU(FeedForward):
     def parameter_bytes(self) -> int:
         return (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
 
+    def workspace_elements_per_token(self) -> int:
+        return 3 * self.inter + self.hidden          # gate and up of a library-product step, act, out
+
     def forward(self, x, batch, then_norm=None):
         rows = x.shape[0]
         act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)

@@ -35,6 +35,9 @@ class RMSNorm(Norm):
     def parameter_bytes(self) -> int:
         return self.weight.numel() * 4
 
+    def workspace_elements_per_token(self) -> int:
+        return self.size
+
     def following(self, residual: torch.Tensor, batch) -> gemm.FollowingNorm | None:
         """This norm of ``residual + (a product's result)``, as an offer to that product."""
         if self.dtype != torch.bfloat16 or residual is None:

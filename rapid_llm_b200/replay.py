@@ -12,7 +12,10 @@ Steps are read from standard input, one JSON object a line::
 All entries of a step run as one batch.  A request is admitted when its id is first seen
 and gives back what it holds when a step lists it under ``end``.  For a step in which
 something is wanted, ``OUT/<step>.f32`` receives the logits at the wanted places, in the
-order of the entries and of ``want``, as little-endian float32 ``[wanted, vocab]``.  After
+order of the entries and of ``want``, as little-endian float32 ``[wanted, vocab]``.  Every
+step also writes ``OUT/<step>.pages.json``: for each request of the step, the page ids it held
+after the step, one list per cache group in position order (0 = a page given back because the
+window has passed it), so that a reader can see pages used again.  After
 every step ``done <step>`` is printed and flushed.  ``--max-tokens`` sizes the cache pool:
 the most tokens live requests hold at any time, each request's count rounded up to a whole
 number of pages.
@@ -52,6 +55,7 @@ class Replayer:
         self.runner = runner
         self.out_dir = out_dir
         self._staging = None
+        self.last_pages: dict[str, list[list[int]]] = {}
 
     def run_step(self, record: dict) -> np.ndarray | None:
         """Run one record; returns (and, with ``out_dir``, writes) the wanted logits."""
@@ -79,6 +83,10 @@ class Replayer:
                 if self.out_dir is not None:
                     host.tofile(self.out_dir / f"{step}.f32")
             runner.check_fault()
+        self.last_pages = {str(entry.request_id): [list(map(int, group)) for group in runner.cache.pages_of(entry.request_id)]
+                           for entry in entries}
+        if self.out_dir is not None:
+            (self.out_dir / f"{step}.pages.json").write_text(json.dumps(self.last_pages))
         for request_id in record.get("end", []):
             if runner.cache.has(request_id):
                 runner.release(request_id)

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from rapid_llm_b200.ops import kernels
-from rapid_llm_b200.parts.attention import DECODE_TARGET_CTAS, MAX_SPLITS, AttentionItems
+from rapid_llm_b200.parts.attention import DEFAULT_SMS, MAX_SPLITS, AttentionItems
 from rapid_llm_b200.parts.base import StepShape
 
 
@@ -49,7 +49,7 @@ def test_a_decode_only_step_splits_by_the_number_of_entries_alone():
     planner = AttentionItems(4, 8)
     short = planner.plan(StepShape(np.ones(4, np.int32), np.full(4, 3, np.int32), decode_only=True))
     long = planner.plan(StepShape(np.ones(4, np.int32), np.full(4, 7000, np.int32), decode_only=True))
-    assert short["splits"] == long["splits"] == min(MAX_SPLITS, DECODE_TARGET_CTAS // (4 * 8))
+    assert short["splits"] == long["splits"] == min(MAX_SPLITS, DEFAULT_SMS // (4 * 8))
     assert np.array_equal(short["decode_items"], long["decode_items"])
     full = planner.plan(StepShape(np.ones(64, np.int32), np.full(64, 1000, np.int32), decode_only=True))
     assert full["splits"] == 1

@@ -153,3 +153,31 @@ def test_dirty_rows_are_reported_once():
     assert cache.take_dirty(0) == []            # same page: the row did not change
     cache.reserve("a", 17)
     assert cache.take_dirty(0) == [0]
+
+
+def test_pages_sized_from_free_memory():
+    """The pool takes the given share of free memory after the largest step's buffers are set aside,
+    is capped by what the slots can hold, and is never empty."""
+    from rapid_llm_b200.engine.runner import pages_that_fit
+
+    gib = 1 << 30
+    page = 36 * 2 * 8 * 128 * 16 * 2                       # a page of 16 tokens over 36 layers of 8 x 128 keys and values
+    assert pages_that_fit(100 * gib, 0.9, page, reserve=4 * gib, cap=10**9) == (90 * gib - 4 * gib) // page
+    assert pages_that_fit(100 * gib, 0.9, page, reserve=4 * gib, cap=1000) == 1000
+    assert pages_that_fit(1 * gib, 0.5, page, reserve=2 * gib, cap=1000) == 1      # nothing left: one page, and the step fails loudly
+    assert pages_that_fit(100 * gib, 1.0, 0, reserve=0, cap=77) == 77               # no mixer keeps pages
+
+
+def test_a_cache_need_with_a_row_of_its_own_per_token():
+    from rapid_llm_b200.cache.manager import plan_groups
+    from rapid_llm_b200.parts.base import CacheNeed
+
+    keys_and_values = CacheNeed("full", 2, 64)
+    latent = CacheNeed("full", token_shape=(72,))
+    assert keys_and_values.page_shape(16) == (2, 2, 16, 64) and keys_and_values.elements_per_token() == 256
+    assert latent.page_shape(16) == (16, 72) and latent.elements_per_token() == 72
+    groups, entry_group = plan_groups([keys_and_values, latent, None, latent, keys_and_values])
+    assert entry_group == [0, 1, None, 1, 0] and [g.entries for g in groups] == [(0, 4), (1, 3)]
+    import pytest
+    with pytest.raises(ValueError, match="token's row"):
+        plan_groups([CacheNeed("full")])

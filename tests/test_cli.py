@@ -24,7 +24,7 @@ def test_batch_takes_the_references_options():
     text = run_cli("batch", "--help").stdout
     for flag in ("--model-dir", "--max-seq-len", "--max-gpu-num-blocks", "--device", "--temperature", "--top-p",
                  "--max-gen-len", "--repetition-penalty", "--quantization", "--kv-cache-dtype", "--tensor-parallel-size",
-                 "--prompts-file", "--max-num-seqs", "--show-stats", "--cuda-graph", "--no-cuda-graph"):
+                 "--prompts-file", "--max-num-seqs", "--show-stats", "--cuda-graph", "--no-cuda-graph", "--stop-token-ids"):
         assert flag in text, flag
 
 
@@ -48,6 +48,8 @@ def test_random_init_writes_a_model_folder(tmp_path):
 def test_an_option_for_what_is_not_built_ends_with_a_message(tmp_path):
     done = run_cli("batch", "--model-dir", str(tmp_path), "--tensor-parallel-size", "2", check=False)
     assert done.returncode != 0 and "tensor_parallel_size=2" in done.stderr and "Traceback" not in done.stderr
+    words = run_cli("batch", "--model-dir", str(tmp_path), "--stop-token-ids", "7,eos", check=False)
+    assert words.returncode != 0 and "--stop-token-ids" in words.stderr and "Traceback" not in words.stderr
     missing = run_cli("batch", check=False)
     assert missing.returncode != 0 and "model-dir" in missing.stderr
 

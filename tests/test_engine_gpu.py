@@ -98,7 +98,7 @@ def test_whole_tail_and_portions(name, dtype, models):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-def test_mixed_with_pages_used_again(name, dtype, models):
+def test_mixed_with_pages_used_again(name, dtype, models, tmp_path):
     dirs, plains = models[dtype]
     config, weights = plains[name]
     limit = config["max_position_embeddings"]
@@ -110,22 +110,25 @@ def test_mixed_with_pages_used_again(name, dtype, models):
     }
     records, peak = mixed(sequences, seed=7, max_live=4, page=page)
     runner = make_runner(dirs[name], dtype, max_tokens=peak, page_size=page, max_live=4)
-    seen_pages: dict[int, set[str]] = {}
     from rapid_llm_b200.replay import Replayer
 
-    replayer, outputs = Replayer(runner), {}
+    replayer, outputs = Replayer(runner, tmp_path), {}
     for record in records:
-        out = replayer.run_step(dict(record, end=[]))
+        out = replayer.run_step(record)
         if out is not None:
             outputs[record["step"]] = torch.from_numpy(out.copy())
-        for entry in record["entries"]:
-            for page_id in runner.cache.pages_of(entry["id"])[0]:
-                if page_id:
-                    seen_pages.setdefault(page_id, set()).add(entry["id"])
-        for request_id in record["end"]:
-            runner.release(request_id)
         runner.cache.check()
-    assert any(len(owners) > 1 for owners in seen_pages.values()), "no page was used again"
+    # which request held which page, read from the files the replay wrote beside the logits
+    owners: dict[tuple[int, int], set[str]] = {}
+    for record in records:
+        held = json.loads((tmp_path / f"{record['step']}.pages.json").read_text())
+        assert set(held) == {entry["id"] for entry in record["entries"]}
+        for request_id, groups in held.items():
+            for group, pages in enumerate(groups):
+                for page_id in pages:
+                    if page_id:
+                        owners.setdefault((group, page_id), set()).add(request_id)
+    assert any(len(requests) > 1 for requests in owners.values()), "no page was used again"
     plain = {rid: forward_logits(config, weights, tokens) for rid, tokens in sequences.items()}
     compare(collect(records, outputs), plain, dtype)
 

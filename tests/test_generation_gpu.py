@@ -64,6 +64,42 @@ def test_graph_and_eager_decode_agree(tiny_dirs):
     assert [o.token_ids for o in eager] == [o.token_ids for o in graph]
 
 
+def test_the_command_line_from_a_folder_to_token_ids(tiny_dirs, tiny_plain, tmp_path):
+    """``python -m rapid_llm_b200.cli batch --prompt-ids-file``: a model folder and a file of prompts in, the
+    plain implementation's greedy tokens out; with ``--stop-token-ids`` a request ends at that token."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    config, weights = tiny_plain["A"]
+    prompts = random_prompts(config["vocab_size"], [5, 17, 33], 1)
+    ids_file = tmp_path / "prompts.txt"
+    ids_file.write_text("".join(" ".join(map(str, prompt)) + "\n" for prompt in prompts))
+    root = Path(__file__).resolve().parents[1]
+    base = [sys.executable, "-m", "rapid_llm_b200.cli", "batch", "--model-dir", str(tiny_dirs["A"]), "--dtype", "float32",
+            "--prompt-ids-file", str(ids_file), "--temperature", "0", "--repetition-penalty", "1.0", "--max-gen-len", "8",
+            "--max-seq-len", "128", "--max-gpu-num-blocks", "32", "--max-num-seqs", "4", "--max-chunk-size", "13",
+            "--max-num-batched-tokens", "64"]
+
+    def run(*extra):
+        done = subprocess.run(base + list(extra), cwd=root, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        blocks = done.stdout.split("--- [")[1:]           # "0] reason ---\n<ids or nothing>\n"
+        reasons = [block.split()[1] for block in blocks]
+        tokens = [[int(t) for t in block.split("---", 1)[1].split()] for block in blocks]
+        return reasons, tokens
+
+    want = [greedy_generate(config, weights, prompt, 8) for prompt in prompts]
+    reasons, tokens = run()
+    assert tokens == want and reasons == ["length"] * 3
+    stop = next(token for full in want for place, token in enumerate(full) if place and token not in full[:place])
+    reasons, tokens = run("--stop-token-ids", f"{stop}, 100000")
+    assert any(stop in full for full in want)
+    for reason, got, full in zip(reasons, tokens, want):
+        cut = full.index(stop) if stop in full else len(full)
+        assert got == full[:cut] and reason == ("eos" if stop in full else "length")
+
+
 def test_a_token_budget_below_the_number_of_slots(tiny_dirs, tiny_plain):
     """Six tokens a step and eight slots: five requests decoding from a graph pad to six rows, within the
     budget (the next power of two would not fit)."""

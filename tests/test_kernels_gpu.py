@@ -156,6 +156,28 @@ def test_gemm_bf16_inner_range_split_over_a_cluster(t, n, k_, swiglu, split):
     torch.testing.assert_close(outs[0].float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
 
 
+@pytest.mark.parametrize("split", [0, 1, 4])
+@pytest.mark.parametrize("t,n,k_,swiglu", [(1, 130, 64, False), (8, 384, 1024, False), (40, 200, 520, True),
+                                           (64, 256, 2048, True), (200, 300, 264, False), (300, 140, 512, True)])
+def test_gemm_bf16_adds_a_bias(t, n, k_, swiglu, split):
+    """A float32 bias per output column, for the fused SwiGLU per gate and per up column, added before the
+    SiLU: in the direct epilogue and in the cluster's reduction."""
+    if t > 64 and split > 1:
+        pytest.skip("token tiles above 64 do not split the inner range")
+    x = rand((t, k_), torch.bfloat16, seed=44).to(DEV)
+    rows = (2 if swiglu else 1) * n
+    w = rand((rows, k_), torch.bfloat16, scale=0.05, seed=45).to(DEV)
+    bias = rand((rows,), torch.float32, scale=2.0, seed=46).to(DEV)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16(x, w, out, fault, swiglu=swiglu, k_split=split, bias=bias)
+    assert fault.item() == 0
+    want = x.float() @ w.float().T + bias
+    if swiglu:
+        want = torch.nn.functional.silu(want[:, :n]) * want[:, n:]
+    torch.testing.assert_close(out.float(), want, rtol=6e-3, atol=2e-3)
+
+
 def device_rand(shape, scale, seed):
     """Large operands are drawn on the device: a billion normal draws take the CPU tens of seconds."""
     generator = torch.Generator(device=DEV).manual_seed(seed)

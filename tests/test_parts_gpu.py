@@ -73,6 +73,49 @@ def test_norm_feed_forward_attention_and_block(name, dtype, folders):
     runner.check_fault()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens", [23, 150])      # a step of the streaming product; one of the library product
+def test_attention_with_a_bias_on_q_k_and_v(dtype, tokens, folders):
+    """The attention part built with ``qkv_bias`` (no model here has one): its checkpoint names, and the
+    bias added in float32 before the per-head norms, against the plain functions put together by hand."""
+    from plain_qwen3 import apply_rope, causal_attention
+    from rapid_llm_b200.config import PartSpec
+    from rapid_llm_b200.parts import MIXERS
+
+    hidden, heads, kv_heads, dim, eps, theta = 80, 6, 3, 48, 3e-6, 50000.0
+    part = MIXERS.build(PartSpec("gqa_attention", {
+        "hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": dim, "qk_norm": True,
+        "qk_norm_eps": eps, "qkv_bias": True,
+        "position": PartSpec("rope", {"head_dim": dim, "rotary_dim": dim, "theta": theta, "max_positions": 512}),
+    }), dtype={"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], device="cuda:0")
+    specs = part.tensor_specs()
+    assert {"q_proj.bias", "k_proj.bias", "v_proj.bias"} <= set(specs) and specs["k_proj.bias"].shape == (kv_heads * dim,)
+    generator = torch.Generator().manual_seed(12)
+    weights = {}
+    for name, spec in specs.items():
+        scale = 0.5 if name.endswith("bias") else 0.05
+        value = torch.randn(spec.shape, generator=generator) * scale + (1.0 if "norm" in name else 0.0)
+        weights[name] = value.to(part.dtype).float() if spec.kind == "matrix" else value
+        part.load_tensor(name, weights[name])
+
+    dirs, _ = folders[dtype]
+    runner = runner_for(dirs["C"], dtype, "C")           # a cache of the same geometry (3 kv heads of 48)
+    batch = whole_batch(runner, tokens)
+    x = torch.randn(tokens, hidden, generator=generator).to(part.dtype)
+    out = part.forward(x.to("cuda:0"), batch, runner.layer_caches()[0])
+    runner.check_fault()
+
+    xf = x.float()
+    q = (xf @ weights["q_proj.weight"].T + weights["q_proj.bias"]).view(tokens, heads, dim)
+    key = (xf @ weights["k_proj.weight"].T + weights["k_proj.bias"]).view(tokens, kv_heads, dim)
+    value = (xf @ weights["v_proj.weight"].T + weights["v_proj.bias"]).view(tokens, kv_heads, dim)
+    q, key = rms_norm(q, weights["q_norm.weight"], eps), rms_norm(key, weights["k_norm.weight"], eps)
+    cos, sin = rope_angles(torch.arange(tokens), dim, theta)
+    attended = causal_attention(apply_rope(q, cos, sin), apply_rope(key, cos, sin), value, dim**-0.5)
+    want = attended.reshape(tokens, heads * dim) @ weights["o_proj.weight"].T
+    torch.testing.assert_close(out.float().cpu(), want, **for_dtype(dtype))
+
+
 def test_rope_tables_are_the_plain_angles():
     from rapid_llm_b200.parts.rope import RotaryEmbedding
 
@@ -237,6 +280,122 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for name in tokens:
         torch.testing.assert_close(torch.cat(pieces[name]), whole[name], **for_dtype("float32"))
     assert float(whole["a"].abs().max()) > 0
+
+
+def test_a_toy_mixer_with_rows_of_its_own_in_the_pages(tmp_path):
+    """A mixer that caches one row per token of a width it chooses (neither keys nor values): the cache
+    manager gives it pages ``[page, width]`` from its ``CacheNeed.token_shape``, in a group of its own beside the
+    attention layer's, and the pages are used again by later requests.  y_t = mean of the rows 0..t, times W."""
+    from rapid_llm_b200.config import EngineConfig, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.parts import MIXERS, CacheNeed, Mixer, TensorSpec
+    from rapid_llm_b200.weights import write_random_model
+
+    hidden, width, vocab = 32, 24, 83
+
+    @MIXERS.register("toy_mean_of_rows")
+    class ToyMeanOfRows(Mixer):
+        def __init__(self, *, hidden_size, width, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.down = self.new_storage((width, hidden_size), "matrix")
+            self.up = self.new_storage((hidden_size, width), "matrix")
+
+        def cache_need(self):
+            return CacheNeed("full", token_shape=(self.down.shape[0],))
+
+        def tensor_specs(self):
+            return {"down.weight": TensorSpec(tuple(self.down.shape)), "up.weight": TensorSpec(tuple(self.up.shape))}
+
+        def load_tensor(self, name, tensor):
+            (self.down if name == "down.weight" else self.up).copy_(tensor)
+
+        def forward(self, x, batch, cache):
+            group = batch.groups[cache.group]
+            rows = x.float() @ self.down.float().T
+            flat = cache.pages.view(-1, self.down.shape[0])            # [pages * page_size, width]
+            flat[group.kv_dest.long()] = rows.to(flat.dtype)
+            out = torch.empty_like(x)
+            for index in range(batch.num_entries):
+                begin, end = int(batch.h_cu_seqlens[index]), int(batch.h_cu_seqlens[index + 1])
+                start, slot = int(batch.h_entry_start[index]), int(batch.h_entry_slot[index])
+                count = start + end - begin
+                pages = group.block_table[slot, : -(-count // group.page_size)].long()
+                held = cache.pages[pages].reshape(-1, self.down.shape[0])[:count].float()
+                means = held.cumsum(0)[start:] / torch.arange(start + 1, count + 1, device=x.device)[:, None]
+                out[begin:end] = (means @ self.up.float().T).to(x.dtype)
+            return out
+
+    @dataclasses.dataclass(frozen=True)
+    class RowsConfig:
+        vocab_size: int
+        architecture = "ToyMeanOfRowsForCausalLM"
+        model_type = "toy_mean_of_rows"
+
+        @classmethod
+        def from_dict(cls, raw, overrides=None):
+            return cls(dict(raw, **(overrides or {}))["vocab_size"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "model_type": self.model_type, "vocab_size": self.vocab_size}
+
+        def to_spec(self):
+            norm = PartSpec("rmsnorm", {"size": hidden, "eps": 1e-5})
+            toy = PartSpec("toy_mean_of_rows", {"hidden_size": hidden, "width": width})
+            attention = PartSpec("gqa_attention", {
+                "hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                "position": PartSpec("rope", {"head_dim": 16, "rotary_dim": 16, "theta": 10000.0, "max_positions": 64}),
+            })
+            ffn = PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48})
+            layers = tuple(LayerSpec("prenorm", mixer, ffn, norm, f"model.layers.{i}.") for i, mixer in enumerate((toy, attention, toy)))
+            return ModelSpec(
+                architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=hidden, max_positions=64,
+                embedding=PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": hidden}),
+                layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(3)), final_norm=norm,
+                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": hidden, "tied": True}),
+            )
+
+    register_architecture(RowsConfig)
+    folder = write_random_model(tmp_path / "rows", RowsConfig(vocab), seed=5)
+    engine = EngineConfig(dtype=torch.float32, max_seq_len=64, page_size=8, num_pages=9, max_num_seqs=3,
+                          max_num_batched_tokens=64, use_cuda_graph=False)
+    runner = ModelRunner.from_folder(folder, engine)
+    shapes = sorted(tuple(pages.shape) for pages in runner.storage.pages)
+    assert shapes == [(1, 10, 2, 1, 8, 16), (2, 10, 8, width)]         # keys and values of one layer; rows of two
+
+    generator = torch.Generator().manual_seed(6)
+    tokens = {name: torch.randint(0, vocab, (count,), generator=generator).tolist()
+              for name, count in (("a", 30), ("b", 21), ("c", 37))}
+    whole = {}
+    for name, ids in tokens.items():
+        runner.admit(name)
+        whole[name] = runner.step([StepEntry(name, ids, list(range(len(ids))))]).cpu().clone()
+        runner.release(name)
+    # two at a time in portions, the third once pages are free again: 9 pages of 8 hold 72 tokens
+    pieces = {name: [] for name in tokens}
+    fed = {name: 0 for name in tokens}
+    cuts = {"a": [7, 2, 11, 10], "b": [1, 13, 7], "c": [20, 2, 15]}
+    for names in (("a", "b"), ("c",)):
+        for name in names:
+            runner.admit(name)
+        for step in range(4):
+            entries = []
+            for name in names:
+                if step < len(cuts[name]):
+                    size = cuts[name][step]
+                    entries.append(StepEntry(name, tokens[name][fed[name] : fed[name] + size], list(range(size))))
+                    fed[name] += size
+            if not entries:
+                continue
+            logits = runner.step(entries).cpu()
+            at = 0
+            for entry in entries:
+                pieces[entry.request_id].append(logits[at : at + len(entry.tokens)].clone())
+                at += len(entry.tokens)
+        for name in names:
+            runner.release(name)
+        runner.cache.check()
+    for name in tokens:
+        torch.testing.assert_close(torch.cat(pieces[name]), whole[name], **for_dtype("float32"))
 
 
 def test_state_advances_once_per_token_when_decode_steps_are_captured(tmp_path):

@@ -12,8 +12,8 @@ from rapid_llm_b200.sampling import SamplingParams
 class ScriptedExecutor:
     """Keeps the real cache bookkeeping, returns ``1000 + index of the generated token``."""
 
-    def __init__(self, config: EngineConfig, pages: int) -> None:
-        groups, _ = plan_groups([CacheNeed("full", 1, 16)])
+    def __init__(self, config: EngineConfig, pages: int, needs=None) -> None:
+        groups, _ = plan_groups(needs or [CacheNeed("full", 1, 16)])
         self.cache = CacheManager(groups, page_size=config.page_size, num_pages=pages,
                                   max_num_seqs=config.max_num_seqs, max_seq_len=config.max_seq_len)
         self.steps: list[list[tuple]] = []
@@ -36,15 +36,17 @@ class ScriptedExecutor:
                 index = len(entry.request.output_token_ids)
                 stop = self.stop_after.get(entry.request.request_id)
                 sampled.append(7 if stop is not None and index >= stop else 1000 + index)
+        for entry in entries:
+            self.cache.release_passed(entry.request.request_id)      # as the step function does
         self.cache.check()
         return sampled
 
 
-def make(pages=64, **overrides):
+def make(pages=64, needs=None, **overrides):
     values = dict(max_seq_len=256, page_size=16, max_num_seqs=4, max_num_batched_tokens=64, max_chunk_size=32)
     values.update(overrides)
     config = EngineConfig(**values)
-    executor = ScriptedExecutor(config, pages)
+    executor = ScriptedExecutor(config, pages, needs)
     return Scheduler(executor, config, stop_token_ids=[7]), executor
 
 
@@ -245,6 +247,8 @@ class RunAheadExecutor(ScriptedExecutor):
                 index = sum(1 for t in entry.request.output_token_ids)          # stand-ins count
                 stop = self.stop_after.get(entry.request.request_id)
                 sampled.append(7 if stop is not None and index >= stop else 1000 + index)
+        for entry in entries:
+            self.cache.release_passed(entry.request.request_id)      # as the step function does
         self.cache.check()
         self.fed.append(fed)
         self.previous_result = sampled
@@ -455,3 +459,19 @@ def test_a_decode_bucket_stays_within_what_a_step_may_carry():
     assert decode_bucket(1, 64, 48) == 1
     for count in range(1, 49):
         assert count <= decode_bucket(count, 64, 48) <= 48
+
+
+def test_a_long_request_fits_a_small_pool_of_a_windowed_group():
+    """Five pages of 16 hold a window of 32 keys, a portion of 32 tokens and the ragged page at either end:
+    a request of 200 tokens runs through such a pool, since the pages its window has passed come back;
+    with all keys kept the same pool refuses it at submission."""
+    window = [CacheNeed("window", 1, 16, window=32)]
+    scheduler, executor = make(pages=5, needs=window)
+    request = scheduler.add_request(list(range(190)), greedy(10), "long")
+    scheduler.run_to_completion()
+    assert request.finish_reason == "length" and len(request.output_token_ids) == 10
+    assert executor.cache.num_free_pages() == 5
+    with pytest.raises(ValueError, match="pages of cache group 0"):
+        make(pages=5)[0].add_request(list(range(190)), greedy(10), "long")
+    with pytest.raises(ValueError, match="pages of cache group 0"):
+        make(pages=4, needs=window)[0].add_request(list(range(190)), greedy(10), "long")
