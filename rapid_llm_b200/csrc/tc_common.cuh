@@ -185,6 +185,18 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// The same barrier with a vote: true if `mine` is true in every one of the `threads` threads.  A
+// decision that leads some threads past a later barrier and others not must be taken this way, or a
+// thread whose wait ran out a moment before its neighbours' leaves them waiting for ever.
+__device__ __forceinline__ bool named_barrier_and(int id, int threads, bool mine) {
+  uint32_t all;
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.u32 q, %3, 0;\n bar.red.and.pred p, %1, %2, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(all)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(mine ? 1u : 0u))
+      : "memory");
+  return all != 0;
+}
 // Makes shared-memory writes of this thread visible to the tensor cores and the copy engine.
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -112,6 +112,10 @@ class StepBatch:
     decode_only: bool = False
     extras: dict[str, Any] = field(default_factory=dict)
     feedback: torch.Tensor | None = None     # ids the previous step sampled, for token ids -(row + 1)
+    # Parts may queue their products for one persistent kernel (``ops.gemm`` with ``defer``): set by the model's
+    # forward pass, which runs the queue before anything but a kernel of ``ops.kernels`` reads a result.  A part
+    # called by itself gets finished results.
+    defer_products: bool = False
 
     @property
     def num_logit_rows(self) -> int:

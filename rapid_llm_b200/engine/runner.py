@@ -23,7 +23,7 @@ import torch
 from ..cache import CacheManager, CacheStorage, plan_groups
 from ..config import EngineConfig, load_config
 from ..models.causal_lm import CausalLM
-from ..ops import kernels
+from ..ops import gemm, kernels
 from ..parts.base import StepShape
 from ..weights import fill_random_on_device, load_weights
 from .batch import GroupView, LayerCache, StepBatch, Workspace
@@ -380,7 +380,9 @@ class ModelRunner:
         previous = kernels.PDL
         kernels.PDL = self.config.use_dependent_launch
         try:
-            return self.model.forward(batch, caches)
+            logits = self.model.forward(batch, caches)
+            gemm.flush()         # products still queued for the persistent kernel (a step that wants no logits)
+            return logits
         finally:
             kernels.PDL = previous
 
@@ -432,6 +434,7 @@ class ModelRunner:
         word = int(self.fault.item())
         if word:
             self.fault.zero_()
+            kernels.gemm_chain_reset(self.device)      # a kernel that gave up leaves its counters as they were
             raise RuntimeError(f"a kernel reported a fault: {kernels.describe_fault(word)}")
 
     def memory_report(self) -> dict[str, int]:

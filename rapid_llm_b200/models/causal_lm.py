@@ -11,6 +11,7 @@ import torch
 
 from ..config.model_spec import ModelSpec
 from ..engine.batch import LayerCache, StepBatch
+from ..ops import gemm
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, CacheNeed, StateNeed, TensorSpec
 from ..parts.norm import ADD, PLAIN
 
@@ -92,6 +93,7 @@ class CausalLM:
     # -- forward ------------------------------------------------------------------- #
     def forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""
+        batch.defer_products = True      # the queue is run below, before anything but a kernel reads a result
         x = self.embedding.forward(batch)
         residual = None
         schedule = self.spec.schedule
@@ -99,6 +101,8 @@ class CausalLM:
             # the norm that the next layer starts with may ride on this layer's last product
             after = self.layers[schedule[position + 1].layer].leading_norm() if position + 1 < len(schedule) else None
             x, residual = self.layers[entry.layer].forward(x, residual, batch, caches[position], then_norm=after)
+        if batch.num_logit_rows == 0 or not self.final_norm.reads_deferred:
+            gemm.flush()
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=self.dtype, device=self.device)
         if residual is None:
@@ -111,4 +115,6 @@ class CausalLM:
                 x, residual, batch, mode=ADD, write_residual=False,
                 row_index=batch.logit_rows, name="final_normed",
             )
-        return self.head.forward(hidden, batch)
+        logits = self.head.forward(hidden, batch)
+        gemm.flush()
+        return logits

@@ -11,6 +11,16 @@ measurements.
 A weight-only RMS norm between two tensor-core products rides on them instead of running as a
 kernel of its own (:class:`FollowingNorm` into the product before it, :class:`ScaledRows` out
 of it and into the product after it); ``FUSE_NORMS`` switches that off.
+
+Products of a small step that follow one another (a layer's output projection, gate/up, down, the
+next layer's q/k/v) run as ONE persistent kernel whose weight stream does not stop at their
+boundaries (``csrc/gemm_chain.cu``).  A caller that passes ``defer=True`` lets its product wait
+in a queue; the queue runs when it is full, when a product that cannot join it comes, or before
+any other kernel of :mod:`ops.kernels` is launched (so a deferred result may only be handed to
+such a kernel or to another product, never to a library call).  ``CHAIN`` switches it on; it is
+off by default: measured on the 8B layer shapes the persistent kernel loses more at each phase's end
+(partial tiles and the barrier go through global memory, about 8 us a phase) than its continuous
+weight stream gains over kernels chained by programmatic dependent launch.
 """
 
 from __future__ import annotations
@@ -25,6 +35,41 @@ from . import kernels
 TENSOR_CORE_MAX_TOKENS = 64
 FORCE: str | None = None      # "tcgen05", "library" or None (choose by size)
 FUSE_NORMS = True             # let a norm between two tensor-core products ride on them
+CHAIN = False                 # run deferred products of a small step as one persistent kernel
+
+_PENDING: list[dict] = []     # deferred products, in order
+_PENDING_FAULT: list[torch.Tensor] = []
+
+
+def flush() -> None:
+    """Run the deferred products now (one persistent kernel, or the single-product kernel for one)."""
+    if not _PENDING:
+        return
+    products, fault = list(_PENDING), _PENDING_FAULT[0]
+    _PENDING.clear()
+    _PENDING_FAULT.clear()
+    if len(products) == 1:
+        product = products[0]
+        kernels.gemm_bf16(product.pop("x"), product.pop("w"), product.pop("out"), fault, **product)
+    else:
+        kernels.gemm_chain(products, fault)
+
+
+kernels.BEFORE_LAUNCH = flush
+
+
+def _product(x, weight, out, fault, defer: bool, **options) -> None:
+    """One tensor-core product: queued if the caller allows it, else run at once (after the queue)."""
+    options = {name: value for name, value in options.items() if value is not None and value is not False}
+    if defer and CHAIN and x.shape[0] <= kernels.GEMM_CHAIN_MAX_TOKENS:
+        if _PENDING and (len(_PENDING) == kernels.GEMM_CHAIN_MAX_PHASES or _PENDING[0]["x"].shape[0] != x.shape[0]
+                         or _PENDING_FAULT[0] is not fault):
+            flush()
+        _PENDING.append({"x": x, "w": weight, "out": out, **options})
+        if not _PENDING_FAULT:
+            _PENDING_FAULT.append(fault)
+        return
+    kernels.gemm_bf16(x, weight, out, fault, **options)
 
 
 @dataclass
@@ -85,12 +130,13 @@ def _bias_as(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 
 def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | None = None, *,
-           then_norm: FollowingNorm | None = None, bias: torch.Tensor | None = None):
+           then_norm: FollowingNorm | None = None, bias: torch.Tensor | None = None, defer: bool = False):
     """``out[T, N] = x[T, K] @ weight[N, K]^T (+ bias[N], float32)``; all on the GPU, same dtype.
 
     ``x`` may be :class:`ScaledRows`.  With ``then_norm`` the product may take the norm along:
     it then returns :class:`ScaledRows` (the residual is updated, ``out`` is not written);
-    otherwise it returns ``out`` and the caller runs the norm.
+    otherwise it returns ``out`` and the caller runs the norm.  With ``defer`` the product may be
+    queued (see the module's text): its result exists once :func:`flush` has run.
     """
     x, scale = _open_scale(x)
     if not x.is_cuda:
@@ -107,10 +153,12 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
                 and rows <= TENSOR_CORE_MAX_TOKENS):
             normed = then_norm.workspace.get("normed", rows, width, x.dtype)
             sumsq = then_norm.workspace.get("normed_sumsq", rows, kernels.gemm_bf16_sumsq_count(width), torch.float32)
-            kernels.gemm_bf16(x, weight, normed, fault, residual=then_norm.residual, norm_weight=then_norm.weight,
-                              sumsq_out=sumsq, bias=bias, **scale)
+            _product(x, weight, normed, fault, defer, residual=then_norm.residual, norm_weight=then_norm.weight,
+                     sumsq_out=sumsq, bias=bias, **scale)
             return ScaledRows(normed, sumsq, then_norm.eps, width)
-        return kernels.gemm_bf16(x, weight, out, fault, bias=bias, **scale)
+        _product(x, weight, out, fault, defer, bias=bias, **scale)
+        return out
+    flush()
     if scale:
         raise kernels.KernelError("linear: rows with an open scale need the tensor-core product")
     if bias is None:
@@ -120,7 +168,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
     return out
 
 
-def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor) -> torch.Tensor:
+def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor, *,
+                 defer: bool = False) -> torch.Tensor:
     """``act = silu(x @ gate^T) * (x @ up^T)`` for a ``[2 I, K]`` weight with the gate rows first.
 
     One fused tensor-core kernel where it applies; otherwise the product into a ``[T, 2 I]``
@@ -128,7 +177,8 @@ def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: 
     """
     x, scale = _open_scale(x)
     if use_tensor_core_kernel(x, gate_up):
-        return kernels.gemm_bf16(x, gate_up, act, fault, swiglu=True, **scale)
+        _product(x, gate_up, act, fault, defer, swiglu=True, **scale)
+        return act
     if scale:
         raise kernels.KernelError("gated_linear: rows with an open scale need the tensor-core product")
     wide = workspace.get("ffn_gate_up", x.shape[0], gate_up.shape[0], x.dtype)

@@ -48,7 +48,14 @@ def _ptr(tensor: torch.Tensor | None) -> c_void_p:
     return c_void_p(tensor.data_ptr())
 
 
+# Called before every launch of this module: whoever has queued work that the launch may depend on
+# (``ops.gemm`` queues the products of a small step for one persistent kernel) runs it first.
+BEFORE_LAUNCH = None
+
+
 def _stream() -> c_void_p:
+    if BEFORE_LAUNCH is not None:
+        BEFORE_LAUNCH()
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -541,6 +548,108 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
         f"gemm_bf16({tokens}x{k} by {n_out})",
     )
     return out
+
+
+class _ChainPhase(ctypes.Structure):
+    """``RlChainPhase`` of ``csrc/gemm_chain.cu``."""
+
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("out", c_void_p), ("n_out", c_int), ("k", c_int), ("swiglu", c_int),
+        ("residual", c_void_p), ("norm_weight", c_void_p), ("sumsq_out", c_void_p), ("sumsq_in", c_void_p),
+        ("sumsq_count", c_int), ("norm_eps", c_float), ("norm_size", c_int), ("bias", c_void_p),
+    ]
+
+
+GEMM_CHAIN_MAX_PHASES = 4
+GEMM_CHAIN_MAX_TOKENS = 64
+_CHAIN_STATE: dict[torch.device, dict] = {}
+
+
+def _chain_lib() -> ctypes.CDLL:
+    lib = gemm_lib()
+    if not getattr(lib, "_chain_declared", False):
+        lib.rl_gemm_chain.argtypes = [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        lib.rl_gemm_chain.restype = c_int
+        lib.rl_gemm_chain_scratch_floats.argtypes = [c_void_p, c_int, c_int]
+        lib.rl_gemm_chain_scratch_floats.restype = c_longlong
+        lib.rl_gemm_chain_counter_words.restype = c_int
+        lib._chain_declared = True
+    return lib
+
+
+def gemm_chain_reset(device=None) -> None:
+    """Zero the chain kernel's counters (after a fault: the kernel keeps them zero only when it ends well)."""
+    for key, state in _CHAIN_STATE.items():
+        if device is None or key == torch.device(device):
+            state["counters"].zero_()
+
+
+def gemm_chain(products: list[dict], fault: torch.Tensor, trace: torch.Tensor | None = None) -> None:
+    """Two to four bfloat16 products of the same (at most 64) tokens as one persistent kernel, each reading
+    what earlier ones wrote.  A product is the keyword arguments of :func:`gemm_bf16` (``x``, ``w``, ``out``,
+    ``swiglu``, ``residual``, ``norm_weight``, ``sumsq_out``, ``sumsq_in``, ``norm_eps``, ``norm_size``,
+    ``bias``); the results are those of calling it once per product, up to the order of float32 additions.
+    Scratch for partial tiles and the kernel's counters are kept per device and grow on demand.  ``trace``
+    (int64 ``[multiprocessors, 4, 8]``) receives the kernel's time stamps per CTA, phase and event."""
+    count = len(products)
+    if not 1 <= count <= GEMM_CHAIN_MAX_PHASES:
+        raise KernelError(f"gemm_chain: takes 1 to {GEMM_CHAIN_MAX_PHASES} products, got {count}")
+    tokens = products[0]["x"].shape[0]
+    if not 0 < tokens <= GEMM_CHAIN_MAX_TOKENS:
+        raise KernelError(f"gemm_chain: takes 1 to {GEMM_CHAIN_MAX_TOKENS} tokens, got {tokens}")
+    array = (_ChainPhase * count)()
+    for slot, product in zip(array, products):
+        x, w, out = product["x"], product["w"], product["out"]
+        swiglu = bool(product.get("swiglu", False))
+        extras = [product.get(name) for name in ("residual", "norm_weight", "sumsq_out", "sumsq_in", "bias")]
+        _need_cuda(x, w, out, fault, *extras)
+        for name, tensor in (("x", x), ("w", w), ("out", out)):
+            _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
+        for name, tensor in zip(("residual", "norm_weight", "sumsq_out", "sumsq_in", "bias"), extras):
+            _expect(name, tensor, torch.float32), _contig(name, tensor)
+        n_out = out.shape[1]
+        if x.shape[0] != tokens or out.shape[0] != tokens or w.shape != ((2 if swiglu else 1) * n_out, x.shape[1]):
+            raise KernelError(f"gemm_chain: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+        if not gemm_bf16_supports(x, w):
+            raise KernelError("gemm_chain: the inner size must be a multiple of 8 and the operands 16-byte aligned")
+        residual, norm_weight, sumsq_out, sumsq_in, bias = extras
+        if any(t is not None for t in (residual, norm_weight, sumsq_out)):
+            if residual is None or norm_weight is None or sumsq_out is None or swiglu:
+                raise KernelError("gemm_chain: a following norm needs residual, norm_weight and sumsq_out, and no swiglu")
+            if (residual.shape != (tokens, n_out) or norm_weight.shape != (n_out,)
+                    or sumsq_out.shape != (tokens, gemm_bf16_sumsq_count(n_out))):
+                raise KernelError("gemm_chain: residual, norm_weight or sumsq_out do not have the product's shape")
+        if sumsq_in is not None and (sumsq_in.dim() != 2 or sumsq_in.shape[0] != tokens or sumsq_in.shape[1] % 4
+                                     or product.get("norm_size", 0) <= 0):
+            raise KernelError("gemm_chain: sumsq_in must be [tokens, a multiple of 4] and norm_size positive")
+        if bias is not None and bias.shape != (w.shape[0],):
+            raise KernelError("gemm_chain: the bias does not have the weight's rows")
+        slot.x, slot.w, slot.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+        slot.n_out, slot.k, slot.swiglu = n_out, x.shape[1], int(swiglu)
+        slot.residual = None if residual is None else residual.data_ptr()
+        slot.norm_weight = None if norm_weight is None else norm_weight.data_ptr()
+        slot.sumsq_out = None if sumsq_out is None else sumsq_out.data_ptr()
+        slot.sumsq_in = None if sumsq_in is None else sumsq_in.data_ptr()
+        slot.sumsq_count = 0 if sumsq_in is None else sumsq_in.shape[1]
+        slot.norm_eps, slot.norm_size = float(product.get("norm_eps", 0.0)), int(product.get("norm_size", 0))
+        slot.bias = None if bias is None else bias.data_ptr()
+    lib = _chain_lib()
+    device = fault.device
+    state = _CHAIN_STATE.get(device)
+    if state is None:
+        state = {"counters": torch.zeros(lib.rl_gemm_chain_counter_words(), dtype=torch.int32, device=device),
+                 "scratch": torch.empty(1 << 20, dtype=torch.float32, device=device), "retired": []}
+        _CHAIN_STATE[device] = state
+    need = int(lib.rl_gemm_chain_scratch_floats(ctypes.byref(array), count, tokens))
+    if need > state["scratch"].numel():
+        state["retired"].append(state["scratch"])          # a captured graph may still hold its address
+        state["scratch"] = torch.empty(need, dtype=torch.float32, device=device)
+    stream = _stream()
+    _check(
+        lib.rl_gemm_chain(ctypes.byref(array), count, tokens, _ptr(state["scratch"]), state["scratch"].numel(),
+                          _ptr(state["counters"]), _ptr(trace), int(PDL), _ptr(fault), stream),
+        f"gemm_chain({count} products of {tokens} tokens)",
+    )
 
 
 def sample(

@@ -230,7 +230,7 @@ class GQAAttention(Mixer):
         group = batch.groups[cache.group]
         rows = x.shape[0]
         qkv = batch.workspace.get("attn_qkv", rows, self.qkv.shape[0], x.dtype)
-        gemm.linear(x, self.qkv, qkv, batch.fault, bias=self.qkv_bias)
+        gemm.linear(x, self.qkv, qkv, batch.fault, bias=self.qkv_bias, defer=batch.defer_products)
         q = batch.workspace.get("attn_q", rows, self.hq * self.d, x.dtype)
         cos, sin = self.position.tables()
         kernels.qk_norm_rope_write(
@@ -245,7 +245,7 @@ class GQAAttention(Mixer):
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
-        return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm)
+        return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)
 
     def attend(self, q, pages, out, batch, group) -> None:
         if q.dtype == torch.bfloat16:

@@ -197,6 +197,11 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    # Whether ``forward`` may be handed the result of a product that is still queued (``ops.gemm`` with
+    # ``defer``): true only for a norm that launches through ``ops.kernels``, which runs the queue first.
+    # For any other norm the caller runs the queue before it calls.
+    reads_deferred = False
+
     def forward(self, x, residual, batch, *, mode: int, write_residual: bool, row_index=None, name="normed"):
         raise NotImplementedError
 

@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import LayerSpec
+from ..ops import gemm
 from ..ops.gemm import ScaledRows
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, TensorSpec
 from .norm import ADD, FIRST
@@ -88,6 +89,8 @@ class PreNormBlock(Block):
 
     def forward(self, x, residual, batch, cache, then_norm=None):
         """``(x, residual)`` in, ``(x, residual)`` out; ``residual`` is ``None`` for the first layer."""
+        if not self.mixer_norm.reads_deferred:
+            gemm.flush()        # a norm that is no kernel of ops.kernels reads finished results only
         if isinstance(x, ScaledRows):
             normed = x          # the block before took this block's first norm along
         elif residual is None:
@@ -103,6 +106,8 @@ class PreNormBlock(Block):
         if isinstance(mixed, ScaledRows):
             normed = mixed
         else:
+            if not self.feed_forward_norm.reads_deferred:
+                gemm.flush()
             normed = self.feed_forward_norm.forward(mixed, residual, batch, mode=ADD, write_residual=True)
         if self.feed_forward.rides_norms:
             offer = then_norm.following(residual, batch) if then_norm is not None else None

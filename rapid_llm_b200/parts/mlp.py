@@ -54,6 +54,6 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch, then_norm=None):
         rows = x.shape[0]
         act = batch.workspace.get("ffn_act", rows, self.inter, x.dtype)
-        gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault)
+        gemm.gated_linear(x, self.gate_up, act, batch.workspace, batch.fault, defer=batch.defer_products)
         out = batch.workspace.get("ffn_out", rows, self.hidden, x.dtype)
-        return gemm.linear(act, self.down, out, batch.fault, then_norm=then_norm)
+        return gemm.linear(act, self.down, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)

@@ -18,6 +18,8 @@ FIRST, ADD, PLAIN = 0, 1, 2
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    reads_deferred = True       # it launches through ops.kernels, which runs queued products first
+
     def __init__(self, *, size: int, eps: float, dtype, device) -> None:
         super().__init__(dtype=dtype, device=device)
         self.size = int(size)

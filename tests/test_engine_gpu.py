@@ -193,6 +193,31 @@ def test_norms_ride_on_the_products_of_small_steps(name, models, monkeypatch):
         torch.testing.assert_close(got, results[False][position], **tolerance)
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_products_of_small_steps_as_one_persistent_kernel(name, models, monkeypatch):
+    """With ``ops.gemm.CHAIN`` the products that follow one another in a small bfloat16 step (output projection,
+    gate/up, down, the next layer's q/k/v) are queued and run as one kernel; the logits are the plain
+    implementation's, in portions and from a captured decode graph."""
+    from rapid_llm_b200.engine.runner import StepEntry
+    from rapid_llm_b200.ops import gemm, kernels
+
+    dirs, plains = models["bfloat16"]
+    config, weights = plains[name]
+    tokens = random_tokens(config["vocab_size"], 90, 78)
+    plain = forward_logits(config, weights, tokens)
+    calls = []
+    real = kernels.gemm_chain
+    monkeypatch.setattr(kernels, "gemm_chain", lambda products, fault, **k: (calls.append(len(products)), real(products, fault, **k))[1])
+    monkeypatch.setattr(gemm, "CHAIN", True)
+    runner = make_runner(dirs[name], "bfloat16", max_tokens=128, page_size=PAGE_SIZES[name])
+    records = portions("n", tokens, [70, 9, 1, 1, 2])[:5]         # a large step, then small ones
+    rows = collect(records, replay(runner, records))
+    layers = config["num_hidden_layers"]
+    assert calls == ([4] * (layers - 1) + [3]) * 4, calls           # per small step: one chain a layer
+    compare(rows, {"n": {p: plain[p] for p in rows["n"]}}, "bfloat16")
+    assert not gemm._PENDING
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_steps_that_nobody_waits_for(dtype, models):
     """Portions that want no logits are never read back, so the host prepares several steps

@@ -92,9 +92,8 @@ def test_the_command_line_from_a_folder_to_token_ids(tiny_dirs, tiny_plain, tmp_
     want = [greedy_generate(config, weights, prompt, 8) for prompt in prompts]
     reasons, tokens = run()
     assert tokens == want and reasons == ["length"] * 3
-    stop = next(token for full in want for place, token in enumerate(full) if place and token not in full[:place])
+    stop = want[1][-1]                # wherever it first shows in a request's tokens, the request ends before it
     reasons, tokens = run("--stop-token-ids", f"{stop}, 100000")
-    assert any(stop in full for full in want)
     for reason, got, full in zip(reasons, tokens, want):
         cut = full.index(stop) if stop in full else len(full)
         assert got == full[:cut] and reason == ("eos" if stop in full else "length")

@@ -178,6 +178,72 @@ def test_gemm_bf16_adds_a_bias(t, n, k_, swiglu, split):
     torch.testing.assert_close(out.float(), want, rtol=6e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("pdl", [False, True])
+@pytest.mark.parametrize("t,hidden,inter,qkv_rows", [(1, 256, 384, 512), (8, 4096, 12288, 6144), (16, 520, 1000, 136),
+                                                      (33, 1024, 2816, 1536), (64, 4096, 12288, 6144), (5, 128, 136, 72)])
+def test_gemm_chain_runs_a_layers_products_as_one_kernel(t, hidden, inter, qkv_rows, pdl):
+    """Output projection (residual add, the next norm's weight), gate/up with the SiLU (the row's scale),
+    down (residual add, norm weight), q/k/v of the next layer (scale, a bias): four products in one
+    persistent kernel, against float32 arithmetic and against the same products launched one by one; a
+    second run on the same inputs gives the same bits (sums in segment order, counters back at zero)."""
+    kernels = k()
+    eps = 1e-5
+    gen = lambda shape, scale, seed: device_rand(shape, scale, seed)      # noqa: E731
+    attended = gen((t, hidden), 1.0, 50)
+    w_o, w_gu = gen((hidden, hidden), 0.03, 51), gen((2 * inter, hidden), 0.03, 52)
+    w_down, w_qkv = gen((hidden, inter), 0.03, 53), gen((qkv_rows, hidden), 0.03, 54)
+    norm1 = (1.0 + 0.2 * torch.randn(hidden, generator=torch.Generator().manual_seed(55))).to(DEV)
+    norm2 = (1.0 + 0.2 * torch.randn(hidden, generator=torch.Generator().manual_seed(56))).to(DEV)
+    bias = torch.randn(qkv_rows, generator=torch.Generator().manual_seed(57)).to(DEV)
+    residual0 = torch.randn((t, hidden), generator=torch.Generator().manual_seed(58)).to(DEV) * 2.0
+    residual0[t // 2] *= 20.0                      # a scale taken from the wrong row shows
+
+    def run(chain: bool):
+        residual = residual0.clone()
+        normed = torch.full((t, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+        sumsq = torch.full((t, kernels.gemm_bf16_sumsq_count(hidden)), float("nan"), dtype=torch.float32, device=DEV)
+        act = torch.full((t, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qkv = torch.full((t, qkv_rows), float("nan"), dtype=torch.bfloat16, device=DEV)
+        fault = fault_word()
+        products = [
+            dict(x=attended, w=w_o, out=normed, residual=residual, norm_weight=norm1, sumsq_out=sumsq),
+            dict(x=normed, w=w_gu, out=act, swiglu=True, sumsq_in=sumsq, norm_eps=eps, norm_size=hidden),
+            dict(x=act, w=w_down, out=normed, residual=residual, norm_weight=norm2, sumsq_out=sumsq),
+            dict(x=normed, w=w_qkv, out=qkv, sumsq_in=sumsq, norm_eps=eps, norm_size=hidden, bias=bias),
+        ]
+        kernels.PDL = pdl
+        try:
+            if chain:
+                kernels.gemm_chain(products, fault)
+            else:
+                for product in products:
+                    product = dict(product)
+                    kernels.gemm_bf16(product.pop("x"), product.pop("w"), product.pop("out"), fault, **product)
+        finally:
+            kernels.PDL = False
+        assert fault.item() == 0
+        return residual, act, qkv
+
+    residual, act, qkv = run(chain=True)
+    again = run(chain=True)
+    assert all(torch.equal(a, b) for a, b in zip((residual, act, qkv), again))
+
+    r1 = residual0 + attended.float() @ w_o.float().T
+    x1 = rms_norm(r1, norm1, eps)
+    gate_up = x1 @ w_gu.float().T
+    want_act = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+    r2 = r1 + want_act.to(torch.bfloat16).float() @ w_down.float().T
+    want_qkv = rms_norm(r2, norm2, eps) @ w_qkv.float().T + bias
+    one_by_one = run(chain=False)
+    # intermediate roundings to bfloat16 differ between the float32 arithmetic and both kernels: loose against
+    # the arithmetic, tight between the two ways of launching
+    torch.testing.assert_close(act.float(), want_act, rtol=3e-2, atol=3e-2 * float(want_act.abs().max()) / 4)
+    torch.testing.assert_close(residual, r2, rtol=2e-2, atol=2e-2 * float(r2.abs().mean()))
+    torch.testing.assert_close(qkv.float(), want_qkv, rtol=3e-2, atol=3e-2 * float(want_qkv.abs().max()) / 4)
+    for got, other in zip((residual, act, qkv), one_by_one):
+        torch.testing.assert_close(got.float(), other.float(), rtol=1e-2, atol=1e-2 * float(other.float().abs().max()) / 4)
+
+
 def device_rand(shape, scale, seed):
     """Large operands are drawn on the device: a billion normal draws take the CPU tens of seconds."""
     generator = torch.Generator(device=DEV).manual_seed(seed)
