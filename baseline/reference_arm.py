@@ -172,16 +172,20 @@ def main() -> int:
         return 0
 
     # prefill of one 2,048-token prompt: submit, step until its first token; best of three
-    prefill_ms = []
+    prefill_ms, prefill_device_ms = [], []
     for trial in range(max(args.warmup, 1) + 3):
         request = scheduler.add_request("", greedy(1), prompt_token_ids=random_prompts(1, PREFILL_TOKENS, vocab, 11 + trial)[0])
         torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         started = time.perf_counter()
+        begin.record()
         while not request.output_token_ids and request.finish_reason is None:
             scheduler.step()
+        end.record()
         torch.cuda.synchronize()
         if trial >= max(args.warmup, 1):
             prefill_ms.append((time.perf_counter() - started) * 1000.0)
+            prefill_device_ms.append(begin.elapsed_time(end))
         drain()
     say(f"prefill {min(prefill_ms):.2f} ms")
 
@@ -218,7 +222,7 @@ def main() -> int:
 
     print(json.dumps({
         "device_ms": device_ms, "tokens": tokens, "wall_ms": wall_ms, "wall_tokens": wall_tokens,
-        "prefill_ms": min(prefill_ms), "layers": config["num_hidden_layers"], "layers_full": layers_full,
+        "prefill_ms": min(prefill_ms), "prefill_device_ms": min(prefill_device_ms), "layers": config["num_hidden_layers"], "layers_full": layers_full,
         "finished_early": sum(1 for r in requests if r.finish_reason not in (None, "abort")),
     }))
     return 0
