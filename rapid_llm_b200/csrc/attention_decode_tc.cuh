@@ -41,7 +41,7 @@ namespace RL_ATTENTION_NS {
 constexpr int kTcD = 128;
 constexpr int kTcKeys = 128;                    // keys per block = M of the score product
 constexpr int kTcRows = 16;                     // packed query rows per item = N of both products
-constexpr int kTcStages = 3;
+constexpr int kTcMaxStages = 3;                 // tiles of keys (and of values) in flight ahead of the math, per CTA
 constexpr int kTcTeams = 2;
 constexpr int kTcProducerWarps = 4;             // warps 0, 1: TMA of keys, warps 2, 3: TMA of values
 constexpr int kTcIssuerWarp = kTcProducerWarps;  // then one warp that issues the products
@@ -53,7 +53,11 @@ constexpr int kTcHalfBytes = kTcKeys * 128;     // one 64-wide half of a 128-key
 constexpr int kTcTileBytes = 2 * kTcHalfBytes;  // K or V of one block
 constexpr int kTcStageBytes = 2 * kTcTileBytes;
 constexpr int kTcOperandBytes = 2 * kTcRows * 128;   // Q or P^T: 16 rows, two 64-wide halves
-constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + (1 + 2 * kTcTeams) * kTcOperandBytes + 1024;
+// Shared memory of a CTA with rings of `stages` key tiles and `stages` value tiles.  Three stages take a whole
+// multiprocessor: one CTA streams by itself.  With one stage two CTAs fit a multiprocessor, and while one of
+// them sets itself up for its item (page ids, queries, first tiles: a quarter of a short item's time) the other
+// streams; a step with more items than multiprocessors runs faster that way.
+constexpr int tc_smem_bytes(int stages) { return stages * kTcStageBytes + (1 + 2 * kTcTeams) * kTcOperandBytes + 1024; }
 constexpr uint32_t kTcIdescScore = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcRows >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kTcIdescValue = kTcIdescScore | (1u << 15);     // A (the values) is MN-major
 
@@ -82,10 +86,11 @@ __device__ __forceinline__ float warp_max_redux(float v) {
 
 // kRows: how many of the 16 columns of the products carry query rows (a power of two); the
 // per-row work of the softmax threads is unrolled over exactly these.
-template <int kRows>
-__global__ void __launch_bounds__(kTcThreads, 1)
+template <int kRows, int kTcStages>
+__global__ void __launch_bounds__(kTcThreads, kTcStages == 1 ? 2 : 1)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const DecodeTcArgs args) {
   static_assert(kRows >= 1 && kRows <= kTcRows && (kRows & (kRows - 1)) == 0, "rows: a power of two up to 16");
+  static_assert(kTcStages >= 1 && kTcStages <= kTcMaxStages, "stages");
   extern __shared__ unsigned char tc_smem_raw[];
   __shared__ __align__(8) uint64_t full_k[kTcStages], full_v[kTcStages], empty_k[kTcStages], empty_v[kTcStages];
   __shared__ __align__(8) uint64_t score_ready[kTcTeams][2], p_ready[kTcTeams][2], value_ready[kTcTeams][2];

@@ -553,12 +553,21 @@ static int launch_prefill_tc(const AttentionArgs& a, int n_items, bool pdl, cuda
                        map, t);
 }
 
-static bool g_decode_tc_configured[5] = {};   // per row-count instantiation; file-local on purpose
+static bool g_decode_tc_configured[5][2] = {};   // per row-count and ring-depth instantiation; file-local on purpose
 
-template <int kRows>
-static int launch_decode_tc_rows(const CUtensorMap& map, const DecodeTcArgs& t, int n_items, bool pdl,
-                                 cudaStream_t stream, bool* configured) {
-  auto kernel = attention_decode_tc_kernel<kRows>;
+static int decode_tc_sm_count() {
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+    sms = 148;
+  return sms;
+}
+
+template <int kRows, int kStages>
+static int launch_decode_tc_stages(const CUtensorMap& map, const DecodeTcArgs& t, int n_items, bool pdl,
+                                   cudaStream_t stream, bool* configured) {
+  auto kernel = attention_decode_tc_kernel<kRows, kStages>;
+  constexpr int kTcSmemBytes = tc_smem_bytes(kStages);
   if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -592,11 +601,24 @@ static int launch_decode_tc_rows(const CUtensorMap& map, const DecodeTcArgs& t, 
   return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map, t));
 }
 
+// More CTAs than multiprocessors, each by itself (no cluster): two shallow CTAs per multiprocessor, so that one
+// streams while the other starts.  Decided by the number of items alone: a captured decode graph replays the same
+// choice at every context length.
+// `rings`: 0 = decide here, 2 = deep, 3 = shallow (for measurements).
+template <int kRows>
+static int launch_decode_tc_rows(const CUtensorMap& map, const DecodeTcArgs& t, int n_items, bool pdl,
+                                 cudaStream_t stream, bool* configured, int rings) {
+  const bool shallow = rings == 3 || (rings != 2 && !t.cluster_merge &&
+                                      static_cast<long long>(n_items) * t.hkv > decode_tc_sm_count());
+  if (shallow) return launch_decode_tc_stages<kRows, 1>(map, t, n_items, pdl, stream, configured + 1);
+  return launch_decode_tc_stages<kRows, kTcMaxStages>(map, t, n_items, pdl, stream, configured);
+}
+
 // cluster_merge: the `splits` items of a tile are consecutive in the grid and launched as one
 // thread-block cluster, whose CTAs merge their partial results among themselves.  max_rows: the
 // most packed rows any of the items has (0 = not known).
 static int launch_decode_tc(const AttentionArgs& a, int n_items, int max_rows, bool cluster_merge, bool pdl,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int rings = 0) {
   CUtensorMap map;
   const long long rows = static_cast<long long>(a.num_pages) * 2 * a.hkv * a.page_size;
   int status = make_map(&map, a.cache, rows, kD, a.page_size < kTcKeys ? a.page_size : kTcKeys);
@@ -608,11 +630,11 @@ static int launch_decode_tc(const AttentionArgs& a, int n_items, int max_rows, b
   t.num_pages = a.num_pages; t.max_pages = a.max_pages; t.slots = a.slots; t.window = a.window;
   t.splits = a.splits; t.cluster_merge = cluster_merge ? 1 : 0; t.scale_log2 = a.scale_log2; t.fault = a.fault;
   if (max_rows <= 0 || max_rows > kTcRows) max_rows = kTcRows;
-  if (max_rows <= 1) return launch_decode_tc_rows<1>(map, t, n_items, pdl, stream, &g_decode_tc_configured[0]);
-  if (max_rows <= 2) return launch_decode_tc_rows<2>(map, t, n_items, pdl, stream, &g_decode_tc_configured[1]);
-  if (max_rows <= 4) return launch_decode_tc_rows<4>(map, t, n_items, pdl, stream, &g_decode_tc_configured[2]);
-  if (max_rows <= 8) return launch_decode_tc_rows<8>(map, t, n_items, pdl, stream, &g_decode_tc_configured[3]);
-  return launch_decode_tc_rows<16>(map, t, n_items, pdl, stream, &g_decode_tc_configured[4]);
+  if (max_rows <= 1) return launch_decode_tc_rows<1>(map, t, n_items, pdl, stream, g_decode_tc_configured[0], rings);
+  if (max_rows <= 2) return launch_decode_tc_rows<2>(map, t, n_items, pdl, stream, g_decode_tc_configured[1], rings);
+  if (max_rows <= 4) return launch_decode_tc_rows<4>(map, t, n_items, pdl, stream, g_decode_tc_configured[2], rings);
+  if (max_rows <= 8) return launch_decode_tc_rows<8>(map, t, n_items, pdl, stream, g_decode_tc_configured[3], rings);
+  return launch_decode_tc_rows<16>(map, t, n_items, pdl, stream, g_decode_tc_configured[4], rings);
 }
 
 }  // namespace RL_ATTENTION_NS
@@ -633,7 +655,8 @@ int rl_attention_decode_rows() { return 16; }
 // chunk_rows: packed rows per chunk item: 64 (or 0) = the mma.sync tiles, 256 = the tcgen05
 // kernel (head size 128, pages it takes, splits == 1).
 // decode_kernel: 0 = the tcgen05 kernel for decode tiles where it applies, 1 = always the
-// mma.sync tiles.  decode_rows: the most packed rows any decode tile has (0 = not known).
+// mma.sync tiles, 2 / 3 = the tcgen05 kernel with deep rings (one CTA per multiprocessor) / shallow
+// rings (two) whatever the number of items.  decode_rows: the most packed rows any decode tile has (0 = not known).
 // chunk_items / decode_items: [n, 4] int32 (entry, first packed row, split, 0).  With
 // splits > 1, part_out [tokens, hq, splits, D] and part_lse [tokens, hq, splits] are scratch
 // and every (row, split) pair must be covered by exactly one item.
@@ -683,7 +706,8 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
     args.items = decode_items;
     if (decode_kernel != 1 && attn::decode_tc_supported(page_size)) {
       merged_in_cluster = n_chunk_items == 0 && splits > 1 && splits <= 8 && n_decode_items % splits == 0;
-      status = attn::launch_decode_tc(args, n_decode_items, decode_rows, merged_in_cluster, pdl != 0, stream);
+      status = attn::launch_decode_tc(args, n_decode_items, decode_rows, merged_in_cluster, pdl != 0, stream,
+                                      decode_kernel == 2 || decode_kernel == 3 ? decode_kernel : 0);
     } else
       status = attn::launch_attention<1, 4, 3>(args, n_decode_items, pdl != 0, stream);
     if (status != 0) return status;

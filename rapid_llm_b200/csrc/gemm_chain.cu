@@ -34,6 +34,14 @@
 //
 // The counters are zero when the kernel starts and are zeroed again by the CTA that leaves last.
 //
+// Measured on the four products of a Qwen3-8B layer at 8 tokens (cold caches, one launch): 104 us against
+// 59 us of streaming; a phase's end (partial tiles parked and counted, the others' awaited, sums, stores, the
+// barrier, the next activation tiles) costs about 8 us, of which the ring hides 4.  A variant that gave each
+// tile to a cluster of two CTAs (halves of the inner range, summed through distributed shared memory) ended a
+// phase in 5 us, but left the narrow products (32 tiles) to 64 of 148 multiprocessors, each of which drew only
+// about 35 GB/s from memory: 129 us.  Kernels chained by programmatic dependent launch take 76 us for the same
+// products inside a decode step, which is why the engine does not use this kernel by default.
+//
 // The reference runs these products as separate library calls (rapid_llm/kernels/ops/gemm/linear.py:17-40,
 // rapid_llm/modules/mlp.py:52-68, rapid_llm/models/base.py:231-266).
 #include <cuda.h>

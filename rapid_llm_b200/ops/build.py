@@ -45,7 +45,7 @@ LIBRARIES: dict[str, list[str]] = {
         "gemm_f32.cu",
         "sampling.cu",
     ],
-    "gemm": ["gemm_bf16.cu", "gemm_chain.cu"],
+    "gemm": ["gemm_bf16.cu", "gemm_chain.cu", "gemm_bf16_pair.cu"],
 }
 LIBRARY_FLAGS: dict[str, list[str]] = {}
 

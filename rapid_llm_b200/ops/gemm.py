@@ -5,8 +5,10 @@ float32 runs the hand-written true 32-bit kernel.  bfloat16 steps of up to
 tcgen05/TMA kernel, which streams the weight once at close to memory speed; larger steps call
 the library product (cuBLAS through ``torch.mm``), which is where the reference's engine
 uses a library as well (``rapid_llm/kernels/ops/gemm/linear.py:17-40``) and is still the
-faster of the two at thousands of tokens.  ``FORCE`` pins one of the two for tests and
-measurements.
+faster of the two at thousands of tokens.  ``FORCE`` pins one for tests and measurements:
+``"tcgen05"`` (the streaming kernel at any size), ``"pair"`` (for steps above 64 tokens the kernel
+that pairs two CTAs on 256 x 256 tiles, ``csrc/gemm_bf16_pair.cu``: 0.85 to 1.0 of the library's pace at
+2,048 tokens and more, about half of it at a few hundred) or ``"library"``.
 
 A weight-only RMS norm between two tensor-core products rides on them instead of running as a
 kernel of its own (:class:`FollowingNorm` into the product before it, :class:`ScaledRows` out
@@ -33,7 +35,7 @@ import torch
 from . import kernels
 
 TENSOR_CORE_MAX_TOKENS = 64
-FORCE: str | None = None      # "tcgen05", "library" or None (choose by size)
+FORCE: str | None = None      # "tcgen05", "pair", "library" or None (choose by size)
 FUSE_NORMS = True             # let a norm between two tensor-core products ride on them
 CHAIN = False                 # run deferred products of a small step as one persistent kernel
 
@@ -113,7 +115,7 @@ def _open_scale(x) -> tuple[torch.Tensor, dict]:
 def use_tensor_core_kernel(x: torch.Tensor, weight: torch.Tensor) -> bool:
     if x.dtype != torch.bfloat16 or not kernels.gemm_bf16_supports(x, weight):
         return False
-    if FORCE is not None:
+    if FORCE is not None and FORCE != "pair":
         return FORCE == "tcgen05"
     return x.shape[0] <= TENSOR_CORE_MAX_TOKENS
 
@@ -161,6 +163,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
     flush()
     if scale:
         raise kernels.KernelError("linear: rows with an open scale need the tensor-core product")
+    if FORCE == "pair" and fault is not None and kernels.gemm_bf16_supports(x, weight):
+        return kernels.gemm_bf16_pair(x, weight, out, fault, bias=bias)
     if bias is None:
         torch.mm(x, weight.t(), out=out)
     else:

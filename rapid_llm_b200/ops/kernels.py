@@ -430,7 +430,7 @@ def attention_mma(
             _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
-            _ptr(fault), int(PDL), 1 if decode_kernel == "mma" else 0, int(decode_rows), int(chunk_rows), _stream(),
+            _ptr(fault), int(PDL), {"auto": 0, "mma": 1, "deep": 2, "shallow": 3}[decode_kernel], int(decode_rows), int(chunk_rows), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )
@@ -550,6 +550,47 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
     return out
 
 
+def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor,
+                   bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[T, N] = x[T, K] @ w[N, K]^T (+ bias)`` in bfloat16 for steps of many tokens: pairs of CTAs on
+    256 x 256 tiles (``tcgen05.mma.cta_group::2``), persistent over the tiles."""
+    _need_cuda(x, w, out, fault, bias)
+    for name, tensor in (("x", x), ("w", w), ("out", out)):
+        _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
+    tokens, k = x.shape
+    n_out = out.shape[1]
+    if w.shape != (n_out, k) or out.shape[0] != tokens:
+        raise KernelError(f"gemm_bf16_pair: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+    if not gemm_bf16_supports(x, w):
+        raise KernelError("gemm_bf16_pair: the inner size must be a multiple of 8 and the operands 16-byte aligned")
+    if bias is not None:
+        _expect("bias", bias, torch.float32), _contig("bias", bias)
+        if bias.shape != (n_out,):
+            raise KernelError("gemm_bf16_pair: the bias does not have the weight's rows")
+    if tokens == 0:
+        return out
+    lib = gemm_lib()
+    if not getattr(lib, "_pair_declared", False):
+        lib.rl_gemm_bf16_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p]
+        lib.rl_gemm_bf16_pair.restype = c_int
+        lib.rl_gemm_bf16_pair_scratch_floats.restype = c_longlong
+        lib.rl_gemm_bf16_pair_counter_words.restype = c_int
+        lib._pair_declared = True
+    state = _PAIR_STATE.get(fault.device)
+    if state is None:        # partial tiles of the pairs' first segments, and the tiles' counters (the kernel keeps them zero)
+        state = (torch.empty(lib.rl_gemm_bf16_pair_scratch_floats(), dtype=torch.float32, device=fault.device),
+                 torch.zeros(lib.rl_gemm_bf16_pair_counter_words(), dtype=torch.int32, device=fault.device))
+        _PAIR_STATE[fault.device] = state
+    _check(lib.rl_gemm_bf16_pair(_ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(PDL), _ptr(bias), _ptr(state[0]),
+                                 _ptr(state[1]), _ptr(fault), _stream()),
+           f"gemm_bf16_pair({tokens}x{k} by {n_out})")
+    return out
+
+
+_PAIR_STATE: dict[torch.device, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
 class _ChainPhase(ctypes.Structure):
     """``RlChainPhase`` of ``csrc/gemm_chain.cu``."""
 
@@ -569,9 +610,9 @@ def _chain_lib() -> ctypes.CDLL:
     lib = gemm_lib()
     if not getattr(lib, "_chain_declared", False):
         lib.rl_gemm_chain.argtypes = [c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
-        lib.rl_gemm_chain.restype = c_int
         lib.rl_gemm_chain_scratch_floats.argtypes = [c_void_p, c_int, c_int]
         lib.rl_gemm_chain_scratch_floats.restype = c_longlong
+        lib.rl_gemm_chain.restype = c_int
         lib.rl_gemm_chain_counter_words.restype = c_int
         lib._chain_declared = True
     return lib
@@ -582,6 +623,9 @@ def gemm_chain_reset(device=None) -> None:
     for key, state in _CHAIN_STATE.items():
         if device is None or key == torch.device(device):
             state["counters"].zero_()
+    for key, state in _PAIR_STATE.items():
+        if device is None or key == torch.device(device):
+            state[1].zero_()
 
 
 def gemm_chain(products: list[dict], fault: torch.Tensor, trace: torch.Tensor | None = None) -> None:

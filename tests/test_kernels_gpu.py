@@ -276,6 +276,37 @@ def test_gemm_bf16_when_a_cta_walks_several_tiles(t, n, k_, swiglu):
         torch.testing.assert_close(out[:, begin:end].float(), want, rtol=6e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("t,n,k_,bias", [
+    (65, 130, 64, False), (128, 256, 128, True), (256, 256, 256, False),      # one tile, shared by as many pairs as get eight k-blocks
+    (300, 520, 264, True), (100, 6144, 4096, False),                          # ragged edges; the 128-token tile
+    (512, 4096, 12288, False),                                                # 32 tiles, every one shared by two or three pairs
+    (1000, 1300, 1024, True),
+    (2048, 6144, 4096, False),                                                # 192 tiles on 74 pairs: two whole rounds and 44 shared tiles
+    (2048, 24576, 4096, False), (4096, 4096, 12288, True),
+])
+def test_gemm_bf16_pair_of_ctas_on_one_tile(t, n, k_, bias):
+    """``tcgen05.mma.cta_group::2``: two CTAs, each with half of a 256 x 256 tile's operands, one issuing thread;
+    whole rounds of tiles dealt round-robin, the left-over tiles' k-ranges shared between pairs and summed by the
+    owner in run order.  Against the float32 product; a second call gives the same bits."""
+    x = device_rand((t, k_), 1.0, seed=60)
+    w = device_rand((n, k_), 0.05, seed=61)
+    b = torch.randn(n, generator=torch.Generator().manual_seed(62)).to(DEV) if bias else None
+    fault = fault_word()
+    outs = []
+    for _ in range(2):
+        out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        k().gemm_bf16_pair(x, w, out, fault, bias=b)
+        outs.append(out)
+    assert fault.item() == 0 and torch.equal(outs[0], outs[1])
+    step = 4096
+    for begin in range(0, n, step):
+        end = min(n, begin + step)
+        want = x.float() @ w[begin:end].float().T
+        if bias:
+            want = want + b[begin:end]
+        torch.testing.assert_close(outs[0][:, begin:end].float(), want, rtol=6e-3, atol=2e-3)
+
+
 @pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
 @pytest.mark.parametrize("t,n,k_,swiglu", [(16, 300, 1024, False), (64, 256, 4096, False), (40, 57100, 640, False),
                                            (64, 200, 4096, True), (128, 260, 2048, False), (256, 300, 1024, False)])
@@ -608,7 +639,7 @@ def test_attention_mma(hq, hkv, d, page, window, splits):
     torch.testing.assert_close(got, want, **for_dtype(dtype))
 
 
-@pytest.mark.parametrize("decode_kernel", ["auto", "mma"])
+@pytest.mark.parametrize("decode_kernel", ["auto", "mma", "deep", "shallow"])
 @pytest.mark.parametrize(
     "hq,hkv,page,window,splits,lengths,new_counts",
     [(32, 8, 16, 0, None, [1, 5, 128, 129, 1000, 257, 2049], [1, 1, 1, 1, 1, 1, 1]),
@@ -619,13 +650,28 @@ def test_attention_mma(hq, hkv, d, page, window, splits):
      (8, 8, 256, 77, 4, [900], [5])],
 )
 def test_attention_decode_kernels(hq, hkv, page, window, splits, lengths, new_counts, decode_kernel):
-    """Decode tiles at head size 128: the tcgen05 kernel (auto) and the mma.sync tiles give the plain result."""
+    """Decode tiles at head size 128: the tcgen05 kernel (auto; with deep rings, one CTA per multiprocessor; with
+    shallow rings, two) and the mma.sync tiles give the plain result."""
     dtype, d = torch.bfloat16, 128
     case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=page + hq)
     scale = d**-0.5
     got = run_mma(case, lengths, new_counts, hq, hkv, d, scale, window, splits, decode_kernel)
     want = plain_paged(case, dtype, lengths, new_counts, scale, window)
     torch.testing.assert_close(got, want, **for_dtype(dtype))
+
+
+def test_attention_decode_of_more_items_than_multiprocessors():
+    """Ninety requests over four kv heads are 360 CTAs: the step takes the shallow rings by itself, two CTAs per
+    multiprocessor, and gives the bits of the deep rings (the same sums in the same order)."""
+    dtype, d, hq, hkv, page = torch.bfloat16, 128, 8, 4, 16
+    generator = torch.Generator().manual_seed(3)
+    lengths = torch.randint(1, 700, (90,), generator=generator).tolist()
+    new_counts = [1] * len(lengths)
+    case = paged_case(dtype, hq, hkv, d, page, lengths, new_counts, seed=31)
+    scale = d**-0.5
+    got = {which: run_mma(case, lengths, new_counts, hq, hkv, d, scale, 0, None, which) for which in ("auto", "deep", "shallow")}
+    assert torch.equal(got["auto"], got["shallow"]) and torch.equal(got["deep"], got["shallow"])
+    torch.testing.assert_close(got["auto"], plain_paged(case, dtype, lengths, new_counts, scale, 0), **for_dtype(dtype))
 
 
 @pytest.mark.parametrize("decode_kernel", ["auto", "mma"])
