@@ -17,8 +17,8 @@
 // tile is then split over the CTAs of a thread-block cluster: each accumulates its slice in
 // tensor memory, parks the float32 partial tile in its own shared memory, and after a
 // cluster barrier every CTA sums a share of the tile's token columns over all ranks through
-// distributed shared memory, in rank order (so the sum does not depend on timing), and
-// stores it.  No global scratch, no atomics.  With many tokens the k-range is not split and a
+// distributed shared memory (16 bytes, four weight rows of a column, per load), in rank order
+// (so the sum does not depend on timing), and stores it.  No global scratch, no atomics.  With many tokens the k-range is not split and a
 // CTA walks several tiles, the epilogue of one overlapping the products of the next.
 //
 // A norm between two products can ride on them instead of being a kernel of its own (steps of up
@@ -359,54 +359,96 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 
   if (args.k_split > 1) {
-    // sum the partial tiles of the cluster's CTAs: rank r takes the token columns r, r + k_split, ...
+    // sum the partial tiles of the cluster's CTAs: rank r takes the token columns r, r + k_split, ...; each of
+    // its four epilogue warps takes every fourth of those, a lane four neighbouring weight rows of the column.
+    // What bounds this step is the number of requests between the CTAs' shared memories, not their latency
+    // (a 64-token tile summed with 4-byte loads took 3.3 us, eight columns a rank): a lane fetches its four
+    // rows of a rank's partial tile in one 16-byte load, a warp 512 consecutive bytes.
     __syncwarp();
     cluster_sync();
     if (warp >= 2 && Shape::kCanSplit && !*aborted) {
-      const int n_local = (warp & 3) * 32 + lane;
       const int tile = static_cast<int>(blockIdx.y);
       const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
-      const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
-      // where the other ranks keep this thread's row of the partial tile
+      const int rows0 = 4 * lane;                                // this lane's rows of the tile
+      const int n = n_tile * kTileN + rows0, t0 = t_tile * BN;
+      // where the other ranks keep these rows of a column of the partial tile
       uint32_t peer[8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) peer[q] = q < args.k_split ? peer_smem(smem_base + n_local * 4, q) : 0u;
+      for (int q = 0; q < 8; ++q) peer[q] = q < args.k_split ? peer_smem(smem_base + rows0 * 4, q) : 0u;
       const bool scaled = BN <= 64 && args.sumsq_in != nullptr;
       const bool norm_follows = !kSwiglu && args.residual != nullptr;
-      const float norm_w = norm_follows && n < args.N ? args.norm_weight[n] : 0.0f;
-      const float bias_gate = args.bias != nullptr && n < args.N ? args.bias[n] : 0.0f;
-      const float bias_up = kSwiglu && args.bias != nullptr && n < args.N ? args.bias[args.up_offset + n] : 0.0f;
-      for (int j = rank; j < BN && t0 + j < args.T; j += args.k_split) {
-        // all loads first, the sums (in rank order) after: a remote load takes hundreds of cycles,
-        // and a warp that adds each value as it arrives pays that once per rank
-        float gate_part[8], up_part[8];
-        const size_t at = static_cast<size_t>(t0 + j) * args.N + n;
-        const float before = norm_follows && n < args.N ? args.residual[at] : 0.0f;
+      float norm_w[4], bias_gate[4], bias_up[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const bool live = n + r < args.N;
+        norm_w[r] = norm_follows && live ? args.norm_weight[n + r] : 0.0f;
+        bias_gate[r] = args.bias != nullptr && live ? args.bias[n + r] : 0.0f;
+        bias_up[r] = kSwiglu && args.bias != nullptr && live ? args.bias[args.up_offset + n + r] : 0.0f;
+      }
+      // output rows are 16-byte-aligned groups of four only if the row length allows it
+      const bool wide_rows = (args.N & 3) == 0;
+      for (int j = rank + (warp - 2) * args.k_split; j < BN && t0 + j < args.T; j += 4 * args.k_split) {
+        // all loads first, the sums (in rank order) after
+        float4 gate_part[8], up_part[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          gate_part[q] = q < args.k_split ? load_peer_f32(peer[q] + j * kTileN * 4) : 0.0f;
-          up_part[q] = kSwiglu && q < args.k_split ? load_peer_f32(peer[q] + (BN + j) * kTileN * 4) : 0.0f;
+          gate_part[q] = q < args.k_split ? load_peer_f32x4(peer[q] + j * kTileN * 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          up_part[q] = kSwiglu && q < args.k_split ? load_peer_f32x4(peer[q] + (BN + j) * kTileN * 4)
+                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        float gate = 0.0f, up = 0.0f;
+        float gate[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           if (q < args.k_split) {
-            gate += gate_part[q];
-            up += up_part[q];
+            gate[0] += gate_part[q].x; gate[1] += gate_part[q].y; gate[2] += gate_part[q].z; gate[3] += gate_part[q].w;
+            up[0] += up_part[q].x; up[1] += up_part[q].y; up[2] += up_part[q].z; up[3] += up_part[q].w;
           }
         }
-        if (scaled) {
-          gate *= row_scale[j];
-          up *= row_scale[j];
+        const float scale = scaled ? row_scale[j] : 1.0f;
+        const size_t at = static_cast<size_t>(t0 + j) * args.N + n;
+        float result[4], squares = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float g = gate[r] * scale + bias_gate[r], u = up[r] * scale + bias_up[r];
+          result[r] = kSwiglu ? silu_mul(g, u) : g;
         }
-        gate += bias_gate;
-        up += bias_up;
         if (norm_follows) {
-          const float sq = warp_sum(n < args.N ? store_for_norm(args, at, norm_w, before + gate) : 0.0f);
-          if (lane == 0)
-            args.sumsq_out[static_cast<size_t>(t0 + j) * (4 * args.n_tiles) + 4 * n_tile + (warp & 3)] = sq;
-        } else if (n < args.N) {
-          args.out[at] = __float2bfloat16_rn(kSwiglu ? silu_mul(gate, up) : gate);
+          float before[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          if (wide_rows && n + 3 < args.N) {
+            const float4 old = *reinterpret_cast<const float4*>(args.residual + at);
+            before[0] = old.x; before[1] = old.y; before[2] = old.z; before[3] = old.w;
+          } else {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+              if (n + r < args.N) before[r] = args.residual[at + r];
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            before[r] += result[r];                                // the new residual
+            result[r] = before[r] * norm_w[r];
+            if (n + r < args.N) squares += before[r] * before[r];
+          }
+          if (wide_rows && n + 3 < args.N) {
+            *reinterpret_cast<float4*>(args.residual + at) = make_float4(before[0], before[1], before[2], before[3]);
+          } else {
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+              if (n + r < args.N) args.residual[at + r] = before[r];
+          }
+          // the whole tile's squares of this token in the first of the tile's four places, zeros in the others
+          const float sq = warp_sum(squares);
+          if (lane < 4) args.sumsq_out[static_cast<size_t>(t0 + j) * (4 * args.n_tiles) + 4 * n_tile + lane] = lane == 0 ? sq : 0.0f;
+        }
+        if (wide_rows && n + 3 < args.N) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(result[0], result[1]), hi = __floats2bfloat162_rn(result[2], result[3]);
+          uint2 packed;
+          packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(args.out + at) = packed;
+        } else {
+#pragma unroll
+          for (int r = 0; r < 4; ++r)
+            if (n + r < args.N) args.out[at + r] = __float2bfloat16_rn(result[r]);
         }
       }
     }
@@ -449,8 +491,8 @@ static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, GemmA
     configured = true;
   }
   // how many CTAs the GPU holds at once, and how finely to split k so that they all stream
-  // (three of the smallest tiles' CTAs fit an SM and splitting for three pays there; measured)
-  const int resident = sm_count() * (Shape::kShareSm ? (!kSwiglu && BN <= 16 ? 3 : 2) : 1);
+  // (three CTAs of the plain products' small tiles fit an SM and splitting for three pays there; measured)
+  const int resident = sm_count() * (Shape::kShareSm ? (!kSwiglu ? 3 : 2) : 1);
   const int tiles = args.n_tiles * args.t_tiles;
   int split = 1;
   if (Shape::kCanSplit) {

@@ -246,6 +246,14 @@ __device__ __forceinline__ float load_peer_f32(uint32_t remote_address) {
   return value;
 }
 
+__device__ __forceinline__ float4 load_peer_f32x4(uint32_t remote_address) {
+  float4 value;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
+               : "r"(remote_address));
+  return value;
+}
+
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
 // eight rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
 __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_address) {
