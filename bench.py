@@ -46,10 +46,10 @@ SHAPES = {
 }
 CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
 PUBLISHED_TOK_S = 216.6   # Qwen3-8B bf16, batch 8, 1x A10: docs/benchmark_models.md:191 of the reference (other hardware)
-# The reference publishes no B200 number.  What value is divided by is the reference's own engine on this
-# workload on a B200 of this pool, as the round-end run of the previous round recorded it.
+# The reference publishes no B200 number.  What `value` is divided by is the reference's own engine on this
+# workload on one B200, measured by `bench.py --impl reference --steps 20 --warmup 5` on a fresh machine.
 REFERENCE_SAME_GPU_TOK_S = 1500.4
-BASELINE_NOTE = ("1500.4 tok/s: the unmodified reference engine, this workload, one B200 (recorded in BASELINE.md); "
+BASELINE_NOTE = ("1500.4 tok/s: the unmodified reference engine, this workload, one B200 (bench.py --impl reference); "
                  "its only published figure is 216.6 tok/s on 1x A10 (docs/benchmark_models.md:191)")
 
 
@@ -153,6 +153,17 @@ def random_prompts(count: int, length: int, vocab: int, seed: int) -> list[list[
     return torch.randint(0, vocab, (count, length), generator=generator).tolist()
 
 
+TEMPERATURE = 0.0      # > 0: every request samples with this temperature and top-p 0.9 (set by --temperature)
+
+
+def sampling_params(max_gen_len: int, index: int):
+    from rapid_llm_b200 import SamplingParams
+
+    if TEMPERATURE > 0:
+        return SamplingParams(temperature=TEMPERATURE, top_p=0.9, repetition_penalty=1.0, max_gen_len=max_gen_len, seed=index)
+    return SamplingParams.greedy(max_gen_len=max_gen_len)
+
+
 def decode_run(llm, batch: int, steps: int, warmup: int, seed: int) -> dict:
     """Prefill ``batch`` prompts, then time ``steps`` decode steps on the device and by wall clock."""
     import torch
@@ -164,9 +175,9 @@ def decode_run(llm, batch: int, steps: int, warmup: int, seed: int) -> dict:
     # every request must still be decoding when the last timed step runs: the prompts are
     # prefilled two per step while the earlier requests already decode
     prefill_steps = -(-batch * PROMPT_LEN // PREFILL_TOKENS)
-    params = SamplingParams.greedy(max_gen_len=4 * steps + warmup + prefill_steps + 8)
     vocab = runner.model.spec.vocab_size
-    requests = [scheduler.add_request(p, params) for p in random_prompts(batch, PROMPT_LEN, vocab, seed)]
+    requests = [scheduler.add_request(p, sampling_params(4 * steps + warmup + prefill_steps + 8, index))
+                for index, p in enumerate(random_prompts(batch, PROMPT_LEN, vocab, seed))]
     while any(r.num_computed_tokens < len(r.prompt_token_ids) for r in requests):
         scheduler.step()                                   # prefill, untimed
     for _ in range(warmup):
@@ -416,8 +427,7 @@ def run_ours(args) -> dict:
     if args.timeline:
         return write_timeline(llm, args.batch, args.timeline, seed=args.batch, step=args.timeline_step)
     check = graph_check(llm, seed=5)
-    prefill = prefill_run(llm, args.warmup, seed=11) if "prefill" in args.parts else {"device_ms": float("nan"), "e2e_ms": float("nan")}
-    prefill_ms = prefill["device_ms"]
+    prefill = prefill_run(llm, args.warmup, seed=11) if "prefill" in args.parts else None
     results = {}
     for batch in batches:
         if batch == args.batch or "points" not in args.parts:
@@ -457,18 +467,20 @@ def run_ours(args) -> dict:
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed per step)",
             "baseline_ref": BASELINE_NOTE, "peaks": peaks["source"], "timed": "median of 3 windows of `steps` steps",
+            "sampling": f"temperature {TEMPERATURE}, top-p 0.9" if TEMPERATURE > 0 else "greedy",
         },
         "e2e": {
             "value": round(main["tokens"] / (main["wall_ms"] / 1000.0), 1), "unit": "tok/s",
             "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1),
-            "ttft_ms": round(prefill["e2e_ms"], 3), "tpot_ms": round(main["wall_ms"] / args.steps, 4),
+            "ttft_ms": round(prefill["e2e_ms"], 3) if prefill else None, "tpot_ms": round(main["wall_ms"] / args.steps, 4),
         },
         "windows_ms": main["windows_ms"],
         "check": check,
         "gpu_launches": main["launches"],
-        "prefill": {
-            "value": round(PREFILL_TOKENS / (prefill_ms / 1000.0), 1), "tokens": PREFILL_TOKENS,
-            "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms / 1000.0) / (peaks["bf16_tflops"] * 1e12), 4),
+        "prefill": None if prefill is None else {
+            "value": round(PREFILL_TOKENS / (prefill["device_ms"] / 1000.0), 1), "tokens": PREFILL_TOKENS,
+            "ms": round(prefill["device_ms"], 3),
+            "frac": round(flops / (prefill["device_ms"] / 1000.0) / (peaks["bf16_tflops"] * 1e12), 4),
             "e2e_ms": round(prefill["e2e_ms"], 3),
         },
         "roofline": {
@@ -581,6 +593,8 @@ def main() -> int:
                         "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
                         "prompts of mixed lengths through generate()")
     parser.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
+    parser.add_argument("--temperature", type=float, default=0.0, help="sample with this temperature and top-p 0.9 "
+                        "instead of greedily (the benchmark's workload is greedy)")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (both numbers are reported)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--parts", default="prefill,points", help="extra measurements beside the main decode run "
@@ -598,6 +612,7 @@ def main() -> int:
         args.warmup = 3
     args.parts = {part for part in args.parts.split(",") if part}
     args.points = [int(x) for x in args.points.split(",") if x]
+    globals()["TEMPERATURE"] = args.temperature
     globals()["PROMPT_LEN"] = args.prompt_len
     globals()["CONTEXT"] = args.context
     result = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -99,6 +99,19 @@ def test_the_command_line_from_a_folder_to_token_ids(tiny_dirs, tiny_plain, tmp_
         assert got == full[:cut] and reason == ("eos" if stop in full else "length")
 
 
+def test_the_pool_is_sized_from_free_memory_when_no_size_is_given(tiny_dirs, tiny_plain):
+    """Without ``max_gpu_num_blocks`` the pool takes what the slots can hold at full length (a tiny model on an
+    empty GPU is far from the memory limit), and generation runs on it."""
+    from rapid_llm_b200 import SamplingParams
+
+    config, weights = tiny_plain["A"]
+    llm = make_llm(tiny_dirs["A"], "float32", "A", max_gpu_num_blocks=None, max_num_seqs=3)
+    pool = llm.runner.cache.pools[0]
+    assert pool.num_pages == 3 * (128 // PAGE_SIZES["A"])
+    prompt = random_prompts(config["vocab_size"], [11], 4)[0]
+    assert llm.generate([prompt], SamplingParams.greedy(max_gen_len=5))[0].token_ids == greedy_generate(config, weights, prompt, 5)
+
+
 def test_a_token_budget_below_the_number_of_slots(tiny_dirs, tiny_plain):
     """Six tokens a step and eight slots: five requests decoding from a graph pad to six rows, within the
     budget (the next power of two would not fit)."""
