@@ -1,8 +1,12 @@
-"""Toy parts defined here, outside the framework: a feed-forward that routes every token to one
-of several experts and a position encoding of its own (interpolated positions, a partial
-rotation).  Both are registered, named by a configuration layer by layer beside the stock
-parts, given random weights, loaded and stepped without a change to the framework's files, and
-compared with a plain restatement built from the plain implementation's functions."""
+"""Toy parts of three other roles, defined here and nowhere in the framework: a feed-forward that routes
+each token to one of a few experts, a position encoding that is not the rotary one the framework ships, and an
+embedding that adds a learned row per absolute position.  They are registered, written as a random model
+folder, loaded, and stepped whole, in portions and token by token through captured graphs, beside the
+framework's own attention and feed-forward in other layers (different feed-forwards, windows and position
+encodings layer by layer), in both precisions, against a plain computation that is written out below.
+
+The toys are arithmetic for a test, not a model of anyone's.
+"""
 
 from __future__ import annotations
 
@@ -10,71 +14,105 @@ import dataclasses
 
 import pytest
 import torch
-from plain_qwen3 import apply_rope, causal_attention, rms_norm, rope_angles, swiglu
-from tolerances import for_dtype
+from plain_qwen3 import apply_rope, causal_attention, load_model_dir, rms_norm, rope_angles, swiglu
+from tolerances import at_scale
 
 pytestmark = pytest.mark.gpu
 
-HIDDEN, HEADS, KV_HEADS, HEAD_DIM, VOCAB, EXPERTS, INNER = 48, 6, 2, 32, 131, 3, 40
-ROTARY, SCALE, THETA, EPS, POSITIONS = 16, 4.0, 5000.0, 1e-5, 96
+HIDDEN, VOCAB, POSITIONS = 48, 211, 96
+HEADS, KV_HEADS, HEAD_DIM, ROTARY = 6, 2, 32, 16
+EPS, THETA, SLOW = 3e-6, 5000.0, 2.5
+WINDOW = 8
+EXPERTS = (3, 0, 2)          # experts of the routed feed-forward per layer; 0 = the framework's dense one
+INNER = 40
+SAFE_MARGIN = 0.05           # smallest gap between the two best router logits that the test's sequences keep
+
+
+def toy_angles(positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The toy position encoding: frequencies 1 / (1 + i), positions slowed by a constant."""
+    inv_freq = 1.0 / (1.0 + torch.arange(ROTARY // 2, dtype=torch.float32))
+    angles = (positions.to(torch.float32) / SLOW)[:, None] * inv_freq[None, :]
+    return torch.cos(angles), torch.sin(angles)
 
 
 def register_toys():
     from rapid_llm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
-    from rapid_llm_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding, TensorSpec
+    from rapid_llm_b200.ops import kernels
+    from rapid_llm_b200.parts import TensorSpec
+    from rapid_llm_b200.parts.base import EMBEDDINGS, FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, Part, PositionEncoding
 
-    @FEED_FORWARDS.register("toy_routed")
-    class ToyRouted(FeedForward):
-        """y = p_e * down_e(relu(up_e x)) with e the expert of the largest router logit and p its
-        softmax probability."""
-
-        def __init__(self, *, hidden_size, inner_size, experts, dtype, device):
+    @POSITION_ENCODINGS.register("toy_slowed_rotation")
+    class ToySlowedRotation(PositionEncoding):
+        def __init__(self, *, rotary_dim, max_positions, dtype, device):
             super().__init__(dtype=dtype, device=device)
-            self.experts = experts
-            self.router = self.new_storage((experts, hidden_size), "matrix")
-            self.up = [self.new_storage((inner_size, hidden_size), "matrix") for _ in range(experts)]
-            self.down = [self.new_storage((hidden_size, inner_size), "matrix") for _ in range(experts)]
-            self.shapes = {"router.weight": (experts, hidden_size)}
-            for e in range(experts):
-                self.shapes[f"experts.{e}.up.weight"] = (inner_size, hidden_size)
-                self.shapes[f"experts.{e}.down.weight"] = (hidden_size, inner_size)
-
-        def tensor_specs(self):
-            return {name: TensorSpec(shape) for name, shape in self.shapes.items()}
-
-        def load_tensor(self, name, tensor):
-            if name == "router.weight":
-                self.router.copy_(tensor)
-            else:
-                _, index, which, _ = name.split(".")
-                (self.up if which == "up" else self.down)[int(index)].copy_(tensor)
-
-        def forward(self, x, batch):
-            logits = x.float() @ self.router.float().T
-            probability, expert = torch.softmax(logits, dim=-1).max(dim=-1)
-            out = torch.zeros_like(x)
-            for e in range(self.experts):
-                rows = torch.nonzero(expert == e).flatten()
-                if rows.numel():
-                    hidden = torch.relu(x[rows].float() @ self.up[e].float().T)
-                    out[rows] = (probability[rows, None] * (hidden @ self.down[e].float().T)).to(x.dtype)
-            return out
-
-    @POSITION_ENCODINGS.register("toy_interpolated")
-    class ToyInterpolated(PositionEncoding):
-        """Rotation by the angles of position / scale over the first ``rotary_dim`` sizes of a head."""
-
-        def __init__(self, *, rotary_dim, theta, scale, max_positions, dtype, device, head_dim=None):
-            super().__init__(dtype=dtype, device=device)
-            cos, sin = rope_angles(torch.arange(max_positions) / scale, rotary_dim, theta)
-            self.cos, self.sin = cos.to(self.device).contiguous(), sin.to(self.device).contiguous()
+            assert rotary_dim == ROTARY
+            cos, sin = toy_angles(torch.arange(max_positions))
+            self.cos, self.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
 
         def tables(self):
             return self.cos, self.sin
 
+    @EMBEDDINGS.register("toy_token_plus_position")
+    class ToyTokenPlusPosition(Part):
+        """x_t = E[id_t] + P[position_t]."""
+
+        def __init__(self, *, vocab_size, hidden_size, max_positions, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.weight = self.new_storage((vocab_size, hidden_size), "matrix")
+            self.places = self.new_storage((max_positions, hidden_size), "matrix")
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec(tuple(self.weight.shape)), "places": TensorSpec(tuple(self.places.shape))}
+
+        def load_tensor(self, name, tensor):
+            {"weight": self.weight, "places": self.places}[name].copy_(tensor)
+
+        def forward(self, batch):
+            out = batch.workspace.get("embedded", batch.num_tokens, self.weight.shape[1], self.dtype)
+            kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback)
+            summed = out.float() + self.places[batch.positions.long()].float()      # device indices: capturable
+            return out.copy_(summed.to(self.dtype))
+
+    @FEED_FORWARDS.register("toy_one_of_experts")
+    class ToyOneOfExperts(FeedForward):
+        """Router logits in float32, the best expert alone runs for a token, its result times its softmax weight.
+        Every expert is computed for every token and masked: no shape depends on the routing, so a decode
+        step can be captured."""
+
+        def __init__(self, *, hidden_size, inner_size, experts, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.router = self.new_storage((experts, hidden_size), "vector")      # kept in float32
+            self.up = self.new_storage((experts, inner_size, hidden_size), "matrix")
+            self.down = self.new_storage((experts, hidden_size, inner_size), "matrix")
+
+        def tensor_specs(self):
+            specs = {"router.weight": TensorSpec(tuple(self.router.shape), "vector")}
+            for expert in range(self.up.shape[0]):
+                specs[f"experts.{expert}.up.weight"] = TensorSpec(tuple(self.up.shape[1:]))
+                specs[f"experts.{expert}.down.weight"] = TensorSpec(tuple(self.down.shape[1:]))
+            return specs
+
+        def load_tensor(self, name, tensor):
+            if name == "router.weight":
+                self.router.copy_(tensor.to(torch.float32))
+                return
+            _, expert, which, _ = name.split(".")
+            (self.up if which == "up" else self.down)[int(expert)].copy_(tensor)
+
+        def forward(self, x, batch):
+            logits = x.float() @ self.router.T
+            share = torch.softmax(logits, dim=-1)
+            best = logits.argmax(dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for expert in range(self.up.shape[0]):
+                inner = torch.relu(x @ self.up[expert].T)
+                result = (inner @ self.down[expert].T).float()
+                out += result * (share[:, expert] * (best == expert))[:, None]
+            return out.to(x.dtype)
+
     @dataclasses.dataclass(frozen=True)
     class ToyPartsConfig:
-        vocab_size: int = VOCAB
+        vocab_size: int
         architecture = "ToyPartsForCausalLM"
         model_type = "toy_parts"
 
@@ -87,110 +125,145 @@ def register_toys():
 
         def to_spec(self):
             norm = PartSpec("rmsnorm", {"size": HIDDEN, "eps": EPS})
-
-            def attention(position):
-                return PartSpec("gqa_attention", {
+            toy_position = PartSpec("toy_slowed_rotation", {"rotary_dim": ROTARY, "max_positions": POSITIONS})
+            rope = PartSpec("rope", {"head_dim": HEAD_DIM, "rotary_dim": ROTARY, "theta": THETA, "max_positions": POSITIONS})
+            layers = []
+            for index, experts in enumerate(EXPERTS):
+                attention = PartSpec("gqa_attention", {
                     "hidden_size": HIDDEN, "num_heads": HEADS, "num_kv_heads": KV_HEADS, "head_dim": HEAD_DIM,
-                    "position": position, "qk_norm": True, "qk_norm_eps": EPS})
-
-            toy_position = PartSpec("toy_interpolated", {
-                "rotary_dim": ROTARY, "theta": THETA, "scale": SCALE, "max_positions": POSITIONS})
-            rope = PartSpec("rope", {"head_dim": HEAD_DIM, "rotary_dim": HEAD_DIM, "theta": THETA, "max_positions": POSITIONS})
-            routed = PartSpec("toy_routed", {"hidden_size": HIDDEN, "inner_size": INNER, "experts": EXPERTS})
-            dense = PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": INNER})
-            layers = (
-                LayerSpec("prenorm", attention(toy_position), routed, norm, "model.layers.0."),
-                LayerSpec("prenorm", attention(rope), dense, norm, "model.layers.1."),
-                LayerSpec("prenorm", attention(toy_position), dense, norm, "model.layers.2."),
-            )
+                    "position": rope if index == 1 else toy_position, "qk_norm": index != 2, "qk_norm_eps": EPS,
+                    "window": WINDOW if index == 1 else 0,
+                })
+                if experts:
+                    ffn = PartSpec("toy_one_of_experts", {"hidden_size": HIDDEN, "inner_size": INNER, "experts": experts})
+                else:
+                    ffn = PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": 2 * INNER})
+                layers.append(LayerSpec("prenorm", attention, ffn, norm, f"model.layers.{index}."))
             return ModelSpec(
                 architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=HIDDEN, max_positions=POSITIONS,
-                embedding=PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN}),
-                layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(3)), final_norm=norm,
-                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "tied": False}),
+                embedding=PartSpec("toy_token_plus_position",
+                                   {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "max_positions": POSITIONS}),
+                layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(len(layers))), final_norm=norm,
+                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "tied": True}),
             )
 
     register_architecture(ToyPartsConfig)
     return ToyPartsConfig
 
 
-def plain_logits(weights, tokens):
-    """The same model from the plain implementation's functions, whole sequence, no cache."""
-    weights = {name: value.float() for name, value in weights.items()}
-    positions = torch.arange(len(tokens))
-    h = weights["model.embed_tokens.weight"][torch.as_tensor(tokens)]
-
-    def attention(x, prefix, cos, sin):
-        count = x.shape[0]
-        q = (x @ weights[prefix + "q_proj.weight"].T).view(count, HEADS, HEAD_DIM)
-        k = (x @ weights[prefix + "k_proj.weight"].T).view(count, KV_HEADS, HEAD_DIM)
-        v = (x @ weights[prefix + "v_proj.weight"].T).view(count, KV_HEADS, HEAD_DIM)
-        q = apply_rope(rms_norm(q, weights[prefix + "q_norm.weight"], EPS), cos, sin)
-        k = apply_rope(rms_norm(k, weights[prefix + "k_norm.weight"], EPS), cos, sin)
-        return causal_attention(q, k, v, HEAD_DIM**-0.5).reshape(count, -1) @ weights[prefix + "o_proj.weight"].T
-
-    def routed(x, prefix):
-        probability, expert = torch.softmax(x @ weights[prefix + "router.weight"].T, dim=-1).max(dim=-1)
-        out = torch.zeros_like(x)
-        for row in range(x.shape[0]):
-            e = int(expert[row])
-            hidden = torch.relu(x[row] @ weights[f"{prefix}experts.{e}.up.weight"].T)
-            out[row] = probability[row] * (hidden @ weights[f"{prefix}experts.{e}.down.weight"].T)
-        return out
-
-    toy_angles = rope_angles(positions / SCALE, ROTARY, THETA)
-    stock_angles = rope_angles(positions, HEAD_DIM, THETA)
-    for index, (angles, feed_forward) in enumerate([(toy_angles, routed), (stock_angles, None), (toy_angles, None)]):
+@torch.no_grad()
+def plain_logits(weights: dict, ids: list[int]) -> tuple[torch.Tensor, float]:
+    """Logits of one whole sequence in float32, and the smallest gap between the two best router logits."""
+    positions = torch.arange(len(ids))
+    h = weights["model.embed_tokens.weight"][ids] + weights["model.embed_tokens.places"][positions]
+    smallest = float("inf")
+    for index, experts in enumerate(EXPERTS):
         prefix = f"model.layers.{index}."
-        h = h + attention(rms_norm(h, weights[prefix + "input_layernorm.weight"], EPS), prefix + "self_attn.", *angles)
+        x = rms_norm(h, weights[prefix + "input_layernorm.weight"], EPS)
+        tokens = x.shape[0]
+        q = (x @ weights[prefix + "self_attn.q_proj.weight"].T).view(tokens, HEADS, HEAD_DIM)
+        k = (x @ weights[prefix + "self_attn.k_proj.weight"].T).view(tokens, KV_HEADS, HEAD_DIM)
+        v = (x @ weights[prefix + "self_attn.v_proj.weight"].T).view(tokens, KV_HEADS, HEAD_DIM)
+        if index != 2:
+            q = rms_norm(q, weights[prefix + "self_attn.q_norm.weight"], EPS)
+            k = rms_norm(k, weights[prefix + "self_attn.k_norm.weight"], EPS)
+        cos, sin = rope_angles(positions, ROTARY, THETA) if index == 1 else toy_angles(positions)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        attended = causal_attention(q, k, v, HEAD_DIM**-0.5, WINDOW if index == 1 else 0)
+        h = h + attended.reshape(tokens, HEADS * HEAD_DIM) @ weights[prefix + "self_attn.o_proj.weight"].T
         x = rms_norm(h, weights[prefix + "post_attention_layernorm.weight"], EPS)
-        h = h + (routed(x, prefix + "mlp.") if feed_forward else swiglu(x, weights, prefix))
-    return rms_norm(h, weights["model.norm.weight"], EPS) @ weights["lm_head.weight"].T
+        if not experts:
+            h = h + swiglu(x, weights, prefix)
+            continue
+        logits = x @ weights[prefix + "mlp.router.weight"].T
+        top = logits.topk(2, dim=-1).values
+        smallest = min(smallest, float((top[:, 0] - top[:, 1]).min()))
+        share, best = torch.softmax(logits, dim=-1), logits.argmax(dim=-1)
+        out = torch.zeros_like(h)
+        for token in range(tokens):
+            expert = int(best[token])
+            inner = torch.relu(x[token] @ weights[prefix + f"mlp.experts.{expert}.up.weight"].T)
+            out[token] = share[token, expert] * (inner @ weights[prefix + f"mlp.experts.{expert}.down.weight"].T)
+        h = h + out
+    h = rms_norm(h, weights["model.norm.weight"], EPS)
+    return h @ weights["model.embed_tokens.weight"].T, smallest
 
 
-def test_a_routed_feed_forward_and_a_position_encoding_of_the_tests_own(tmp_path):
-    from plain_qwen3 import read_safetensors
+def sequences_with_clear_routing(weights, lengths, seed):
+    """Token sequences whose router decisions are not near a tie: a rounding error must not be able to send a
+    token to another expert, or the comparison would test the luck of the draw."""
+    generator = torch.Generator().manual_seed(seed)
+    chosen = {}
+    for name, length in lengths.items():
+        for _ in range(2000):
+            ids = torch.randint(0, VOCAB, (length,), generator=generator).tolist()
+            logits, margin = plain_logits(weights, ids)
+            if margin > SAFE_MARGIN:
+                chosen[name] = (ids, logits)
+                break
+        else:
+            raise AssertionError(f"no sequence of {length} tokens with router margins above {SAFE_MARGIN}")
+    return chosen
 
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routing_feed_forward_position_encoding_and_embedding(tmp_path, dtype):
     from rapid_llm_b200.config import EngineConfig
     from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
     from rapid_llm_b200.weights import write_random_model
 
     config_class = register_toys()
-    folder = write_random_model(tmp_path / "toy_parts", config_class(), seed=5)
-    weights = read_safetensors(folder / "model.safetensors")
-    assert "model.layers.0.mlp.experts.2.down.weight" in weights and "model.layers.1.mlp.gate_proj.weight" in weights
-    engine = EngineConfig(dtype=torch.float32, max_seq_len=POSITIONS, page_size=8, num_pages=30, max_num_seqs=3,
-                          max_num_batched_tokens=96, use_cuda_graph=False)
+    torch_dtype = getattr(torch, dtype)
+    folder = write_random_model(tmp_path / "toy_parts", config_class(VOCAB), seed=21, dtype=torch_dtype, std=0.12, norm_std=0.2)
+    _, weights = load_model_dir(folder)
+    assert "model.layers.0.mlp.router.weight" in weights and "model.layers.1.mlp.gate_proj.weight" in weights
+    assert "model.layers.2.self_attn.q_norm.weight" not in weights and "model.embed_tokens.places" in weights
+
+    engine = EngineConfig(dtype=torch_dtype, max_seq_len=POSITIONS, page_size=8, num_pages=40, max_num_seqs=3,
+                          max_num_batched_tokens=96, use_cuda_graph=True)
     runner = ModelRunner.from_folder(folder, engine)
+    kinds = [(type(layer.feed_forward).__name__, layer.mixer.window) for layer in runner.model.layers]
+    assert kinds == [("ToyOneOfExperts", 0), ("SwiGLU", WINDOW), ("ToyOneOfExperts", 0)]
+    assert len(runner.cache.groups) == 2          # all keys for two layers, a window of them for one
 
-    generator = torch.Generator().manual_seed(2)
-    tokens = {name: torch.randint(0, VOCAB, (count,), generator=generator).tolist() for name, count in (("a", 70), ("b", 37))}
-    plain = {name: plain_logits(weights, ids) for name, ids in tokens.items()}
-    assert plain["a"].abs().max() > 0
+    tail = 9
+    plain = sequences_with_clear_routing(weights, {"a": 33, "b": 20, "c": 27}, seed=5)
 
-    for name, ids in tokens.items():            # whole
+    # each request alone and whole
+    for name, (ids, want) in plain.items():
         runner.admit(name)
         got = runner.step([StepEntry(name, ids, list(range(len(ids))))]).float().cpu()
-        torch.testing.assert_close(got, plain[name], **for_dtype("float32"))
         runner.release(name)
+        torch.testing.assert_close(got, want, **at_scale(dtype, want))
+        assert float(want.abs().max()) > 0.05
 
-    # portions of one beside single tokens of the other, in slots and pages that were used before
-    for name in tokens:
+    # in portions side by side, then the last tokens one by one from captured graphs
+    cuts = {"a": [5, 2, 17], "b": [9, 2], "c": [2, 13, 3]}
+    fed = {name: 0 for name in plain}
+    pieces = {name: [] for name in plain}
+    for name in plain:
         runner.admit(name)
-    rows = {"a": [], "b": []}
-    fed = {"a": 0, "b": 0}
-    plan = [{"a": 9, "b": 30}, {"a": 2, "b": 1}, {"a": 33, "b": 1}, {"a": 1, "b": 1}, {"a": 25, "b": 4}]
-    for sizes in plan:
+    for step in range(3):
         entries = []
-        for name, size in sizes.items():
-            entries.append(StepEntry(name, tokens[name][fed[name] : fed[name] + size], list(range(size))))
-            fed[name] += size
+        for name, (ids, _) in plain.items():
+            if step < len(cuts[name]):
+                size = cuts[name][step]
+                entries.append(StepEntry(name, ids[fed[name] : fed[name] + size], list(range(size))))
+                fed[name] += size
         logits = runner.step(entries).float().cpu()
         at = 0
         for entry in entries:
-            rows[entry.request_id].append(logits[at : at + len(entry.tokens)].clone())
+            pieces[entry.request_id].append(logits[at : at + len(entry.tokens)].clone())
             at += len(entry.tokens)
+    while any(fed[name] < len(ids) for name, (ids, _) in plain.items()):
+        live = [name for name, (ids, _) in plain.items() if fed[name] < len(ids)]
+        entries = [StepEntry(name, [plain[name][0][fed[name]]], [0]) for name in live]
+        logits = runner.step_decode(entries).float().cpu()
+        for row, name in enumerate(live):
+            pieces[name].append(logits[row : row + 1].clone())
+            fed[name] += 1
     runner.check_fault()
-    for name in tokens:
-        assert fed[name] == len(tokens[name])
-        torch.testing.assert_close(torch.cat(rows[name]), plain[name], **for_dtype("float32"))
+    assert runner._graphs, "the decode steps were not captured"
+    for name, (ids, want) in plain.items():
+        torch.testing.assert_close(torch.cat(pieces[name]), want, **at_scale(dtype, want))
+        assert sum(cuts[name]) + tail <= len(ids)
