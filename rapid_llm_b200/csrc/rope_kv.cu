@@ -222,12 +222,16 @@ __global__ void qk_norm_rope_write_kernel(const RopeArgs a, const int heads_per_
   }
 }
 
-// Heads of 128 in bfloat16 at many tokens, the whole head rotated, no bias: half a warp per
-// head (a lane holds 8 consecutive elements, its rotation partner sits 8 lanes further), so every
-// warp instruction works on two heads, and the loads of a warp's eight heads fly together.
-__global__ void qk_norm_rope_write_pairs_kernel(const RopeArgs a) {
+// Heads of 128 in bfloat16 at many tokens, the whole head rotated, no bias: half a warp per head, so
+// every warp instruction works on two heads, and the loads of a warp's eight heads fly together.  A lane
+// holds four consecutive elements of the head's first half and their rotation partners in the second, so
+// the rotation needs no exchange between lanes and four angles a lane.  The kernel is bound by the bytes
+// it keeps in flight and by instruction issue, not by arithmetic: it stays within 64 registers (eight CTAs,
+// 32 warps a multiprocessor), asks for its heads before its angles (both wait on the position alone) and
+// reads the norm weights where it uses them (they stay in L1).
+__global__ void __launch_bounds__(kRopeWarps * 32, 8) qk_norm_rope_write_pairs_kernel(const RopeArgs a) {
   using T = __nv_bfloat16;
-  constexpr int kHeadsPerWarp = 8, kD = 128;
+  constexpr int kHeadsPerWarp = 8, kD = 128, kHalf = kD / 2;
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_per_token = a.kv_dest ? a.hq + 2 * a.hkv : a.hq;
@@ -241,83 +245,100 @@ __global__ void qk_norm_rope_write_pairs_kernel(const RopeArgs a) {
   const int head_begin = static_cast<int>(index - static_cast<long long>(t) * warps_per_token) * kHeadsPerWarp;
   const int head_end = min(heads_per_token, head_begin + kHeadsPerWarp);
   int pos = a.positions[t];
+  const int dest = a.kv_dest ? a.kv_dest[t] : 0;
+  const int side = lane >> 4, at = (lane & 15) * 4;          // which head of the pair; first element of each half
+  pdl_wait();
+  const T* row = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width;
+  uint2 low[kHeadsPerWarp / 2], high[kHeadsPerWarp / 2];
+#pragma unroll
+  for (int pair = 0; pair < kHeadsPerWarp / 2; ++pair) {
+    const int head = head_begin + 2 * pair + side;
+    low[pair] = high[pair] = make_uint2(0, 0);
+    if (head < head_end) {
+      low[pair] = *reinterpret_cast<const uint2*>(row + static_cast<size_t>(head) * kD + at);
+      high[pair] = *reinterpret_cast<const uint2*>(row + static_cast<size_t>(head) * kD + kHalf + at);
+    }
+  }
   if (pos < 0 || pos >= a.max_pos) {
     if (lane == 0 && head_begin < a.hq + a.hkv) atomicOr(a.fault, kFaultPosition);
     pos = 0;
   }
-  int page = 0, offset = 0;
-  bool bad_page = false;
-  if (a.kv_dest) {
-    const int dest = a.kv_dest[t];
-    page = dest / a.page_size;
-    offset = dest - page * a.page_size;
-    bad_page = dest < 0 || page >= a.num_pages;
+  float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (head_begin < a.hq + a.hkv) {                             // a warp of values alone needs no angles
+    c = __ldg(reinterpret_cast<const float4*>(a.cos_table + static_cast<size_t>(pos) * kHalf + at));
+    s = __ldg(reinterpret_cast<const float4*>(a.sin_table + static_cast<size_t>(pos) * kHalf + at));
   }
-  const int side = lane >> 4, at = (lane & 15) * 8;          // which head of the pair; first element
-  const int angle = at & 63;
-  float c[8], s[8], qw[8], kw[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    c[i] = a.cos_table[static_cast<size_t>(pos) * 64 + angle + i];
-    s[i] = a.sin_table[static_cast<size_t>(pos) * 64 + angle + i];
-    qw[i] = a.q_weight ? a.q_weight[at + i] : 1.0f;
-    kw[i] = a.k_weight ? a.k_weight[at + i] : 1.0f;
-  }
-  pdl_wait();
-  const T* row = static_cast<const T*>(a.qkv) + static_cast<size_t>(t) * a.row_width;
-  uint4 raw[kHeadsPerWarp / 2];
-#pragma unroll
-  for (int pair = 0; pair < kHeadsPerWarp / 2; ++pair) {
-    const int head = head_begin + 2 * pair + side;
-    raw[pair] = make_uint4(0, 0, 0, 0);
-    if (head < head_end) raw[pair] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(head) * kD + at);
-  }
+  const int page = dest / a.page_size, offset = dest - page * a.page_size;
+  const bool bad_page = a.kv_dest != nullptr && (dest < 0 || page >= a.num_pages);
 #pragma unroll
   for (int pair = 0; pair < kHeadsPerWarp / 2; ++pair) {
     const int head = head_begin + 2 * pair + side;
     const int kind = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // q, k, v
-    const __nv_bfloat162* packed = reinterpret_cast<const __nv_bfloat162*>(&raw[pair]);
-    float v[8];
+    T* dst = nullptr;
+    if (head < head_end) {
+      if (kind == 0) {
+        dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * kD + at;
+      } else if (!bad_page) {
+        const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
+        dst = static_cast<T*>(a.cache) +
+              ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * kD + at;
+      } else if ((lane & 15) == 0) {
+        atomicOr(a.fault, kFaultPageId);
+      }
+    }
+    // the pair's two heads may be of different kinds; a warp decides together only what all its lanes share
+    if (!__any_sync(0xffffffffu, kind != 2)) {                 // values: copied as they are
+      if (dst != nullptr) {
+        *reinterpret_cast<uint2*>(dst) = low[pair];
+        *reinterpret_cast<uint2*>(dst + kHalf) = high[pair];
+      }
+      continue;
+    }
+    float x1[4], x2[4];
+    {
+      const __nv_bfloat162* lo = reinterpret_cast<const __nv_bfloat162*>(&low[pair]);
+      const __nv_bfloat162* hi = reinterpret_cast<const __nv_bfloat162*>(&high[pair]);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 two = __bfloat1622float2(packed[i]);
-      v[2 * i] = two.x;
-      v[2 * i + 1] = two.y;
+      for (int i = 0; i < 2; ++i) {
+        const float2 p = __bfloat1622float2(lo[i]), q = __bfloat1622float2(hi[i]);
+        x1[2 * i] = p.x; x1[2 * i + 1] = p.y;
+        x2[2 * i] = q.x; x2[2 * i + 1] = q.y;
+      }
     }
     float sum_sq = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sum_sq += v[i] * v[i];
+    for (int i = 0; i < 4; ++i) sum_sq += x1[i] * x1[i] + x2[i] * x2[i];
 #pragma unroll
     for (int step = 8; step > 0; step >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, step);   // within 16 lanes
-    const bool normed = kind == 0 ? a.q_weight != nullptr : (kind == 1 && a.k_weight != nullptr);
-    const float inv_rms = normed ? rsqrtf(sum_sq / static_cast<float>(kD) + a.eps) : 1.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float scaled = v[i] * inv_rms * (kind == 0 ? qw[i] : kw[i]);
-      const float mine = normed ? scaled : v[i];
-      const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-      // first half of the head: x1 * c - x2 * s; second half: x2 * c + x1 * s; values pass through
-      const float turned = (lane & 8) ? mine * c[i] + other * s[i] : mine * c[i] - other * s[i];
-      v[i] = kind == 2 ? v[i] : turned;
+    const float* weight = kind == 0 ? a.q_weight : (kind == 1 ? a.k_weight : nullptr);
+    if (weight != nullptr) {
+      const float inv_rms = rsqrtf(sum_sq / static_cast<float>(kD) + a.eps);
+      const float4 w1 = __ldg(reinterpret_cast<const float4*>(weight + at));
+      const float4 w2 = __ldg(reinterpret_cast<const float4*>(weight + kHalf + at));
+      x1[0] = x1[0] * inv_rms * w1.x; x1[1] = x1[1] * inv_rms * w1.y; x1[2] = x1[2] * inv_rms * w1.z; x1[3] = x1[3] * inv_rms * w1.w;
+      x2[0] = x2[0] * inv_rms * w2.x; x2[1] = x2[1] * inv_rms * w2.y; x2[2] = x2[2] * inv_rms * w2.z; x2[3] = x2[3] * inv_rms * w2.w;
     }
-    if (head >= head_end) continue;
-    T* dst;
-    if (kind == 0) {
-      dst = static_cast<T*>(a.q_out) + (static_cast<size_t>(t) * a.hq + head) * kD;
-    } else {
-      if (bad_page) {
-        if ((lane & 15) == 0) atomicOr(a.fault, kFaultPageId);
-        continue;
+    if (dst == nullptr) continue;
+    uint2 out1 = low[pair], out2 = high[pair];
+    if (kind != 2) {
+      // first half of the head: x1 * c - x2 * s; second half: x2 * c + x1 * s
+      const float cs[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+      float o1[4], o2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o1[i] = x1[i] * cs[i] - x2[i] * sn[i];
+        o2[i] = x2[i] * cs[i] + x1[i] * sn[i];
       }
-      const int kv_head = kind == 1 ? head - a.hq : head - a.hq - a.hkv;
-      dst = static_cast<T*>(a.cache) +
-            ((((static_cast<size_t>(page) * 2 + (kind - 1)) * a.hkv + kv_head) * a.page_size) + offset) * kD;
-    }
-    uint4 out;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+      __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&out1);
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&out2);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(dst + at) = out;
+      for (int i = 0; i < 2; ++i) {
+        h1[i] = __floats2bfloat162_rn(o1[2 * i], o1[2 * i + 1]);
+        h2[i] = __floats2bfloat162_rn(o2[2 * i], o2[2 * i + 1]);
+      }
+    }
+    *reinterpret_cast<uint2*>(dst) = out1;
+    *reinterpret_cast<uint2*>(dst + kHalf) = out2;
   }
 }
 
@@ -351,7 +372,9 @@ extern "C" int rl_qk_norm_rope_write(int dtype, const void* qkv, int row_width, 
     heads_per_warp = 8;
   const long long warps = static_cast<long long>(tokens) * ((heads_per_token + heads_per_warp - 1) / heads_per_warp);
   const dim3 grid(static_cast<unsigned>((warps + rl::kRopeWarps - 1) / rl::kRopeWarps)), block(rl::kRopeWarps * 32);
-  if (heads_per_warp == 8 && d == 128 && vec == 4 && bias == nullptr && dtype == rl::kBF16)
+  const bool tables_aligned = ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+                                reinterpret_cast<uintptr_t>(q_weight) | reinterpret_cast<uintptr_t>(k_weight)) & 15) == 0;
+  if (heads_per_warp == 8 && d == 128 && vec == 4 && bias == nullptr && dtype == rl::kBF16 && tables_aligned)
     return rl::launch_kernel(rl::qk_norm_rope_write_pairs_kernel, grid, block, 0, stream, pdl != 0, a);
   RL_DISPATCH_DTYPE(dtype, {
     if (vec == 8) return rl::launch_kernel(rl::qk_norm_rope_write_kernel<scalar_t, 8>, grid, block, 0, stream, pdl != 0, a, heads_per_warp);

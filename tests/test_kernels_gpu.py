@@ -436,9 +436,11 @@ def test_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_qk_norm_rope_write_with_many_tokens(dtype):
-    """Enough tokens that a warp takes a run of heads of its token (10 heads: runs of 8 and 2)."""
-    check_qk_norm_rope_write(dtype, hq=6, hkv=2, d=128, rotary=128, page=16, tokens=7600, pages=500)
+@pytest.mark.parametrize("hq,hkv,tokens", [(6, 2, 7600), (5, 1, 11000), (32, 8, 1600)])
+def test_qk_norm_rope_write_with_many_tokens(dtype, hq, hkv, tokens):
+    """Enough tokens that a warp takes a run of heads of its token (10 heads: runs of 8 and 2; 7 heads: a query
+    and a key head, a value head and none share a warp instruction; the 48 heads of the 8B shape)."""
+    check_qk_norm_rope_write(dtype, hq=hq, hkv=hkv, d=128, rotary=128, page=16, tokens=tokens, pages=tokens // 16 + 30)
 
 
 def check_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page, tokens, pages):
