@@ -299,14 +299,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
     const int lo_pos = args.window > 0 ? max(0, pos - args.window + 1) : 0;
     pdl_wait();                                        // queries come from the kernel before
     {
-      // this thread's row of Q: 256 bytes, as the K-major operand [row][64] x 2 halves, swizzled
-      const bf16* src = args.q + (static_cast<size_t>(tok_begin + token) * args.hq + kv_head * group + (p - token * group)) * kPfD;
+      // The warp's 32 rows of Q, 256 bytes each, into the K-major operand [row][64] x 2 halves, swizzled: an
+      // instruction fetches two whole rows (a lane 16 bytes, past L1, which the lists and page ids keep), and all
+      // of a lane's fetches fly together.
+      const int shift = (group & (group - 1)) == 0 ? 31 - __clz(group) : -1;
+      uint4 fetched[16];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint4 value = make_uint4(0, 0, 0, 0);
-        if (valid) value = *reinterpret_cast<const uint4*>(src + c * 8);
-        const uint32_t dst = q_tile(tile) + (c >> 3) * kPfHalfBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(value.x), "r"(value.y), "r"(value.z), "r"(value.w) : "memory");
+      for (int i = 0; i < 16; ++i) {
+        const int rr = quarter * 32 + 2 * i + (lane >> 4);
+        const int pp = row0 + tile * kPfTileRows + rr;
+        const int tt = shift >= 0 ? pp >> shift : pp / group;
+        fetched[i] = make_uint4(0, 0, 0, 0);
+        if (pp < row0 + n_rows && !bad)
+          fetched[i] = __ldcg(reinterpret_cast<const uint4*>(
+              args.q + (static_cast<size_t>(tok_begin + tt) * args.hq + kv_head * group + (pp - tt * group)) * kPfD + (lane & 15) * 8));
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int rr = quarter * 32 + 2 * i + (lane >> 4), c = lane & 15;
+        const uint32_t dst = q_tile(tile) + (c >> 3) * kPfHalfBytes + rr * 128 + (((c & 7) ^ (rr & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(fetched[i].x), "r"(fetched[i].y), "r"(fetched[i].z), "r"(fetched[i].w) : "memory");
       }
       fence_async_smem();
       __syncwarp();
