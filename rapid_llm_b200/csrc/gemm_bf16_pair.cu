@@ -45,8 +45,9 @@ constexpr int kPairMaxTiles = 4096;       // tiles of one product (two counters 
 template <int TN>
 struct PairShape {
   static constexpr int kStageBytes = kPairRows * kPairTileK * 2 + (TN / 2) * kPairTileK * 2;
-  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;
+  static constexpr int kStagingBytes = TN * kPairRows * 2;    // a CTA's tile of the result, [token][weight row], on its way out
+  static constexpr int kStages = (192 * 1024 - kStagingBytes) / kStageBytes > 8 ? 8 : (192 * 1024 - kStagingBytes) / kStageBytes;
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + kStagingBytes + 1024;
   static constexpr int kTmemColumns = 2 * TN;        // two accumulators
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
                                      (static_cast<uint32_t>((2 * kPairRows) >> 4) << 24);
@@ -60,6 +61,7 @@ struct PairArgs {
   int T, N, K;
   int n_tiles, t_tiles, k_blocks;
   int pdl;
+  int out_by_tma;      // tiles of the result leave through map_out (N a multiple of 8, out 16-byte aligned)
   const float* bias;   // [N] or null
   float* scratch;      // [pairs][2][TN][128]: the partial tile of a pair's first segment, per CTA
   unsigned* counters;  // [tiles][2]: partial tiles stored so far, per CTA rank; zero between launches
@@ -162,7 +164,7 @@ __device__ __forceinline__ unsigned pair_load_acquire(const unsigned* p) {
 template <int TN>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      const PairArgs args) {
+                      const __grid_constant__ CUtensorMap map_out, const PairArgs args) {
   using Shape = PairShape<TN>;
   constexpr int kPairStages = Shape::kStages, kPairStageBytes = Shape::kStageBytes, kPairTokens = TN;
   constexpr int kPairTmemColumns = Shape::kTmemColumns;
@@ -180,6 +182,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const uint32_t smem_base = (smem_addr(pair_smem_raw) + 1023u) & ~1023u;
   auto stage_a = [&](int s) { return smem_base + s * kPairStageBytes; };
   auto stage_b = [&](int s) { return smem_base + s * kPairStageBytes + kPairRows * kPairTileK * 2; };
+  const uint32_t staging = smem_base + kPairStages * kPairStageBytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -197,6 +200,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   if (threadIdx.x == 64) {
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_x);
+    if (args.out_by_tma) prefetch_tensormap(&map_out);
   }
   if (warp == 1) {                                // the same warp in both CTAs, together
     tmem_alloc_pair(smem_addr(&tmem_base_slot), kPairTmemColumns);
@@ -281,6 +285,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     int buf = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
+    bool store_in_flight = false;        // a tile of the result is leaving the staging buffer (thread 64 issued it)
     if (args.pdl) pdl_wait();
     PairRun run(args, pair, pairs);
     int tile, kb0, len;
@@ -297,12 +302,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         // not the tile's first k-blocks: the partial tile goes to this pair's place in scratch, [token][row]
         float* mine = args.scratch + (static_cast<size_t>(pair) * 2 + rank) * Shape::kPartialFloats + row_local;
 #pragma unroll 1
-        for (int c = 0; c < kPairTokens; c += 16) {
+        for (int c = 0; c < kPairTokens; c += 64) {
           if (t0 + c >= args.T) break;
-          float v[16];
-          tmem_load16(acc + c, v);
+          uint32_t raw[2][32];
+          tmem_load32(acc + c, raw[0]);
+          tmem_load32(acc + c + 32, raw[1]);
+          tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) __stcg(mine + static_cast<size_t>(c + j) * kPairRows, v[j]);
+          for (int j = 0; j < 64; ++j) __stcg(mine + static_cast<size_t>(c + j) * kPairRows, __uint_as_float(raw[j >> 5][j & 31]));
         }
         __threadfence();
         named_barrier(1, 128);
@@ -332,6 +339,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
           if (!ok) break;
         }
         const float bias = args.bias != nullptr && n < args.N ? args.bias[n] : 0.0f;
+        if (store_in_flight) {
+          // the tile stored before has left the staging buffer (its products took far longer than that)
+          if (threadIdx.x == 64) tma_store_wait_read();
+          named_barrier(1, 128);
+          store_in_flight = false;
+        }
         const float* theirs = args.scratch + (static_cast<size_t>(pair + 1) * 2 + rank) * Shape::kPartialFloats + row_local;
 #pragma unroll 1
         for (int c0 = 0; c0 < kPairTokens; c0 += 64) {
@@ -348,20 +361,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
             for (int j = 0; j < 64; ++j) sum[j] += got[j];
           }
+          // 64 columns of the accumulator per wait: a load of tensor memory takes a fraction of a microsecond
+          // to come back, and sixteen of them in a row were most of a tile's way out
+          uint32_t raw[2][32];
+          tmem_load32(acc + c0, raw[0]);
+          tmem_load32(acc + c0 + 32, raw[1]);
+          tmem_wait_ld();
+          if (args.out_by_tma) {
+            // [token][weight row]: a warp writes 32 neighbouring values of one token per instruction
 #pragma unroll
-          for (int c = 0; c < 64; c += 16) {
-            if (t0 + c0 + c < args.T) {
-              float v[16];
-              tmem_load16(acc + c0 + c, v);
-              if (n < args.N) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  if (t0 + c0 + c + j < args.T)
-                    args.out[static_cast<size_t>(t0 + c0 + c + j) * args.N + n] = __float2bfloat16_rn(v[j] + sum[c + j] + bias);
-              }
+            for (int j = 0; j < 64; ++j) {
+              const __nv_bfloat16 value = __float2bfloat16_rn(__uint_as_float(raw[j >> 5][j & 31]) + sum[j] + bias);
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(staging + ((c0 + j) * kPairRows + row_local) * 2),
+                           "h"(*reinterpret_cast<const unsigned short*>(&value))
+                           : "memory");
             }
+          } else if (n < args.N) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              if (t0 + c0 + j < args.T)
+                args.out[static_cast<size_t>(t0 + c0 + j) * args.N + n] =
+                    __float2bfloat16_rn(__uint_as_float(raw[j >> 5][j & 31]) + sum[j] + bias);
           }
         }
+      }
+      if (kb0 == 0 && args.out_by_tma) {
+        // the tile is whole in the staging buffer: one copy takes it out (what lies past the matrix's edge is not written)
+        fence_async_smem();
+        named_barrier(1, 128);
+        if (threadIdx.x == 64) {
+          tma_store_2d(&map_out, staging, n_tile * 2 * kPairRows + static_cast<int>(rank) * kPairRows, t0);
+          tma_store_commit();
+        }
+        store_in_flight = true;
       }
       // the accumulator may be overwritten: every epilogue warp of both CTAs tells the first CTA
       tc_fence_before();
@@ -370,6 +402,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       acc_phase[buf] ^= 1u;
       buf ^= 1;
     }
+    if (threadIdx.x == 64 && store_in_flight) tma_store_wait_read();   // shared memory is given up below
   }
 
   tc_fence_before();
@@ -391,6 +424,13 @@ static int launch_pair(const void* x, const void* w, PairArgs args, int pairs, c
   if (status != 0) return status;
   status = make_map(&map_x, x, args.T, args.K, TN / 2);
   if (status != 0) return status;
+  CUtensorMap map_out = map_x;
+  args.out_by_tma = 0;
+  if (args.N % 8 == 0 && (reinterpret_cast<uintptr_t>(args.out) & 15) == 0) {
+    status = make_map_plain(&map_out, args.out, args.T, args.N, TN, kPairRows);
+    if (status != 0) return status;
+    args.out_by_tma = 1;
+  }
   auto kernel = gemm_bf16_pair_kernel<TN>;
   bool& configured = g_pair_configured[TN == 256 ? 1 : 0];
   if (!configured) {
@@ -416,7 +456,7 @@ static int launch_pair(const void* x, const void* w, PairArgs args, int pairs, c
   }
   config.attrs = attributes;
   config.numAttrs = count;
-  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, args));
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, map_out, args));
 }
 
 static int pair_count() {
