@@ -61,6 +61,8 @@ constexpr int tc_smem_bytes(int stages) { return stages * kTcStageBytes + (1 + 2
 constexpr uint32_t kTcIdescScore = (1u << 4) | (1u << 7) | (1u << 10) | ((kTcRows >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kTcIdescValue = kTcIdescScore | (1u << 15);     // A (the values) is MN-major
 
+constexpr int kTcMaxClusterSplits = 16;     // key ranges of a tile merged inside one cluster (more than 8: a cluster size that must be asked for)
+
 struct DecodeTcArgs {
   const bf16* q;
   bf16* out;
@@ -492,27 +494,27 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
     cluster_sync();
     if (softmax_warp && team == 0) {
       // where the other ranks keep their row statistics and this thread's column of their results
-      uint32_t peer_lse[8], peer_out[8];
+      uint32_t peer_lse[kTcMaxClusterSplits], peer_out[kTcMaxClusterSplits];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < kTcMaxClusterSplits; ++r) {
         peer_lse[r] = r < args.splits ? peer_smem(smem_addr(&split_lse[0]), r) : 0u;
         peer_out[r] = r < args.splits ? peer_smem(smem_addr(&split_out[t]), r) : 0u;
       }
       for (int n = split; n < n_rows; n += args.splits) {
         // all remote loads of the row first (each takes hundreds of cycles), the arithmetic after
-        float lse_of[8], out_of[8];
+        float lse_of[kTcMaxClusterSplits], out_of[kTcMaxClusterSplits];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < kTcMaxClusterSplits; ++r) {
           lse_of[r] = r < args.splits ? load_peer_f32(peer_lse[r] + n * 4) : -INFINITY;
           out_of[r] = r < args.splits ? load_peer_f32(peer_out[r] + n * 128 * 4) : 0.0f;
         }
         float m = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) m = fmaxf(m, lse_of[r]);
+        for (int r = 0; r < kTcMaxClusterSplits; ++r) m = fmaxf(m, lse_of[r]);
         const float safe = m == -INFINITY ? 0.0f : m;
         float total = 0.0f, value = 0.0f;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < kTcMaxClusterSplits; ++r) {
           if (r < args.splits) {
             const float w = fast_exp2(lse_of[r] - safe);
             total += w;

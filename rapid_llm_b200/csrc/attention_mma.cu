@@ -571,6 +571,9 @@ static int launch_decode_tc_stages(const CUtensorMap& map, const DecodeTcArgs& t
   if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
+    // clusters of more than 8 CTAs (up to 16 key ranges of a tile) have to be asked for
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return static_cast<int>(e);
     *configured = true;
   }
   // x: the key ranges of one tile (a cluster when they merge among themselves), y: the kv head,
@@ -660,6 +663,32 @@ int rl_attention_decode_rows() { return 16; }
 // chunk_items / decode_items: [n, 4] int32 (entry, first packed row, split, 0).  With
 // splits > 1, part_out [tokens, hq, splits, D] and part_lse [tokens, hq, splits] are scratch
 // and every (row, split) pair must be covered by exactly one item.
+// How many clusters of `cluster_size` CTAs of the tcgen05 decode kernel (deep rings: one CTA per multiprocessor)
+// the GPU runs at one time, or a negative CUDA error code.  A cluster lives inside one GPC, so the answer is not
+// the number of multiprocessors over the size; the host's planner asks once per size.
+int rl_attention_decode_max_clusters(int cluster_size) {
+  if (attn::kD != attn::kTcD || cluster_size < 1 || cluster_size > attn::kTcMaxClusterSplits) return -static_cast<int>(cudaErrorInvalidValue);
+  auto kernel = attn::attention_decode_tc_kernel<4, attn::kTcMaxStages>;
+  constexpr int kBytes = attn::tc_smem_bytes(attn::kTcMaxStages);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(cluster_size, 1, 64);
+  config.blockDim = dim3(attn::kTcThreads);
+  config.dynamicSmemBytes = kBytes;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = cluster_size;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+  return e == cudaSuccess ? clusters : -static_cast<int>(e);
+}
+
 int rl_attention_mma(const void* q, const void* cache, void* out, float* part_out, float* part_lse,
                      const int* chunk_items, int n_chunk_items, const int* decode_items,
                      int n_decode_items, const int* cu_seqlens, const int* entry_start,
@@ -705,7 +734,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   if (n_decode_items > 0) {
     args.items = decode_items;
     if (decode_kernel != 1 && attn::decode_tc_supported(page_size)) {
-      merged_in_cluster = n_chunk_items == 0 && splits > 1 && splits <= 8 && n_decode_items % splits == 0;
+      merged_in_cluster = n_chunk_items == 0 && splits > 1 && splits <= attn::kTcMaxClusterSplits && n_decode_items % splits == 0;
       status = attn::launch_decode_tc(args, n_decode_items, decode_rows, merged_in_cluster, pdl != 0, stream,
                                       decode_kernel == 2 || decode_kernel == 3 ? decode_kernel : 0);
     } else

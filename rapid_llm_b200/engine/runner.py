@@ -125,7 +125,7 @@ class ModelRunner:
         self.result = torch.zeros(config.max_num_seqs + 2, dtype=torch.int32, device=self.device)
         self.fault = self.result[:1]
         self.steps_run = 0
-        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graphs: dict[tuple, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}      # by (bucket, launch constants)
         self._graph_pool = None
 
     # -- construction ---------------------------------------------------------------- #
@@ -254,6 +254,7 @@ class ModelRunner:
             starts=np.asarray(starts + [0] * pad, dtype=np.int32),
             decode_only=max(lengths) == 1,
             page_size=cache.page_size,
+            padding=pad,
         )
         planned: dict[tuple, dict[str, Any]] = {}
         for planner in self._planners:
@@ -396,7 +397,8 @@ class ModelRunner:
 
         The batch is padded to a bucket size with rows that point at the null page; the
         metadata lives in a fixed device buffer that is refreshed before each replay.  The
-        first step of a bucket runs eagerly and is then captured.  The reference captures
+        first step of a bucket (and of a set of the planners' launch constants, which change at a few
+        context lengths) runs eagerly and is then captured.  The reference captures
         decode graphs per batch size and length bucket (``rapid_llm/executor/cuda_graph.py:45-46,317``).
         """
         if any(len(entry.tokens) != 1 or list(entry.want) != [0] for entry in entries):
@@ -404,7 +406,14 @@ class ModelRunner:
         count = len(entries)
         bucket = self.decode_bucket(count)
         batch = self.prepare(entries, pad_to=bucket)
-        captured = self._graphs.get(bucket)
+        # what a captured step has baked in beside its addresses: the bucket and the planners' launch constants
+        # (plain values and the sizes of their lists); a step that differs in one of them is another graph
+        constants = tuple(
+            (str(key), name, tuple(value.shape) if isinstance(value, torch.Tensor) else value)
+            for key, plan in sorted(batch.extras.items(), key=lambda item: str(item[0])) for name, value in sorted(plan.items())
+        )
+        graph_key = (bucket, constants)
+        captured = self._graphs.get(graph_key)
         if captured is None:
             caches = self.layer_caches()
             logits = self._forward(batch, caches)
@@ -419,7 +428,7 @@ class ModelRunner:
                 self._graph_pool = graph.pool()
             # The eager run above is this step's result.  Capturing executes nothing, and the graph
             # is not replayed now: a mixer with state of its own must see every token once.
-            self._graphs[bucket] = (graph, static_logits, launches)
+            self._graphs[graph_key] = (graph, static_logits, launches)
         else:
             graph, logits, launches = captured
             graph.replay()

@@ -334,6 +334,7 @@ CHUNK_TILE_ROWS = 64       # packed rows (token, head of the group) of a chunk t
 CHUNK_TILE_ROWS_TC = 256   # ... of the tcgen05 kernel (head size 128, unsplit key ranges)
 DECODE_TILE_ROWS = 16      # ... of a decode tile
 TC_HEAD_DIM = 128
+DECODE_TC_KEYS = 128      # keys per block of the tcgen05 decode kernel
 
 
 def attention_tc_takes(head_dim: int, page_size: int) -> bool:
@@ -354,6 +355,8 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
             c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
+        lib.rl_attention_decode_max_clusters.argtypes = [c_int]
+        lib.rl_attention_decode_max_clusters.restype = c_int
         if lib.rl_attention_head_dim() != head_dim:
             raise KernelError(f"the attention library for head size {head_dim} was built for another size")
         if lib.rl_attention_chunk_rows() != CHUNK_TILE_ROWS or lib.rl_attention_decode_rows() != DECODE_TILE_ROWS:
@@ -362,6 +365,22 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
             raise KernelError("the attention library's tensor-core tile size differs from the host's")
         _ATTENTION_LIBS[head_dim] = lib
     return lib
+
+
+def attention_decode_clusters(head_dim: int, device: torch.device) -> dict[int, int]:
+    """``{cluster size: clusters of the tcgen05 decode kernel the GPU runs at one time}`` for the sizes it can
+    launch (a cluster lives inside one GPC, so this is not the number of multiprocessors over the size).
+    Empty where that kernel does not exist (other head sizes)."""
+    if head_dim != TC_HEAD_DIM:
+        return {}
+    lib = attention_lib(head_dim)
+    table = {}
+    with torch.cuda.device(device):
+        for size in range(1, 17):
+            count = int(lib.rl_attention_decode_max_clusters(size))
+            if count > 0:
+                table[size] = count
+    return table
 
 
 def attention_mma(

@@ -27,10 +27,29 @@ from .base import (
 
 DEFAULT_SMS = 148         # a B200's; planning on the host without a device (tests) assumes it
 MAX_SPLITS = 16
-CLUSTER_SPLITS = 8        # the portable size of a thread-block cluster
+CLUSTER_SPLITS = 16       # the largest thread-block cluster (beyond 8 the kernel asks for it)
 TC_CHUNK_MIN_CTAS = 32    # measured: from here on the unsplit tcgen05 chunk kernel beats the split mma.sync tiles
 TC_CHUNK_SHORT_CONTEXT = 1024   # ... and below this context it does so with any number of CTAs
 MIN_KEYS_PER_SPLIT = 256
+PADDING_FREE_BLOCKS = 32  # blocks of 128 keys from which a decode bucket's padding rows stop counting as clusters
+
+
+# Clusters of the tcgen05 decode kernel a B200 runs at one time, by cluster size (one CTA per multiprocessor, a
+# cluster inside one GPC); what planning on the host without a device assumes.
+DEFAULT_DECODE_CLUSTERS = {1: 148, 2: 74, 3: 45, 4: 33, 5: 26, 6: 22, 7: 15, 8: 15, 9: 15, 10: 11,
+                           11: 7, 12: 7, 13: 7, 14: 7, 15: 7, 16: 7}
+
+
+def cluster_splits(tiles: int, clusters: dict[int, int]) -> int:
+    """Key ranges per tile of a decode-only step on the tcgen05 decode kernel, which merges them inside one
+    thread-block cluster: the largest cluster size of which ``tiles`` clusters still run at one time.  (Two
+    requests of 8 kv heads are 16 tiles: 16 clusters of 8 would fill 128 multiprocessors, but only 15 such
+    clusters fit the GPCs, so the sixteenth would wait for a whole round; 16 clusters of 6 run together.)"""
+    best = 1
+    for size, count in clusters.items():
+        if size > best and size <= CLUSTER_SPLITS and count >= tiles:
+            best = size
+    return best
 
 
 class AttentionItems(StepPlanner):
@@ -39,10 +58,10 @@ class AttentionItems(StepPlanner):
     Every entry's packed rows (token, head of the group) are tiled: entries of one token, or
     of at most 16 packed rows, into decode tiles of 16 rows; the others into chunk tiles.  When
     the tiles are too few to fill the GPU, each tile's key range is split into ``splits`` parts
-    (the same number for the whole step): a function of the number of entries alone in a
-    decode-only step, so that a captured decode graph replays the same item list at every
-    context length (a power of two up to 8 where the tcgen05 decode kernel merges the parts inside
-    a thread-block cluster); bounded by the longest context otherwise.  Chunk tiles have 256 rows
+    (the same number for the whole step): in a decode-only step a function of the number of entries and
+    of a coarse class of the longest context, so that a captured decode graph replays the same launches at nearly every
+    context length (where the tcgen05 decode kernel merges the parts inside a thread-block cluster: the
+    largest cluster of which that many run at one time); bounded by the longest context otherwise.  Chunk tiles have 256 rows
     for the tcgen05 kernel, which takes head size 128, the usual page sizes and unsplit key
     ranges, and 64 rows for the mma.sync kernel otherwise.  The tcgen05 kernel is several times
     faster per key, so it also runs, unsplit, where a split would have been wanted, unless its
@@ -52,12 +71,15 @@ class AttentionItems(StepPlanner):
     (``rapid_llm/kernels/ops/attention/flashdecoding.py:43-112``).
     """
 
-    def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0, sms: int = DEFAULT_SMS) -> None:
+    def __init__(self, group: int, num_kv_heads: int, head_dim: int = 0, sms: int = DEFAULT_SMS,
+                 decode_clusters: dict[int, int] | None = None) -> None:
         self.group, self.num_kv_heads, self.head_dim = int(group), int(num_kv_heads), int(head_dim)
+        self.decode_clusters = dict(decode_clusters or DEFAULT_DECODE_CLUSTERS)
         # work items the kernels want in flight: two CTAs per multiprocessor, one in a decode-only
         # step, whose kernel keeps a whole multiprocessor's shared memory busy
         self.target_ctas, self.decode_target_ctas = 2 * int(sms), int(sms)
-        self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim, int(sms))
+        self.key = ("attention_items", self.group, self.num_kv_heads, self.head_dim, int(sms),
+                    tuple(sorted(self.decode_clusters.items())))
 
     def capacity(self, max_tokens: int, max_entries: int) -> int:
         chunk_tiles = -(-max_tokens * self.group // kernels.CHUNK_TILE_ROWS) + max_entries
@@ -80,9 +102,18 @@ class AttentionItems(StepPlanner):
                 longest = int((starts + lengths).max())
                 splits = max(1, min(splits, longest // MIN_KEYS_PER_SPLIT))
             elif tensor_core:
-                # the tcgen05 decode kernel merges a tile's key ranges inside one thread-block
-                # cluster: at most 8 CTAs, and a power of two schedules best
-                splits = 1 << (min(splits, CLUSTER_SPLITS).bit_length() - 1)
+                # ... and no more key ranges than the longest context has blocks of keys, rounded down to a power
+                # of two: a step's launch constants then change at a handful of context lengths only (the runner
+                # keeps a captured graph per set of constants)
+                blocks = max(1, -(-int((starts + lengths).max()) // kernels.DECODE_TC_KEYS))
+                # On long contexts the padding rows of a decode bucket do not count: their clusters come last in the
+                # grid, see one key each, and the round they add (a few microseconds) costs less than the real rows
+                # gain from more CTAs (measured at batch 5 of a bucket of 8: 5 % slower at 1,024 tokens, 10 % faster at 32,000).
+                counted = ctas
+                if blocks >= PADDING_FREE_BLOCKS:
+                    real = len(lengths) - int(shape.padding)
+                    counted = max(1, int(tiles[:real].sum()) * self.num_kv_heads)
+                splits = min(cluster_splits(counted, self.decode_clusters), 1 << (blocks.bit_length() - 1))
             if splits == 1 or chunk_rows == kernels.CHUNK_TILE_ROWS or bool(is_decode.all()):
                 break
             # The tcgen05 chunk kernel does not split key ranges, but it is several times faster per
@@ -149,7 +180,10 @@ class GQAAttention(Mixer):
         self.shares_cache = bool(shares_cache)
         device = torch.device(device)
         sms = torch.cuda.get_device_properties(device).multi_processor_count if device.type == "cuda" else DEFAULT_SMS
-        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms)
+        clusters = None
+        if device.type == "cuda" and dtype == torch.bfloat16:
+            clusters = kernels.attention_decode_clusters(self.d, device) or None
+        self._items = AttentionItems(self.hq // self.hkv, self.hkv, self.d, sms, clusters)
         self.position = POSITION_ENCODINGS.build(position, dtype=dtype, device=device)
         self.rotary_dim = int(position.params.get("rotary_dim", self.d))
 

@@ -107,6 +107,7 @@ class StepShape:
     starts: Any           # numpy int32 [entries]
     decode_only: bool
     page_size: int = 0    # tokens per cache page (0 = not said)
+    padding: int = 0      # how many of the entries, at the end, are padding rows
 
 
 class StepPlanner:

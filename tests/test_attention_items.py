@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from rapid_llm_b200.ops import kernels
-from rapid_llm_b200.parts.attention import DEFAULT_SMS, MAX_SPLITS, AttentionItems
+from rapid_llm_b200.parts.attention import DEFAULT_DECODE_CLUSTERS, DEFAULT_SMS, MAX_SPLITS, AttentionItems
 from rapid_llm_b200.parts.base import StepShape
 
 
@@ -55,13 +55,38 @@ def test_a_decode_only_step_splits_by_the_number_of_entries_alone():
     assert full["splits"] == 1
 
 
-def test_decode_steps_of_the_cluster_kernel_split_into_a_power_of_two_up_to_eight():
-    planner = AttentionItems(4, 8, 128)
-    for entries, want in [(1, 8), (2, 8), (3, 4), (4, 4), (8, 2), (9, 2), (16, 1)]:
-        plan = planner.plan(StepShape(np.ones(entries, np.int32), np.full(entries, 500, np.int32), True, page_size=16))
+def test_decode_steps_of_the_cluster_kernel_take_the_largest_cluster_that_runs_in_one_round():
+    planner = AttentionItems(4, 8, 128)      # 8 kv heads: a request is 8 tiles
+    for entries, want in [(1, 10), (2, 6), (3, 5), (4, 4), (5, 3), (6, 2), (8, 2), (9, 2), (10, 1), (16, 1)]:
+        plan = planner.plan(StepShape(np.ones(entries, np.int32), np.full(entries, 5000, np.int32), True, page_size=16))
         assert plan["splits"] == want, entries
+        assert DEFAULT_DECODE_CLUSTERS[want] >= entries * 8          # all of the step's clusters run at one time
+    # another GPU's table: few clusters of any size above two
+    small = AttentionItems(4, 8, 128, decode_clusters={1: 60, 2: 30, 3: 4})
+    assert small.plan(StepShape(np.ones(1, np.int32), np.full(1, 5000, np.int32), True, page_size=16))["splits"] == 2
     other_page = planner.plan(StepShape(np.ones(1, np.int32), np.full(1, 500, np.int32), True, page_size=24))
     assert other_page["splits"] == MAX_SPLITS            # the mma.sync tiles merge in a kernel of their own
+
+
+def test_padding_rows_of_a_decode_bucket_do_not_count_as_clusters():
+    planner = AttentionItems(4, 8, 128)
+    lengths, starts = np.ones(8, np.int32), np.array([5000] * 5 + [0] * 3, np.int32)
+    padded = planner.plan(StepShape(lengths, starts, True, page_size=16, padding=3))
+    full = planner.plan(StepShape(lengths, np.full(8, 5000, np.int32), True, page_size=16))
+    assert (padded["splits"], full["splits"]) == (3, 2)
+    short = planner.plan(StepShape(lengths, np.array([1000] * 5 + [0] * 3, np.int32), True, page_size=16, padding=3))
+    assert short["splits"] == 2                     # on short contexts the extra round of padding clusters costs more
+    assert len(padded["decode_items"]) == 8 * 3 and list(padded["decode_items"][-9:, 0]) == [5, 5, 5, 6, 6, 6, 7, 7, 7]
+
+
+def test_decode_steps_of_the_cluster_kernel_split_no_finer_than_the_context_has_blocks():
+    planner = AttentionItems(4, 8, 128)
+    seen = []
+    for context in (1, 100, 127, 128, 300, 511, 512, 1000, 1023, 1024, 2047, 2048, 30000):
+        plan = planner.plan(StepShape(np.ones(1, np.int32), np.full(1, context, np.int32), True, page_size=16))
+        seen.append(plan["splits"])
+    assert seen == [1, 1, 1, 2, 2, 4, 4, 8, 8, 8, 10, 10, 10]    # the new token's key counts: 129 keys are two blocks
+    assert len(set(seen)) <= 5                                    # so few graphs per batch size
 
 
 def test_short_contexts_are_not_split_in_a_mixed_step():

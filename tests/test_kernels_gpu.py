@@ -649,7 +649,11 @@ def test_attention_mma(hq, hkv, d, page, window, splits):
      (12, 3, 8, 100, None, [333, 50, 128], [1, 1, 2]),          # a window; two tokens still fit a decode tile
      (40, 2, 64, 0, 2, [400, 90], [1, 1]),                      # a group of 20 rows: two decode tiles per request
      (4, 4, 128, 0, None, [513, 127], [3, 1]),                  # pages as long as a block
-     (8, 8, 256, 77, 4, [900], [5])],
+     (8, 8, 256, 77, 4, [900], [5]),
+     (8, 1, 16, 0, 10, [5000], [1]),                            # clusters of more than eight CTAs, and of odd sizes
+     (8, 2, 16, 0, 16, [3000, 40], [1, 1]),
+     (16, 4, 16, 0, 6, [2000, 700], [1, 1]),
+     (8, 2, 32, 500, 5, [1500], [1])],
 )
 def test_attention_decode_kernels(hq, hkv, page, window, splits, lengths, new_counts, decode_kernel):
     """Decode tiles at head size 128: the tcgen05 kernel (auto; with deep rings, one CTA per multiprocessor; with
