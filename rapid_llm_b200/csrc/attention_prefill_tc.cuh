@@ -54,6 +54,32 @@ constexpr float kPfRescaleStep = 8.0f;          // the reference maximum follows
 constexpr uint32_t kPfIdescScore = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kPfIdescValue = kPfIdescScore | (1u << 16);     // B (the values) is MN-major
 
+// Two float32 values in one 64-bit register and the instructions that work on both at once (sm_100): the
+// softmax threads are bound by what a warp can issue, and these halve the scale-and-shift and the sums.
+__device__ __forceinline__ unsigned long long pf_pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void pf_unpack2(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long pf_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long pf_add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float pf_max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 struct PrefillTcArgs {
   const bf16* q;
   bf16* out;
@@ -326,7 +352,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
     }
 
     const int my_blocks = tile_blocks[tile];
-    float ref_max = -INFINITY, row_sum = 0.0f;         // exponentials are taken against ref_max
+    float ref_max = -INFINITY;                         // exponentials are taken against ref_max
+    unsigned long long row_sum2 = pf_pack2(0.0f, 0.0f);   // the row's sum as two halves (even and odd keys)
     bool ok = true;
     for (int b = 0; b < my_blocks && ok; ++b) {
       const int kb = k_begin + b * kPfKeys;
@@ -347,12 +374,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
           if (!(key <= pos && key >= lo_pos)) score[i >> 5][i & 31] = 0xff800000u;
         }
       }
-      // eight running maxima: one chain of 128 dependent comparisons would cost their latencies in a row
+      // eight running maxima, two new scores a comparison: one chain of dependent comparisons would cost their
+      // latencies in a row
       float lane_max[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) lane_max[i] = __uint_as_float(score[0][i]);
 #pragma unroll
-      for (int i = 8; i < kPfKeys; ++i) lane_max[i & 7] = fmaxf(lane_max[i & 7], __uint_as_float(score[i >> 5][i & 31]));
+      for (int i = 8; i + 16 <= kPfKeys; i += 16) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          lane_max[c] = pf_max3(lane_max[c], __uint_as_float(score[(i + c) >> 5][(i + c) & 31]),
+                                __uint_as_float(score[(i + c + 8) >> 5][(i + c + 8) & 31]));
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) lane_max[c] = fmaxf(lane_max[c], __uint_as_float(score[3][24 + c]));
       float block_max = fmaxf(fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3])),
                               fmaxf(fmaxf(lane_max[4], lane_max[5]), fmaxf(lane_max[6], lane_max[7])));
       block_max *= args.scale_log2;                    // the scale is positive
@@ -366,7 +401,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
       if (moves) {
         alpha = ref_max == -INFINITY ? 0.0f : fast_exp2(ref_max - block_max);
         ref_max = block_max;
-        row_sum *= alpha;
+        float even, odd;
+        pf_unpack2(row_sum2, even, odd);
+        row_sum2 = pf_pack2(even * alpha, odd * alpha);
       }
       if (b > 0 && __any_sync(0xffffffffu, moves)) {
 #pragma unroll
@@ -380,15 +417,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
         }
       }
       const float shift = ref_max == -INFINITY ? 0.0f : ref_max;
-      // P = 2^(s * scale - ref_max) as bfloat16, two per column, over S's columns
+      // P = 2^(s * scale - ref_max) as bfloat16, two per column, over S's columns; scale-and-shift and the sum
+      // work on two keys an instruction
+      const unsigned long long scale2 = pf_pack2(args.scale_log2, args.scale_log2), shift2 = pf_pack2(-shift, -shift);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float e0 = fast_exp2(__uint_as_float(score[c][2 * i]) * args.scale_log2 - shift);
-          const float e1 = fast_exp2(__uint_as_float(score[c][2 * i + 1]) * args.scale_log2 - shift);
-          row_sum += e0 + e1;
+          float x0, x1;
+          pf_unpack2(pf_fma2(pf_pack2(__uint_as_float(score[c][2 * i]), __uint_as_float(score[c][2 * i + 1])), scale2, shift2), x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          row_sum2 = pf_add2(row_sum2, pf_pack2(e0, e1));
           const __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
           packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
         }
@@ -406,6 +446,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const
     bf16* dst = args.out + (static_cast<size_t>(tok_begin + token) * args.hq + kv_head * group + (p - token * group)) * kPfD;
     if (all_ok && my_blocks > 0) {
       tc_fence_after();
+      float even, odd;
+      pf_unpack2(row_sum2, even, odd);
+      const float row_sum = even + odd;
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
