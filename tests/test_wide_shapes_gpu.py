@@ -180,6 +180,41 @@ def test_graph_decode_of_three_requests_padded_to_a_bucket_of_four(tmp_path):
     runner.cache.check()
 
 
+def test_graph_decode_across_the_context_lengths_at_which_its_launches_change(tmp_path):
+    """Heads of 128: a decode tile is cut into no more key ranges than the context has blocks of 128 keys
+    (1, 2, 4, 8, then what the GPU's clusters allow), so a request that grows from 100 to 1,100 tokens
+    passes through several captured graphs of one bucket; the steps before, at and after every change are
+    compared with the plain implementation, and a replayed graph with a freshly captured one."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, intermediate_size=384))
+    raw.update(num_hidden_layers=2, vocab_size=400, max_position_embeddings=1280)
+    folder = write_random_model(tmp_path / "classes", Qwen3Config.from_dict(raw), 16, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    generator = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, 400, (1100,), generator=generator).tolist()
+    plain = forward_logits(config, weights, ids)
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=1280, page_size=16, num_pages=96, max_num_seqs=2,
+                          max_num_batched_tokens=1280, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    tolerance = at_scale("bfloat16", plain)
+    runner.admit("a")
+    runner.step([StepEntry("a", ids[:100], [])])
+    seen = []
+    for at in range(100, 1100):
+        got = runner.step_decode([StepEntry("a", ids[at : at + 1], [0])]).float().cpu()
+        torch.testing.assert_close(got[0], plain[at], **tolerance)
+        splits = sorted({value for _, constants in runner._graphs for _, name, value in constants if name == "splits"})
+        if not seen or seen[-1] != splits:
+            seen.append(splits)
+    runner.check_fault()
+    runner.cache.check()
+    assert seen[-1][:4] == [1, 2, 4, 8] and len(seen) >= 4          # one graph per class, each used again after its capture
+    assert {bucket for bucket, _ in runner._graphs} == {1}
+
+
 def test_the_same_steps_give_the_same_bits(tmp_path):
     """Reduction orders are fixed (cluster sums in rank order, split key ranges merged in order, no
     atomics on values): two engines fed the same steps return identical logits, bit for bit."""
