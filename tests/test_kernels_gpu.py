@@ -436,7 +436,7 @@ def test_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hq,hkv,tokens", [(6, 2, 7600), (5, 1, 11000), (32, 8, 1600)])
+@pytest.mark.parametrize("hq,hkv,tokens", [(6, 2, 7600), (5, 1, 11000), (32, 8, 1600), (32, 8, 300), (32, 8, 190)])
 def test_qk_norm_rope_write_with_many_tokens(dtype, hq, hkv, tokens):
     """Enough tokens that a warp takes a run of heads of its token (10 heads: runs of 8 and 2; 7 heads: a query
     and a key head, a value head and none share a warp instruction; the 48 heads of the 8B shape)."""
