@@ -64,17 +64,28 @@ class Workspace:
         self.device = device
         self._buffers: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
         self._retired: list[torch.Tensor] = []
+        # the views handed out, by (name, cols, dtype, rows): a step asks for hundreds of them, and making
+        # one costs as much as a launch's other bookkeeping
+        self._views: dict[tuple[str, int, torch.dtype, int], torch.Tensor] = {}
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype, min_rows: int | None = None) -> torch.Tensor:
+        view = self._views.get((name, cols, dtype, rows))
+        if view is not None:
+            return view
         key = (name, cols, dtype)
         buffer = self._buffers.get(key)
         if buffer is None or buffer.shape[0] < rows:
             want = max(rows, self.max_tokens if min_rows is None else min_rows)
             if buffer is not None:
                 self._retired.append(buffer)
+                for stale in [k for k in self._views if k[:3] == key]:
+                    del self._views[stale]
             buffer = torch.empty((want, cols), dtype=dtype, device=self.device)
             self._buffers[key] = buffer
-        return buffer[:rows]
+        view = buffer[:rows]
+        if len(self._views) < 4096:
+            self._views[(name, cols, dtype, rows)] = view
+        return view
 
     def nbytes(self) -> int:
         live = sum(b.numel() * b.element_size() for b in self._buffers.values())

@@ -42,10 +42,10 @@ def dtype_tag(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
 
 
-def _ptr(tensor: torch.Tensor | None) -> c_void_p:
-    if tensor is None:
-        return c_void_p(0)
-    return c_void_p(tensor.data_ptr())
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    """The address as ctypes takes it for a ``c_void_p`` parameter (a plain integer, ``None`` for null): every
+    launcher's signature is declared, so no wrapper object is needed, and a step passes thousands of these."""
+    return None if tensor is None else tensor.data_ptr()
 
 
 # Called before every launch of this module: whoever has queued work that the launch may depend on
@@ -53,10 +53,15 @@ def _ptr(tensor: torch.Tensor | None) -> c_void_p:
 BEFORE_LAUNCH = None
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
+    """The current stream of the current device as a raw handle (asked of torch's C layer directly: the Stream
+    object of ``torch.cuda.current_stream()`` costs several microseconds, and every launch asks)."""
     if BEFORE_LAUNCH is not None:
         BEFORE_LAUNCH()
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _raw_stream(torch.cuda.current_device())
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (lambda device: torch.cuda.current_stream(device).cuda_stream)
 
 
 def _need_cuda(*tensors: torch.Tensor | None) -> None:
