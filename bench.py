@@ -255,8 +255,8 @@ def graph_check(llm, seed: int) -> dict:
 
     runner = llm.runner
     vocab = runner.model.spec.vocab_size
-    prompts = random_prompts(2, 40, vocab, seed)
-    names = ["check0", "check1"]
+    names = ["check0", "check1"][: min(2, runner.config.max_num_seqs)]
+    prompts = random_prompts(len(names), 40, vocab, seed)
 
     def prefill():
         for name in names:
