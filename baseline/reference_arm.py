@@ -35,6 +35,15 @@ QWEN3_8B = {
     "tie_word_embeddings": False, "torch_dtype": "bfloat16", "attention_bias": False,
     "hidden_act": "silu", "use_sliding_window": False, "sliding_window": None,
 }
+# the other layer sizes of the benchmark (the same dictionary as in bench.py, written out again: this file
+# imports nothing of the repository)
+SHAPES = {
+    "8b": {},
+    "14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8,
+            "intermediate_size": 17408},
+    "32b": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "num_key_value_heads": 8,
+            "intermediate_size": 25600},
+}
 CONTEXT, PROMPT_LEN, PREFILL_TOKENS = 8192, 1024, 2048
 
 
@@ -114,16 +123,19 @@ def main() -> int:
     parser.add_argument("--workload", choices=["decode", "serve"], default="decode")
     parser.add_argument("--requests", type=int, default=64)
     parser.add_argument("--workdir", default="/tmp/rapid_llm_b200_reference_arm")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b")
+    parser.add_argument("--context", type=int, default=CONTEXT)
     args = parser.parse_args()
     globals()["PROMPT_LEN"] = args.prompt_len
+    globals()["CONTEXT"] = args.context
 
     import torch
 
-    config = dict(QWEN3_8B)
+    config = dict(QWEN3_8B, **SHAPES[args.shape])
     layers_full = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
-    folder = Path(args.workdir) / f"qwen3_8b_random_L{config['num_hidden_layers']}"
+    folder = Path(args.workdir) / f"qwen3_{args.shape}_random_L{config['num_hidden_layers']}"
     say(f"writing the random model folder {folder}")
     write_model_folder(folder, config, seed=0)
 

@@ -512,9 +512,8 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
     command = [sys.executable, str(arm), "--steps", str(args.steps), "--warmup", str(args.warmup),
                "--batch", str(args.batch), "--prompt-len", str(args.prompt_len),
-               "--workload", args.workload, "--requests", str(args.requests)]
-    if args.shape != "8b":
-        return {"impl": "reference", "unavailable": "the reference arm is set up for the 8B shape of the benchmark only"}
+               "--workload", args.workload, "--requests", str(args.requests), "--shape", args.shape,
+               "--context", str(CONTEXT)]
     if args.layers:
         command += ["--layers", str(args.layers)]
     try:
@@ -527,20 +526,21 @@ def run_reference(args) -> dict:
         tail = " | ".join((done.stderr or done.stdout).strip().splitlines()[-3:])[:400]
         return {"impl": "reference", "unavailable": f"the reference engine failed here (exit {done.returncode}): {tail}"}
     got = json.loads(lines[-1])
+    shape_name, sizes = SHAPES[args.shape]
     if args.workload == "serve":
         return {
-            "metric": f"generated tok/s, continuous batching of {args.requests} requests (Qwen3-8B shape)",
+            "metric": f"generated tok/s, continuous batching of {args.requests} requests ({shape_name} shape)",
             "value": round(got["generated_tokens"] / got["seconds"], 1), "unit": "tok/s", "n_gpus": 1,
             "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "reference",
             "seconds": round(got["seconds"], 3), "prompt_tokens": got["prompt_tokens"],
             "generated_tokens": got["generated_tokens"], "wanted_tokens": got["wanted_tokens"],
             "all_tokens_per_second": round((got["prompt_tokens"] + got["generated_tokens"]) / got["seconds"], 1),
-            "config": {"model": "Qwen3-8B shape, random weights", "layers": got["layers"], "layers_full": got["layers_full"],
+            "config": {"model": f"{shape_name} shape, random weights", "layers": got["layers"], "layers_full": got["layers_full"],
                        "requests": args.requests, "engine": "rapid_llm.engine.Scheduler (stock path, CUDA graphs on)"},
             "clocks": clocks.summary(),
         }
     peaks = measured_peaks()
-    raw = dict(QWEN3_8B)
+    raw = dict(QWEN3_8B, **sizes)
     layers = got["layers"]
     ms_per_step = got["device_ms"] / args.steps
     value = got["tokens"] / (got["device_ms"] / 1000.0)
@@ -549,13 +549,13 @@ def run_reference(args) -> dict:
     achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
     flops = prefill_flops(raw, layers, PREFILL_TOKENS)
     return {
-        "metric": f"decode tok/s at batch {args.batch} (Qwen3-8B shape, {PROMPT_LEN}-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name} shape, {PROMPT_LEN}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(value / REFERENCE_SAME_GPU_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": round(value / REFERENCE_SAME_GPU_TOK_S, 2) if args.shape == "8b" else None, "dtype": "bf16", "data": "synthetic",
         "impl": "reference",
         "config": {
-            "model": "Qwen3-8B shape, random weights", "layers": layers, "layers_full": got["layers_full"],
+            "model": f"{shape_name} shape, random weights", "layers": layers, "layers_full": got["layers_full"],
             "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
             "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE,
