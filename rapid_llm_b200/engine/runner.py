@@ -409,7 +409,8 @@ class ModelRunner:
         # what a captured step has baked in beside its addresses: the bucket and the planners' launch constants
         # (plain values and the sizes of their lists); a step that differs in one of them is another graph
         constants = tuple(
-            (str(key), name, tuple(value.shape) if isinstance(value, torch.Tensor) else value)
+            (str(key), name, tuple(value.shape) if isinstance(value, torch.Tensor)
+             else value if isinstance(value, (int, float, bool, str, type(None))) else repr(value))
             for key, plan in sorted(batch.extras.items(), key=lambda item: str(item[0])) for name, value in sorted(plan.items())
         )
         graph_key = (bucket, constants)
