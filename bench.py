@@ -456,7 +456,7 @@ def run_ours(args) -> dict:
         "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True,
         "scaling": "weak",
-        "vs_baseline": round(value / REFERENCE_SAME_GPU_TOK_S, 2) if (args.shape, args.batch, args.prompt_len) == ("8b", 8, 1024) else None,
+        "vs_baseline": round(value / REFERENCE_SAME_GPU_TOK_S, 2) if (args.shape, args.batch, args.prompt_len, layers) == ("8b", 8, 1024, layers_full) else None,
         "dtype": "bf16",
         "data": "synthetic",
         "impl": "ours",
