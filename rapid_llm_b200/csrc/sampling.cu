@@ -294,8 +294,10 @@ __device__ __forceinline__ float sample_peer_f32(const float* local, unsigned ra
   return value;
 }
 
+// (two CTAs a multiprocessor where the slice allows it: a cluster lives inside one GPC, only 15 clusters of 8 run at
+// one time with one CTA per multiprocessor, and a batch of 64 rows then took five rounds)
 template <typename T>
-__global__ void __launch_bounds__(kSampleThreads, 1)
+__global__ void __launch_bounds__(kSampleThreads, 2)
 sample_cluster_kernel(const T* __restrict__ logits, int vocab, long long row_stride, int slice,
                       const float* __restrict__ temperature, const float* __restrict__ top_p,
                       const float* __restrict__ penalty, const unsigned long long* __restrict__ seeds,
