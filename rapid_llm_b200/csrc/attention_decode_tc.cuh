@@ -495,6 +495,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
     if (softmax_warp && team == 0) {
       // where the other ranks keep their row statistics and this thread's column of their results
       uint32_t peer_lse[kTcMaxClusterSplits], peer_out[kTcMaxClusterSplits];
+      const bool wide = args.splits > 8;               // clusters of more than eight CTAs: the second half of the ranks
 #pragma unroll
       for (int r = 0; r < kTcMaxClusterSplits; ++r) {
         peer_lse[r] = r < args.splits ? peer_smem(smem_addr(&split_lse[0]), r) : 0u;
@@ -504,21 +505,49 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_cache, const 
         // all remote loads of the row first (each takes hundreds of cycles), the arithmetic after
         float lse_of[kTcMaxClusterSplits], out_of[kTcMaxClusterSplits];
 #pragma unroll
-        for (int r = 0; r < kTcMaxClusterSplits; ++r) {
+        for (int r = 0; r < 8; ++r) {
           lse_of[r] = r < args.splits ? load_peer_f32(peer_lse[r] + n * 4) : -INFINITY;
           out_of[r] = r < args.splits ? load_peer_f32(peer_out[r] + n * 128 * 4) : 0.0f;
         }
+#pragma unroll
+        for (int r = 8; r < kTcMaxClusterSplits; ++r) {
+          lse_of[r] = -INFINITY;
+          out_of[r] = 0.0f;
+        }
+        if (wide) {
+#pragma unroll
+          for (int r = 8; r < kTcMaxClusterSplits; ++r) {
+            if (r < args.splits) {
+              lse_of[r] = load_peer_f32(peer_lse[r] + n * 4);
+              out_of[r] = load_peer_f32(peer_out[r] + n * 128 * 4);
+            }
+          }
+        }
         float m = -INFINITY;
 #pragma unroll
-        for (int r = 0; r < kTcMaxClusterSplits; ++r) m = fmaxf(m, lse_of[r]);
+        for (int r = 0; r < 8; ++r) m = fmaxf(m, lse_of[r]);
+        if (wide) {
+#pragma unroll
+          for (int r = 8; r < kTcMaxClusterSplits; ++r) m = fmaxf(m, lse_of[r]);
+        }
         const float safe = m == -INFINITY ? 0.0f : m;
         float total = 0.0f, value = 0.0f;
 #pragma unroll
-        for (int r = 0; r < kTcMaxClusterSplits; ++r) {
+        for (int r = 0; r < 8; ++r) {
           if (r < args.splits) {
             const float w = fast_exp2(lse_of[r] - safe);
             total += w;
             value += w * out_of[r];
+          }
+        }
+        if (wide) {
+#pragma unroll
+          for (int r = 8; r < kTcMaxClusterSplits; ++r) {
+            if (r < args.splits) {
+              const float w = fast_exp2(lse_of[r] - safe);
+              total += w;
+              value += w * out_of[r];
+            }
           }
         }
         const int p = row0 + n, token = p / group;
