@@ -215,6 +215,34 @@ def test_graph_decode_across_the_context_lengths_at_which_its_launches_change(tm
     assert {bucket for bucket, _ in runner._graphs} == {1}
 
 
+def test_graph_decode_with_a_cluster_of_sixteen_key_ranges(tmp_path):
+    """Past 2,048 tokens a single request's decode tile is cut into as many key ranges as the GPU runs clusters of
+    (16 CTAs with two kv heads: a cluster size that has to be asked for), captured and replayed."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, intermediate_size=384))
+    raw.update(num_hidden_layers=2, vocab_size=400, max_position_embeddings=2304)
+    folder = write_random_model(tmp_path / "sixteen", Qwen3Config.from_dict(raw), 17, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    ids = torch.randint(0, 400, (2200,), generator=torch.Generator().manual_seed(10)).tolist()
+    tail = 6
+    plain = forward_logits(config, weights, ids, rows=range(len(ids) - tail, len(ids)))
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=2304, page_size=16, num_pages=160, max_num_seqs=2,
+                          max_num_batched_tokens=2304, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    runner.admit("a")
+    runner.step([StepEntry("a", ids[:-tail], [])])
+    got = []
+    for at in range(len(ids) - tail, len(ids)):
+        got.append(runner.step_decode([StepEntry("a", ids[at : at + 1], [0])]).float().cpu()[0])
+    runner.check_fault()
+    torch.testing.assert_close(torch.stack(got), plain, **at_scale("bfloat16", plain))
+    splits = {value for _, constants in runner._graphs for _, name, value in constants if name == "splits"}
+    assert splits and max(splits) > 8, splits
+
+
 def test_the_same_steps_give_the_same_bits(tmp_path):
     """Reduction orders are fixed (cluster sums in rank order, split key ranges merged in order, no
     atomics on values): two engines fed the same steps return identical logits, bit for bit."""
