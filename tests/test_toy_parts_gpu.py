@@ -1,9 +1,10 @@
-"""Toy parts of three other roles, defined here and nowhere in the framework: a feed-forward that routes
-each token to one of a few experts, a position encoding that is not the rotary one the framework ships, and an
-embedding that adds a learned row per absolute position.  They are registered, written as a random model
-folder, loaded, and stepped whole, in portions and token by token through captured graphs, beside the
-framework's own attention and feed-forward in other layers (different feed-forwards, windows and position
-encodings layer by layer), in both precisions, against a plain computation that is written out below.
+"""Toy parts of the other roles, defined here and nowhere in the framework: a feed-forward that routes
+each token to one of a few experts, a position encoding that is not the rotary one the framework ships, an
+embedding that adds a learned row per absolute position; and, in a second model, a norm with a mean and a bias
+and an arrangement that runs a layer's mixer and feed-forward side by side.  They are registered, written as a
+random model folder, loaded, and stepped whole, in portions and token by token through captured graphs, beside
+the framework's own parts in other layers (different feed-forwards, windows, position encodings, norms and
+arrangements layer by layer), in both precisions, against plain computations that are written out below.
 
 The toys are arithmetic for a test, not a model of anyone's.
 """
@@ -267,3 +268,215 @@ def test_toy_routing_feed_forward_position_encoding_and_embedding(tmp_path, dtyp
     for name, (ids, want) in plain.items():
         torch.testing.assert_close(torch.cat(pieces[name]), want, **at_scale(dtype, want))
         assert sum(cuts[name]) + tail <= len(ids)
+
+
+# ---------------------------------------------------------------------------------------------------
+# The two remaining roles: a norm and an arrangement of a layer's parts, again defined here alone.
+LN_EPS = 2e-5
+
+
+def register_norm_and_arrangement():
+    from rapid_llm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from rapid_llm_b200.parts import TensorSpec
+    from rapid_llm_b200.parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Norm
+    from rapid_llm_b200.parts.norm import ADD, FIRST
+
+    @NORMS.register("toy_layernorm")
+    class ToyLayerNorm(Norm):
+        """y = (r - mean(r)) / sqrt(var(r) + eps) * w + b with r = x or x + residual: a norm with a bias and a mean,
+        which no product can take along (it makes no such offer and runs by itself, on torch's kernels)."""
+
+        def __init__(self, *, size, eps, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.size, self.eps = size, eps
+            self.weight = self.new_storage((size,), "vector")
+            self.bias = self.new_storage((size,), "vector")
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec((self.size,), "vector", init="ones_normal"), "bias": TensorSpec((self.size,), "vector")}
+
+        def load_tensor(self, name, tensor):
+            {"weight": self.weight, "bias": self.bias}[name].copy_(tensor.to(torch.float32))
+
+        def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed"):
+            rows = x if row_index is None else x[row_index.long()]
+            summed = rows.float()
+            if mode == ADD:
+                summed = summed + (residual if row_index is None else residual[row_index.long()])
+            if write_residual:
+                residual.copy_(summed)
+            centred = summed - summed.mean(dim=-1, keepdim=True)
+            out = centred * torch.rsqrt(centred.pow(2).mean(dim=-1, keepdim=True) + self.eps) * self.weight + self.bias
+            return out.to(x.dtype)
+
+    @BLOCKS.register("toy_parallel")
+    class ToyParallelBlock(Block):
+        """h' = h + Mixer(Norm(h)) + FeedForward(Norm(h)): one norm, both parts read it, both results join the
+        residual stream.  The pair it hands on is (mixer's result + feed-forward's result, h)."""
+
+        def __init__(self, *, layer, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.norm = NORMS.build(layer.norm, dtype=dtype, device=device)
+            self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
+            self.children = (("only_norm.", self.norm), ("self_attn.", self.mixer), ("mlp.", self.feed_forward))
+
+        def cache_need(self):
+            return self.mixer.cache_need()
+
+        def step_planners(self):
+            planner = self.mixer.step_planner()
+            return [] if planner is None else [planner]
+
+        def tensor_specs(self):
+            return {prefix + name: spec for prefix, part in self.children for name, spec in part.tensor_specs().items()}
+
+        def load_tensor(self, name, tensor):
+            for prefix, part in self.children:
+                if name.startswith(prefix):
+                    return part.load_tensor(name[len(prefix):], tensor)
+            raise KeyError(name)
+
+        def finalize(self, loaded):
+            for prefix, part in self.children:
+                part.finalize({name[len(prefix):] for name in loaded if name.startswith(prefix)})
+
+        def forward(self, x, residual, batch, cache, then_norm=None):
+            from rapid_llm_b200.ops import gemm
+
+            gemm.flush()          # this block reads results with torch's kernels
+            if residual is None:
+                residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
+                normed = self.norm.forward(x, residual, batch, mode=FIRST, write_residual=True)
+            else:
+                normed = self.norm.forward(x, residual, batch, mode=ADD, write_residual=True)
+            mixed = self.mixer.forward(normed, batch, cache)
+            fed = self.feed_forward.forward(normed, batch)
+            gemm.flush()
+            both = batch.workspace.get("toy_both", x.shape[0], x.shape[1], x.dtype)
+            both.copy_((mixed.float() + fed.float()).to(x.dtype))
+            return both, residual
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyArrangedConfig:
+        vocab_size: int
+        architecture = "ToyArrangedForCausalLM"
+        model_type = "toy_arranged"
+
+        @classmethod
+        def from_dict(cls, raw, overrides=None):
+            return cls(dict(raw, **(overrides or {}))["vocab_size"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "model_type": self.model_type, "vocab_size": self.vocab_size}
+
+        def to_spec(self):
+            layer_norm = PartSpec("toy_layernorm", {"size": HIDDEN, "eps": LN_EPS})
+            rms = PartSpec("rmsnorm", {"size": HIDDEN, "eps": EPS})
+            rope = PartSpec("rope", {"head_dim": HEAD_DIM, "rotary_dim": HEAD_DIM, "theta": THETA, "max_positions": POSITIONS})
+            attention = PartSpec("gqa_attention", {"hidden_size": HIDDEN, "num_heads": HEADS, "num_kv_heads": KV_HEADS,
+                                                   "head_dim": HEAD_DIM, "position": rope, "qk_norm": True, "qk_norm_eps": EPS})
+            ffn = PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": 2 * INNER})
+            layers = (
+                LayerSpec("prenorm", attention, ffn, layer_norm, "model.layers.0."),        # the stock arrangement, the toy norm
+                LayerSpec("toy_parallel", attention, ffn, rms, "model.layers.1."),          # the toy arrangement, the stock norm
+                LayerSpec("toy_parallel", attention, ffn, layer_norm, "model.layers.2."),   # both toys
+                LayerSpec("prenorm", attention, ffn, rms, "model.layers.3."),               # all stock, after a toy block
+            )
+            return ModelSpec(
+                architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=HIDDEN, max_positions=POSITIONS,
+                embedding=PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN}),
+                layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(len(layers))), final_norm=layer_norm,
+                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "tied": False}),
+            )
+
+    register_architecture(ToyArrangedConfig)
+    return ToyArrangedConfig
+
+
+@torch.no_grad()
+def plain_arranged_logits(weights: dict, ids: list[int]) -> torch.Tensor:
+    def layer_norm(h, prefix):
+        centred = h - h.mean(dim=-1, keepdim=True)
+        return centred * torch.rsqrt(centred.pow(2).mean(dim=-1, keepdim=True) + LN_EPS) * weights[prefix + "weight"] + weights[prefix + "bias"]
+
+    def attention(x, prefix):
+        tokens = x.shape[0]
+        positions = torch.arange(tokens)
+        q = rms_norm((x @ weights[prefix + "q_proj.weight"].T).view(tokens, HEADS, HEAD_DIM), weights[prefix + "q_norm.weight"], EPS)
+        k = rms_norm((x @ weights[prefix + "k_proj.weight"].T).view(tokens, KV_HEADS, HEAD_DIM), weights[prefix + "k_norm.weight"], EPS)
+        v = (x @ weights[prefix + "v_proj.weight"].T).view(tokens, KV_HEADS, HEAD_DIM)
+        cos, sin = rope_angles(positions, HEAD_DIM, THETA)
+        out = causal_attention(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, HEAD_DIM**-0.5)
+        return out.reshape(tokens, HEADS * HEAD_DIM) @ weights[prefix + "o_proj.weight"].T
+
+    h = weights["model.embed_tokens.weight"][ids]
+    p = "model.layers.0."
+    h = h + attention(layer_norm(h, p + "input_layernorm."), p + "self_attn.")
+    h = h + swiglu(layer_norm(h, p + "post_attention_layernorm."), weights, p)
+    p = "model.layers.1."
+    x = rms_norm(h, weights[p + "only_norm.weight"], EPS)
+    h = h + attention(x, p + "self_attn.") + swiglu(x, weights, p)
+    p = "model.layers.2."
+    x = layer_norm(h, p + "only_norm.")
+    h = h + attention(x, p + "self_attn.") + swiglu(x, weights, p)
+    p = "model.layers.3."
+    h = h + attention(rms_norm(h, weights[p + "input_layernorm.weight"], EPS), p + "self_attn.")
+    h = h + swiglu(rms_norm(h, weights[p + "post_attention_layernorm.weight"], EPS), weights, p)
+    return layer_norm(h, "model.norm.") @ weights["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_norm_and_toy_arrangement(tmp_path, dtype):
+    """A norm with a mean and a bias and a block that runs mixer and feed-forward side by side, in layers between
+    stock blocks (so that norms ride on products in some layers and run by themselves in others): whole, in portions
+    side by side, and token by token from captured graphs, against the plain computation above."""
+    from rapid_llm_b200.config import EngineConfig
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.weights import write_random_model
+
+    config_class = register_norm_and_arrangement()
+    torch_dtype = getattr(torch, dtype)
+    folder = write_random_model(tmp_path / "toy_arranged", config_class(VOCAB), seed=23, dtype=torch_dtype, std=0.1, norm_std=0.2)
+    _, weights = load_model_dir(folder)
+    assert "model.layers.1.only_norm.weight" in weights and "model.layers.2.only_norm.bias" in weights
+    assert "model.layers.0.input_layernorm.bias" in weights and "model.norm.bias" in weights
+    engine = EngineConfig(dtype=torch_dtype, max_seq_len=POSITIONS, page_size=8, num_pages=40, max_num_seqs=3,
+                          max_num_batched_tokens=96, use_cuda_graph=True)
+    runner = ModelRunner.from_folder(folder, engine)
+    assert [type(layer).__name__ for layer in runner.model.layers] == ["PreNormBlock", "ToyParallelBlock", "ToyParallelBlock", "PreNormBlock"]
+
+    generator = torch.Generator().manual_seed(6)
+    tokens = {name: torch.randint(0, VOCAB, (count,), generator=generator).tolist() for name, count in (("a", 31), ("b", 18))}
+    plain = {name: plain_arranged_logits(weights, ids) for name, ids in tokens.items()}
+    for name, ids in tokens.items():
+        runner.admit(name)
+        got = runner.step([StepEntry(name, ids, list(range(len(ids))))]).float().cpu()
+        runner.release(name)
+        torch.testing.assert_close(got, plain[name], **at_scale(dtype, plain[name]))
+
+    cuts, fed, pieces = {"a": [6, 2, 14], "b": [7, 3]}, {"a": 0, "b": 0}, {"a": [], "b": []}
+    for name in tokens:
+        runner.admit(name)
+    for step in range(3):
+        entries = []
+        for name, ids in tokens.items():
+            if step < len(cuts[name]):
+                size = cuts[name][step]
+                entries.append(StepEntry(name, ids[fed[name] : fed[name] + size], list(range(size))))
+                fed[name] += size
+        logits = runner.step(entries).float().cpu()
+        at = 0
+        for entry in entries:
+            pieces[entry.request_id].append(logits[at : at + len(entry.tokens)].clone())
+            at += len(entry.tokens)
+    while any(fed[name] < len(ids) for name, ids in tokens.items()):
+        live = [name for name, ids in tokens.items() if fed[name] < len(ids)]
+        logits = runner.step_decode([StepEntry(name, [tokens[name][fed[name]]], [0]) for name in live]).float().cpu()
+        for row, name in enumerate(live):
+            pieces[name].append(logits[row : row + 1].clone())
+            fed[name] += 1
+    runner.check_fault()
+    assert runner._graphs
+    for name in tokens:
+        torch.testing.assert_close(torch.cat(pieces[name]), plain[name], **at_scale(dtype, plain[name]))
