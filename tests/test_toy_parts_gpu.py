@@ -1,7 +1,7 @@
 """Toy parts of the other roles, defined here and nowhere in the framework: a feed-forward that routes
 each token to one of a few experts, a position encoding that is not the rotary one the framework ships, an
-embedding that adds a learned row per absolute position; and, in a second model, a norm with a mean and a bias
-and an arrangement that runs a layer's mixer and feed-forward side by side.  They are registered, written as a
+embedding that adds a learned row per absolute position; and, in a second model, a norm with a mean and a bias,
+an arrangement that runs a layer's mixer and feed-forward side by side, and an output head that caps its logits.  They are registered, written as a
 random model folder, loaded, and stepped whole, in portions and token by token through captured graphs, beside
 the framework's own parts in other layers (different feed-forwards, windows, position encodings, norms and
 arrangements layer by layer), in both precisions, against plain computations that are written out below.
@@ -273,13 +273,38 @@ def test_toy_routing_feed_forward_position_encoding_and_embedding(tmp_path, dtyp
 # ---------------------------------------------------------------------------------------------------
 # The two remaining roles: a norm and an arrangement of a layer's parts, again defined here alone.
 LN_EPS = 2e-5
+HEAD_CAP = 1.5
 
 
 def register_norm_and_arrangement():
     from rapid_llm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
     from rapid_llm_b200.parts import TensorSpec
-    from rapid_llm_b200.parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Norm
+    from rapid_llm_b200.parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Norm, Part
+    from rapid_llm_b200.parts.base import HEADS as OUTPUT_HEADS
     from rapid_llm_b200.parts.norm import ADD, FIRST
+
+    @OUTPUT_HEADS.register("toy_capped_head")
+    class ToyCappedHead(Part):
+        """logits = cap * tanh((h W^T) / cap): an output head of the test's own (its product is the framework's)."""
+
+        def __init__(self, *, vocab_size, hidden_size, cap, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.cap = cap
+            self.weight = self.new_storage((vocab_size, hidden_size), "matrix")
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec(tuple(self.weight.shape))}
+
+        def load_tensor(self, name, tensor):
+            self.weight.copy_(tensor)
+
+        def forward(self, hidden_rows, batch):
+            from rapid_llm_b200.ops import gemm
+
+            out = batch.workspace.get("logits", hidden_rows.shape[0], self.weight.shape[0], hidden_rows.dtype, min_rows=64)
+            gemm.linear(hidden_rows, self.weight, out, batch.fault)
+            gemm.flush()
+            return out.copy_((self.cap * torch.tanh(out.float() / self.cap)).to(out.dtype))
 
     @NORMS.register("toy_layernorm")
     class ToyLayerNorm(Norm):
@@ -387,7 +412,7 @@ def register_norm_and_arrangement():
                 architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=HIDDEN, max_positions=POSITIONS,
                 embedding=PartSpec("token_embedding", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN}),
                 layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(len(layers))), final_norm=layer_norm,
-                head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "tied": False}),
+                head=PartSpec("toy_capped_head", {"vocab_size": self.vocab_size, "hidden_size": HIDDEN, "cap": HEAD_CAP}),
             )
 
     register_architecture(ToyArrangedConfig)
@@ -423,7 +448,7 @@ def plain_arranged_logits(weights: dict, ids: list[int]) -> torch.Tensor:
     p = "model.layers.3."
     h = h + attention(rms_norm(h, weights[p + "input_layernorm.weight"], EPS), p + "self_attn.")
     h = h + swiglu(rms_norm(h, weights[p + "post_attention_layernorm.weight"], EPS), weights, p)
-    return layer_norm(h, "model.norm.") @ weights["lm_head.weight"].T
+    return HEAD_CAP * torch.tanh(layer_norm(h, "model.norm.") @ weights["lm_head.weight"].T / HEAD_CAP)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
