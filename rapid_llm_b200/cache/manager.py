@@ -23,7 +23,7 @@ from typing import Hashable, Sequence
 
 import numpy as np
 
-from ..parts.base import CacheNeed, StateNeed
+from ..parts.base import CacheNeed
 
 NULL_PAGE = 0
 
