@@ -144,7 +144,7 @@ def test_embedding_and_head(dtype, folders):
     torch.testing.assert_close(logits.float().cpu(), h.float() @ weights["lm_head.weight"].T, **for_dtype(dtype))
 
 
-def test_run_order_names_a_layer_twice_and_shares_a_cache(tmp_path, tiny_dirs, tiny_plain):
+def test_run_order_names_a_layer_twice(tmp_path, tiny_dirs, tiny_plain):
     """Run order [0, 1, 0]: layer 0 runs twice with its own cache each time."""
     from rapid_llm_b200.config import EngineConfig, ScheduleEntry, load_config
     from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
