@@ -443,6 +443,29 @@ def test_qk_norm_rope_write_with_many_tokens(dtype, hq, hkv, tokens):
     check_qk_norm_rope_write(dtype, hq=hq, hkv=hkv, d=128, rotary=128, page=16, tokens=tokens, pages=tokens // 16 + 30)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,d,tokens", [(6, 32, 21), (3, 128, 40), (32, 128, 320), (5, 128, 2000)])
+def test_qk_norm_rope_write_of_queries_alone(dtype, hq, d, tokens):
+    """A layer that reads another layer's cache has queries only: rows of ``hq`` heads, nothing written to pages
+    (few tokens, and enough of them for the kernel that gives a warp a run of heads)."""
+    eps, theta, max_pos = 1e-6, 10000.0, 500
+    q_in = rand((tokens, hq * d), dtype, seed=18).to(DEV)
+    qw = (1 + 0.1 * rand((d,), torch.float32, seed=19)).to(DEV)
+    positions = torch.randint(0, max_pos, (tokens,), dtype=torch.int32)
+    cos, sin = rope_angles(torch.arange(max_pos), d, theta)
+    q_out = torch.empty((tokens, hq * d), dtype=dtype, device=DEV)
+    fault = fault_word()
+    k().qk_norm_rope_write(
+        q_in, q_out, num_heads=hq, num_kv_heads=2, head_dim=d, rotary_dim=d,
+        cos=cos.to(DEV).contiguous(), sin=sin.to(DEV).contiguous(), positions=positions.to(DEV), eps=eps,
+        fault=fault, q_weight=qw, k_weight=None, kv_dest=None, cache=None, page_size=16,
+    )
+    assert fault.item() == 0
+    c, s = cos[positions.long()], sin[positions.long()]
+    want = apply_rope(rms_norm(q_in.float().cpu().view(tokens, hq, d), qw.cpu(), eps), c, s)
+    torch.testing.assert_close(q_out.float().cpu().view(tokens, hq, d), want, **for_dtype(dtype))
+
+
 def check_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page, tokens, pages):
     eps, theta, max_pos = 1e-5, 50000.0, 300
     qkv = rand((tokens, (hq + 2 * hkv) * d), dtype, seed=8).to(DEV)
