@@ -5,9 +5,12 @@ float32 runs the hand-written true 32-bit kernel.  bfloat16 steps of up to
 tcgen05/TMA kernel, which streams the weight once at close to memory speed; larger steps call
 the library product (cuBLAS through ``torch.mm``), which is where the reference's engine
 uses a library as well (``rapid_llm/kernels/ops/gemm/linear.py:17-40``) and is still the
-faster of the two at thousands of tokens.  ``FORCE`` pins one for tests and measurements:
-``"tcgen05"`` (the streaming kernel at any size), ``"pair"`` (for steps above 64 tokens the kernel
-that pairs two CTAs on 256 x 256 tiles, ``csrc/gemm_bf16_pair.cu``: 0.85 to 1.0 of the library's pace at
+faster of the two at thousands of tokens.  The exception is the gate/up product of steps of
+:data:`PAIR_GATED_MIN_TOKENS` tokens and more: the kernel that pairs two CTAs on 256 x 256 tiles
+(``csrc/gemm_bf16_pair.cu``) applies SiLU(gate) * up in its epilogue, which saves the ``[T, 2 I]``
+intermediate and the activation kernel and is faster than the library with that kernel from there on.
+``FORCE`` pins one for tests and measurements: ``"tcgen05"`` (the streaming kernel at any size),
+``"pair"`` (the pair kernel for every product above 64 tokens: 0.85 to 1.0 of the library's pace at
 2,048 tokens and more, about half of it at a few hundred) or ``"library"``.
 
 A weight-only RMS norm between two tensor-core products rides on them instead of running as a
@@ -35,6 +38,7 @@ import torch
 from . import kernels
 
 TENSOR_CORE_MAX_TOKENS = 64
+PAIR_GATED_MIN_TOKENS = 1024  # gate/up with the activation fused, on pairs of CTAs, from this many tokens on
 FORCE: str | None = None      # "tcgen05", "pair", "library" or None (choose by size)
 FUSE_NORMS = True             # let a norm between two tensor-core products ride on them
 CHAIN = False                 # run deferred products of a small step as one persistent kernel
@@ -185,6 +189,10 @@ def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: 
         return act
     if scale:
         raise kernels.KernelError("gated_linear: rows with an open scale need the tensor-core product")
+    if (x.dtype == torch.bfloat16 and x.shape[0] >= PAIR_GATED_MIN_TOKENS and FORCE in (None, "pair")
+            and kernels.gemm_bf16_supports(x, gate_up) and act.shape[1] % 8 == 0):
+        flush()
+        return kernels.gemm_bf16_pair(x, gate_up, act, fault, swiglu=True)      # no [T, 2 I] intermediate
     wide = workspace.get("ffn_gate_up", x.shape[0], gate_up.shape[0], x.dtype)
     linear(x, gate_up, wide, fault)
     return kernels.silu_mul(wide, act)

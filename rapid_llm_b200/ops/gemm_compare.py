@@ -65,6 +65,26 @@ def main(argv=None) -> int:
             print(f"T={tokens:5d} {name:8s} pair {pair:7.1f} us ({flops / pair / 1e6:5.0f} TFLOP/s)  library {library:7.1f} us "
                   f"({flops / library / 1e6:5.0f})  one CTA a tile {single:7.1f} us  library/pair {library / pair:.2f}  "
                   f"elements off {wrong}", flush=True)
+        # the gate/up product with its activation: one kernel here, the library's product and the SiLU kernel there
+        x = torch.randn((tokens, args.hidden), generator=generator, device=device).to(torch.bfloat16)
+        weights = [(torch.randn((2 * args.intermediate, args.hidden), generator=generator, device=device) * 0.05).to(torch.bfloat16)
+                   for _ in range(3)]
+        act = torch.empty((tokens, args.intermediate), dtype=torch.bfloat16, device=device)
+        wide = torch.empty((tokens, 2 * args.intermediate), dtype=torch.bfloat16, device=device)
+        turn = [0]
+
+        def rotate():
+            turn[0] += 1
+            return weights[turn[0] % 3]
+
+        def library_then_silu():
+            torch.mm(x, rotate().t(), out=wide)
+            kernels.silu_mul(wide, act)
+
+        fused = timed(lambda: kernels.gemm_bf16_pair(x, rotate(), act, fault, swiglu=True))
+        apart = timed(library_then_silu)
+        print(f"T={tokens:5d} gate_up with SiLU(gate) * up: pair, fused {fused:7.1f} us  library + activation kernel {apart:7.1f} us  "
+              f"ratio {apart / fused:.2f}", flush=True)
     print("fault word", int(fault.item()))
     return 0 if int(fault.item()) == 0 else 1
 

@@ -575,28 +575,50 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.
 
 
 def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: torch.Tensor,
-                   bias: torch.Tensor | None = None) -> torch.Tensor:
+                   bias: torch.Tensor | None = None, *, swiglu: bool = False,
+                   residual: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+                   sumsq_out: torch.Tensor | None = None, sumsq_in: torch.Tensor | None = None,
+                   norm_eps: float = 0.0, norm_size: int = 0) -> torch.Tensor:
     """``out[T, N] = x[T, K] @ w[N, K]^T (+ bias)`` in bfloat16 for steps of many tokens: pairs of CTAs on
-    256 x 256 tiles (``tcgen05.mma.cta_group::2``), persistent over the tiles."""
-    _need_cuda(x, w, out, fault, bias)
+    256 x 256 tiles (``tcgen05.mma.cta_group::2``), persistent over the tiles, the tokens on the accumulator's lanes.
+
+    The options are those of :func:`gemm_bf16` and mean the same (``swiglu``: ``w`` is ``[2 N, K]``, gate rows
+    first; ``residual``, ``norm_weight``, ``sumsq_out``: the norm that follows rides, with a slot of
+    ``sumsq_out[T, gemm_bf16_sumsq_count(N)]`` per 32 columns; ``sumsq_in``, ``norm_eps``, ``norm_size``: the scale
+    a norm before the product left open), at any number of tokens.  ``N`` must be a multiple of 8."""
+    _need_cuda(x, w, out, fault, bias, residual, norm_weight, sumsq_out, sumsq_in)
     for name, tensor in (("x", x), ("w", w), ("out", out)):
         _expect(name, tensor, torch.bfloat16), _contig(name, tensor)
     tokens, k = x.shape
     n_out = out.shape[1]
-    if w.shape != (n_out, k) or out.shape[0] != tokens:
+    if w.shape != ((2 if swiglu else 1) * n_out, k) or out.shape[0] != tokens:
         raise KernelError(f"gemm_bf16_pair: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
-    if not gemm_bf16_supports(x, w):
-        raise KernelError("gemm_bf16_pair: the inner size must be a multiple of 8 and the operands 16-byte aligned")
+    if not gemm_bf16_supports(x, w) or n_out % 8:
+        raise KernelError("gemm_bf16_pair: the inner size and the result's width must be multiples of 8 and the operands 16-byte aligned")
     if bias is not None:
         _expect("bias", bias, torch.float32), _contig("bias", bias)
-        if bias.shape != (n_out,):
+        if bias.shape != (w.shape[0],):
             raise KernelError("gemm_bf16_pair: the bias does not have the weight's rows")
+    norm_follows = residual is not None or norm_weight is not None or sumsq_out is not None
+    if norm_follows:
+        if residual is None or norm_weight is None or sumsq_out is None or swiglu:
+            raise KernelError("gemm_bf16_pair: a following norm needs residual, norm_weight and sumsq_out, and no swiglu")
+        for name, tensor in (("residual", residual), ("norm_weight", norm_weight), ("sumsq_out", sumsq_out)):
+            _expect(name, tensor, torch.float32), _contig(name, tensor)
+        if (residual.shape != (tokens, n_out) or norm_weight.shape != (n_out,)
+                or sumsq_out.shape != (tokens, gemm_bf16_sumsq_count(n_out))):
+            raise KernelError("gemm_bf16_pair: residual, norm_weight or sumsq_out do not have the product's shape")
+    if sumsq_in is not None:
+        _expect("sumsq_in", sumsq_in, torch.float32), _contig("sumsq_in", sumsq_in)
+        if sumsq_in.dim() != 2 or sumsq_in.shape[0] != tokens or sumsq_in.shape[1] % 4 or norm_size <= 0:
+            raise KernelError("gemm_bf16_pair: sumsq_in must be [tokens, a multiple of 4] and norm_size positive")
     if tokens == 0:
         return out
     lib = gemm_lib()
     if not getattr(lib, "_pair_declared", False):
-        lib.rl_gemm_bf16_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                          c_void_p, c_void_p, c_void_p]
+        lib.rl_gemm_bf16_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_void_p]
         lib.rl_gemm_bf16_pair.restype = c_int
         lib.rl_gemm_bf16_pair_scratch_floats.restype = c_longlong
         lib.rl_gemm_bf16_pair_counter_words.restype = c_int
@@ -606,8 +628,11 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: t
         state = (torch.empty(lib.rl_gemm_bf16_pair_scratch_floats(), dtype=torch.float32, device=fault.device),
                  torch.zeros(lib.rl_gemm_bf16_pair_counter_words(), dtype=torch.int32, device=fault.device))
         _PAIR_STATE[fault.device] = state
-    _check(lib.rl_gemm_bf16_pair(_ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(PDL), _ptr(bias), _ptr(state[0]),
-                                 _ptr(state[1]), _ptr(fault), _stream()),
+    _check(lib.rl_gemm_bf16_pair(_ptr(x), _ptr(w), _ptr(out), tokens, n_out, k, int(swiglu), int(PDL),
+                                 _ptr(residual), _ptr(norm_weight), _ptr(sumsq_out),
+                                 0 if sumsq_out is None else sumsq_out.shape[1],
+                                 _ptr(sumsq_in), 0 if sumsq_in is None else sumsq_in.shape[1], float(norm_eps), int(norm_size),
+                                 _ptr(bias), _ptr(state[0]), _ptr(state[1]), _ptr(fault), _stream()),
            f"gemm_bf16_pair({tokens}x{k} by {n_out})")
     return out
 

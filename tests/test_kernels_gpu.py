@@ -277,10 +277,10 @@ def test_gemm_bf16_when_a_cta_walks_several_tiles(t, n, k_, swiglu):
 
 
 @pytest.mark.parametrize("t,n,k_,bias", [
-    (65, 130, 64, False), (128, 256, 128, True), (256, 256, 256, False),      # one tile, shared by as many pairs as get eight k-blocks
+    (65, 136, 64, False), (128, 256, 128, True), (256, 256, 256, False),      # one tile, shared by as many pairs as get eight k-blocks
     (300, 520, 264, True), (100, 6144, 4096, False),                          # ragged edges; the 128-token tile
     (512, 4096, 12288, False),                                                # 32 tiles, every one shared by two or three pairs
-    (1000, 1300, 1024, True),
+    (1000, 1304, 1024, True),
     (2048, 6144, 4096, False),                                                # 192 tiles on 74 pairs: two whole rounds and 44 shared tiles
     (2048, 24576, 4096, False), (4096, 4096, 12288, True),
 ])
@@ -305,6 +305,56 @@ def test_gemm_bf16_pair_of_ctas_on_one_tile(t, n, k_, bias):
         if bias:
             want = want + b[begin:end]
         torch.testing.assert_close(outs[0][:, begin:end].float(), want, rtol=6e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("t,n,k_,options", [
+    (128, 256, 128, {"swiglu"}), (300, 200, 320, {"swiglu", "bias", "scale"}), (1030, 1544, 520, {"swiglu", "scale"}),
+    (2048, 12288, 4096, {"swiglu", "scale"}),                                  # the gate/up product of a prompt step
+    (512, 1024, 256, {"norm"}), (333, 392, 320, {"norm", "scale", "bias"}), (700, 4096, 2048, {"norm"}),
+    (260, 264, 72, {"scale"}),
+])
+def test_gemm_bf16_pair_rows_are_the_threads_own(t, n, k_, options):
+    """The tokens are the accumulator's lanes, so the scale a norm left open, a bias, SiLU(gate) * up and the norm
+    that follows (residual, weight, sums of squares per 32 columns) are applied by the thread that owns the row;
+    whole tiles, ragged edges and tiles whose k-range several pairs share.  Against float32 arithmetic."""
+    kernels = k()
+    swiglu, norm = "swiglu" in options, "norm" in options
+    x = device_rand((t, k_), 0.5, seed=70)
+    w = device_rand(((2 if swiglu else 1) * n, k_), 0.05, seed=71)
+    want = x.float() @ w.float().T
+    extra = {}
+    if "scale" in options:
+        sumsq = torch.rand((t, 8), generator=torch.Generator().manual_seed(72)).to(DEV) * k_ / 8
+        extra.update(sumsq_in=sumsq, norm_eps=1e-5, norm_size=k_)
+        want = want * torch.rsqrt(sumsq.sum(1, keepdim=True) / k_ + 1e-5)
+    bias = torch.randn(w.shape[0], generator=torch.Generator().manual_seed(73)).to(DEV) if "bias" in options else None
+    if bias is not None:
+        want = want + bias
+    if swiglu:
+        want = torch.nn.functional.silu(want[:, :n]) * want[:, n:]
+    if norm:
+        residual = torch.randn((t, n), generator=torch.Generator().manual_seed(74)).to(DEV)
+        before = residual.clone()
+        weight = torch.rand(n, generator=torch.Generator().manual_seed(75)).to(DEV) + 0.5
+        table = torch.full((t, kernels.gemm_bf16_sumsq_count(n)), float("nan"), device=DEV)
+        extra.update(residual=residual, norm_weight=weight, sumsq_out=table)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    kernels.gemm_bf16_pair(x, w, out, fault, bias=bias, swiglu=swiglu, **extra)
+    assert fault.item() == 0
+    if norm:
+        after = before + want
+        torch.testing.assert_close(residual, after, rtol=1e-5, atol=2e-4 * max(1.0, float(want.abs().max())))
+        torch.testing.assert_close(table.sum(1), (after**2).sum(1), rtol=1e-4, atol=1e-3)
+        want = after * weight
+    torch.testing.assert_close(out.float(), want, rtol=8e-3, atol=2e-3 * max(1.0, float(want.abs().max())))
+
+
+def test_gemm_bf16_pair_refuses_a_width_that_is_no_multiple_of_8():
+    kernels = k()
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_bf16_pair(torch.zeros((300, 64), dtype=torch.bfloat16, device=DEV), torch.zeros((130, 64), dtype=torch.bfloat16, device=DEV),
+                               torch.zeros((300, 130), dtype=torch.bfloat16, device=DEV), fault_word())
 
 
 @pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
