@@ -72,6 +72,36 @@ def test_one_wide_layer_whole_in_portions_and_decoding(name, tmp_path):
     assert at == {"a": 300, "b": 90}
 
 
+def test_a_step_of_more_than_a_thousand_tokens_at_the_widths_of_a_large_model(tmp_path):
+    """Two prompts of 700 and 400 tokens in one step at hidden 5120 and an intermediate size of 17,408: from 1,024
+    tokens on the gate/up product applies its activation itself, on pairs of CTAs, here over 136 weight tiles and
+    five token tiles of which the last is ragged and holds the end of one request and nothing after it."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.ops import gemm
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(WIDE["heads40_inter17408"])
+    raw["max_position_embeddings"] = 1024
+    folder = write_random_model(tmp_path / "wide", Qwen3Config.from_dict(raw), 12, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    generator = torch.Generator().manual_seed(9)
+    tokens = {"a": torch.randint(0, 1000, (700,), generator=generator).tolist(),
+              "b": torch.randint(0, 1000, (400,), generator=generator).tolist()}
+    assert sum(len(ids) for ids in tokens.values()) >= gemm.PAIR_GATED_MIN_TOKENS
+    plain = {key: forward_logits(config, weights, ids) for key, ids in tokens.items()}
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=1024, page_size=16, num_pages=80, max_num_seqs=2,
+                          max_num_batched_tokens=1536, max_chunk_size=1536, use_cuda_graph=False)
+    runner = ModelRunner.from_folder(folder, engine)
+    runner.admit("a")
+    runner.admit("b")
+    places = {"a": [0, 255, 256, 511, 699], "b": [0, 67, 68, 399]}       # 68: the first row of the last token tile
+    got = runner.step([StepEntry("a", tokens["a"], places["a"]), StepEntry("b", tokens["b"], places["b"])]).float().cpu()
+    want = torch.cat([plain["a"][places["a"]], plain["b"][places["b"]]])
+    torch.testing.assert_close(got, want, **at_scale("bfloat16", plain["a"]))
+    runner.check_fault()
+
+
 def test_a_long_context_with_heads_of_128(tmp_path):
     """3,300 tokens through two narrow layers with heads of 128: prompt portions whose tiles look
     back over thousands of cached keys, then single tokens whose key range is split over a
