@@ -167,7 +167,8 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
     flush()
     if scale:
         raise kernels.KernelError("linear: rows with an open scale need the tensor-core product")
-    if FORCE == "pair" and fault is not None and kernels.gemm_bf16_supports(x, weight):
+    if (FORCE == "pair" and fault is not None and kernels.gemm_bf16_supports(x, weight)
+            and kernels.gemm_bf16_pair_takes(x.shape[0], out.shape[1], False)):
         return kernels.gemm_bf16_pair(x, weight, out, fault, bias=bias)
     if bias is None:
         torch.mm(x, weight.t(), out=out)
@@ -190,7 +191,7 @@ def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: 
     if scale:
         raise kernels.KernelError("gated_linear: rows with an open scale need the tensor-core product")
     if (x.dtype == torch.bfloat16 and x.shape[0] >= PAIR_GATED_MIN_TOKENS and FORCE in (None, "pair")
-            and kernels.gemm_bf16_supports(x, gate_up) and act.shape[1] % 8 == 0):
+            and kernels.gemm_bf16_supports(x, gate_up) and kernels.gemm_bf16_pair_takes(x.shape[0], act.shape[1], True)):
         flush()
         return kernels.gemm_bf16_pair(x, gate_up, act, fault, swiglu=True)      # no [T, 2 I] intermediate
     wide = workspace.get("ffn_gate_up", x.shape[0], gate_up.shape[0], x.dtype)

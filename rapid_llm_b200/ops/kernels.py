@@ -640,6 +640,15 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fault: t
 _PAIR_STATE: dict[torch.device, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
+def gemm_bf16_pair_takes(tokens: int, n_out: int, swiglu: bool) -> bool:
+    """Whether a product of this size is within the pair kernel's table of tiles (256 tokens by 256 columns of the
+    result, 128 with ``swiglu``); larger products are the library's."""
+    lib = gemm_lib()
+    lib.rl_gemm_bf16_pair_counter_words.restype = c_int
+    tiles = -(-int(tokens) // 256) * -(-int(n_out) // (128 if swiglu else 256))
+    return n_out % 8 == 0 and tiles <= lib.rl_gemm_bf16_pair_counter_words() // 2
+
+
 class _ChainPhase(ctypes.Structure):
     """``RlChainPhase`` of ``csrc/gemm_chain.cu``."""
 

@@ -350,6 +350,16 @@ def test_gemm_bf16_pair_rows_are_the_threads_own(t, n, k_, options):
     torch.testing.assert_close(out.float(), want, rtol=8e-3, atol=2e-3 * max(1.0, float(want.abs().max())))
 
 
+def test_gemm_bf16_pair_says_which_products_it_takes():
+    """The router asks before it calls: a width that is no multiple of 8, or more tiles than the kernel's table
+    holds (4,096: 32,768 tokens by 25,600 gated columns are 25,600), goes to the library instead."""
+    kernels = k()
+    assert kernels.gemm_bf16_pair_takes(2048, 12288, True) and kernels.gemm_bf16_pair_takes(8192, 25600, False)
+    assert not kernels.gemm_bf16_pair_takes(2048, 12290, True)
+    assert not kernels.gemm_bf16_pair_takes(32768, 25600, True)
+    assert kernels.gemm_bf16_pair_takes(256 * 32, 128 * 128, True) and not kernels.gemm_bf16_pair_takes(256 * 32 + 1, 128 * 128, True)
+
+
 def test_gemm_bf16_pair_refuses_a_width_that_is_no_multiple_of_8():
     kernels = k()
     with pytest.raises(kernels.KernelError):
