@@ -199,7 +199,7 @@ def test_running_ahead_does_not_change_a_token(tiny_dirs, tiny_dirs_bf16, dtype)
     assert any(reason == "eos" for _, reason in results[True])
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_many_requests_under_pressure_equal_plain(tiny_dirs, tiny_plain, name):
     """Twenty requests of every length through four slots and a pool that holds two of the longest:
     portions beside decoded tokens, evictions, pages and slots used again, graphs and run-ahead on.
