@@ -55,6 +55,7 @@ struct GemmArgs {
   int T, N, K;
   int up_offset;           // first "up" row of the weight (SwiGLU), else unused
   int n_tiles, t_tiles, k_blocks;
+  int tile_rows;           // weight rows a tile brings (kTileN, or fewer so that the tiles of an unsplit SwiGLU product fill the GPU evenly)
   int k_split;             // CTAs (= cluster size) that share one tile's k-range
   int pdl;                 // launched with programmatic stream serialization
   // a norm that follows this product (plain products of one token tile only; all three or none):
@@ -152,9 +153,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int n_tile = tile_of(c.index) / args.t_tiles;
     const int k = (kb_begin + c.kb) * kTileK;
     const uint32_t bar = smem_addr(&full_bar[stage]);
-    mbar_expect_tx(bar, Shape::kStageBytes);
-    tma_load_2d_hint(stage_a(stage, 0), &map_w, bar, k, n_tile * kTileN, weights_once);
-    if (kSwiglu) tma_load_2d_hint(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * kTileN, weights_once);
+    // a tile of fewer than kTileN weight rows fills the first rows of its place; the product still reads all
+    // kTileN, and the accumulator's lanes past the tile's rows are never looked at
+    mbar_expect_tx(bar, kHalves * args.tile_rows * kTileK * 2 + BN * kTileK * 2);
+    tma_load_2d_hint(stage_a(stage, 0), &map_w, bar, k, n_tile * args.tile_rows, weights_once);
+    if (kSwiglu) tma_load_2d_hint(stage_a(stage, 1), &map_w, bar, k, args.up_offset + n_tile * args.tile_rows, weights_once);
   };
   auto load_b = [&](const Cursor& c, int stage) {
     const int t_tile = tile_of(c.index) % args.t_tiles;
@@ -295,7 +298,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     for (int index = 0; index < my_tiles && ok; ++index) {
       const int tile = tile_of(index);
       const int n_tile = tile / args.t_tiles, t_tile = tile - n_tile * args.t_tiles;
-      const int n = n_tile * kTileN + n_local, t0 = t_tile * BN;
+      // (a tile of fewer rows than lanes: only unsplit SwiGLU products, whose lanes past the tile's rows look like
+      // columns past the matrix's edge)
+      const int n = n_local < args.tile_rows ? n_tile * args.tile_rows + n_local : args.N;
+      const int t0 = t_tile * BN;
       ok = mbar_wait(smem_addr(&acc_full_bar[buf]), acc_phase[buf], aborted, args.fault);
       if (!ok) break;
       tc_fence_after();
@@ -572,8 +578,25 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
                               (reinterpret_cast<uintptr_t>(sumsq_in) & 15)))
     return static_cast<int>(cudaErrorInvalidValue);
   const int bn = rl::token_tile(tokens, swiglu != 0);
+  const int t_tiles = (tokens + bn - 1) / bn;
+  // An unsplit SwiGLU product of token tiles that take a multiprocessor each (33 tokens and more) walks its weight
+  // tiles in rounds of one tile per multiprocessor.  Tiles of 128 rows leave the last round part empty (96 tiles
+  // of a 12,288-row product on 148 multiprocessors); tiles of fewer rows, as many as fill the rounds evenly (88:
+  // 140 tiles), shorten every CTA's stream instead.
+  int tile_rows = rl::kTileN;
+  if (swiglu != 0 && bn >= 64 && k_split <= 1) {
+    const long long sms = rl::sm_count();
+    const long long tiles = static_cast<long long>((n_out + rl::kTileN - 1) / rl::kTileN) * t_tiles;
+    const long long rounds = (tiles + sms - 1) / sms;
+    const long long per_token_tile = rounds * sms / t_tiles;                    // weight tiles that fill the rounds
+    if (per_token_tile > 0) {
+      const long long rows = ((n_out + per_token_tile - 1) / per_token_tile + 7) / 8 * 8;
+      if (rows >= 32 && rows < rl::kTileN) tile_rows = static_cast<int>(rows);
+    }
+    if (tile_rows != rl::kTileN) k_split = 1;       // such tiles are never shared by a cluster
+  }
   CUtensorMap map_w, map_x;
-  int status = rl::make_map(&map_w, w, static_cast<long long>(n_out) * (swiglu ? 2 : 1), k, rl::kTileN);
+  int status = rl::make_map(&map_w, w, static_cast<long long>(n_out) * (swiglu ? 2 : 1), k, tile_rows);
   if (status != 0) return status;
   status = rl::make_map(&map_x, x, tokens, k, bn);
   if (status != 0) return status;
@@ -582,8 +605,9 @@ int rl_gemm_bf16_norm(const void* x, const void* w, void* out, int tokens, int n
   args.fault = fault;
   args.T = tokens; args.N = n_out; args.K = k;
   args.up_offset = n_out;
-  args.n_tiles = (n_out + rl::kTileN - 1) / rl::kTileN;
-  args.t_tiles = (tokens + bn - 1) / bn;
+  args.tile_rows = tile_rows;
+  args.n_tiles = (n_out + tile_rows - 1) / tile_rows;
+  args.t_tiles = t_tiles;
   args.k_blocks = (k + rl::kTileK - 1) / rl::kTileK;
   args.k_split = 1;
   args.pdl = pdl;

@@ -137,6 +137,28 @@ def test_gemm_bf16(t, n, k_, swiglu):
     torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
 
 
+@pytest.mark.parametrize("t,n,k_", [(64, 12288, 520), (40, 4800, 264), (33, 3553, 136), (64, 25600, 136), (57, 12290, 72),
+                                    (100, 12288, 264), (200, 17408, 136)])
+def test_gemm_bf16_swiglu_tiles_that_fill_the_rounds(t, n, k_):
+    """An unsplit SwiGLU product of 33 tokens and more takes weight tiles of fewer than 128 rows where 128-row tiles
+    would leave its last round of one tile per multiprocessor part empty (12,288 rows: 140 tiles of 88 instead of 96
+    of 128; 25,600 rows: two even rounds); the lanes past a tile's rows are never stored.  Every column against the
+    float32 arithmetic, ragged widths included."""
+    x = rand((t, k_), torch.bfloat16, seed=30).to(DEV)
+    w = rand((2 * n, k_), torch.bfloat16, scale=0.05, seed=31).to(DEV)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16(x, w, out, fault, swiglu=True)
+    assert fault.item() == 0
+    want = bf16_product(x, w, n, True)
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
+    forced = torch.empty_like(out)
+    k().gemm_bf16(x, w, forced, fault, swiglu=True, k_split=2 if t <= 64 else 1)      # 128-row tiles
+    if t <= 64:
+        torch.testing.assert_close(out.float(), forced.float(), rtol=1e-2, atol=1e-2 * float(want.abs().max()) / 4 + 1e-3)
+
+
 @pytest.mark.parametrize("split", [2, 4, 8])
 @pytest.mark.parametrize("t,n,k_,swiglu", [(8, 256, 4096, False), (33, 384, 1024, False), (64, 130, 12288, False),
                                            (7, 160, 1000, True), (60, 256, 2048, True)])
