@@ -657,6 +657,8 @@ int rl_attention_decode_rows() { return 16; }
 
 // chunk_rows: packed rows per chunk item: 64 (or 0) = the mma.sync tiles, 256 = the tcgen05
 // kernel (head size 128, pages it takes, splits == 1).
+// decode_splits: key ranges of the decode tiles where they differ from `splits` (a step of prompt portions, which
+// the tcgen05 kernel does not split, beside single tokens with long contexts); 0 = the same.
 // decode_kernel: 0 = the tcgen05 kernel for decode tiles where it applies, 1 = always the
 // mma.sync tiles, 2 / 3 = the tcgen05 kernel with deep rings (one CTA per multiprocessor) / shallow
 // rings (two) whatever the number of items.  decode_rows: the most packed rows any decode tile has (0 = not known).
@@ -695,11 +697,17 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
                      int window, int splits, float scale, int* fault, int pdl, int decode_kernel, int decode_rows,
-                     int chunk_rows, cudaStream_t stream) {
+                     int chunk_rows, int decode_splits, cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
       hkv > 65535 || n_chunk_items > 65535 || n_decode_items > 65535)      // grid y dimensions
+    return static_cast<int>(cudaErrorInvalidValue);
+  // key ranges of the decode tiles alone (0 = as `splits`): only where the chunk tiles are not split and the decode
+  // kernel merges its ranges inside a cluster, so that no scratch and no merge kernel are involved
+  if (decode_splits < 0 || (decode_splits > 0 && decode_splits != splits &&
+                            (splits != 1 || decode_kernel == 1 || !attn::decode_tc_supported(page_size) ||
+                             decode_splits > attn::kTcMaxClusterSplits || n_decode_items % decode_splits != 0)))
     return static_cast<int>(cudaErrorInvalidValue);
   attn::AttentionArgs args;
   args.q = static_cast<const attn::bf16*>(q);
@@ -734,9 +742,13 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   if (n_decode_items > 0) {
     args.items = decode_items;
     if (decode_kernel != 1 && attn::decode_tc_supported(page_size)) {
-      merged_in_cluster = n_chunk_items == 0 && splits > 1 && splits <= attn::kTcMaxClusterSplits && n_decode_items % splits == 0;
+      const bool own_splits = decode_splits > 1 && decode_splits != splits;
+      if (own_splits) args.splits = decode_splits;
+      merged_in_cluster = own_splits || (n_chunk_items == 0 && splits > 1 && splits <= attn::kTcMaxClusterSplits &&
+                                         n_decode_items % splits == 0);
       status = attn::launch_decode_tc(args, n_decode_items, decode_rows, merged_in_cluster, pdl != 0, stream,
                                       decode_kernel == 2 || decode_kernel == 3 ? decode_kernel : 0);
+      args.splits = splits;
     } else
       status = attn::launch_attention<1, 4, 3>(args, n_decode_items, pdl != 0, stream);
     if (status != 0) return status;
@@ -836,7 +848,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, 0, stream);
 }
 
 }  // extern "C"

@@ -357,7 +357,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         lib.rl_attention_decode_max_clusters.argtypes = [c_int]
@@ -411,6 +411,7 @@ def attention_mma(
     decode_kernel: str = "auto",
     decode_rows: int = 0,
     chunk_rows: int = CHUNK_TILE_ROWS,
+    decode_splits: int = 0,
 ) -> torch.Tensor:
     """bfloat16 paged causal attention over work items the host cut the step into.
 
@@ -424,7 +425,9 @@ def attention_mma(
     split, 0)`` for tiles of :data:`CHUNK_TILE_ROWS` / :data:`DECODE_TILE_ROWS` packed rows
     (row ``p`` of an entry is token ``p // group``, head ``p % group`` of each kv head).
     With ``splits > 1`` every item exists once per split and ``part_out`` ``[T * Hq * splits,
-    D]`` / ``part_lse`` ``[T * Hq * splits]`` (float32) are scratch.
+    D]`` / ``part_lse`` ``[T * Hq * splits]`` (float32) are scratch.  ``decode_splits`` (0 = as ``splits``) gives
+    the decode items a split count of their own, merged inside the tcgen05 decode kernel's clusters: only with
+    ``splits == 1``, where that kernel applies, up to 16.
     """
     _need_cuda(q, cache, out, chunk_items, decode_items, part_out, part_lse, cu_seqlens, entry_start,
                entry_slot, block_table, fault)
@@ -454,7 +457,8 @@ def attention_mma(
             _ptr(decode_items), n_decode, _ptr(cu_seqlens), _ptr(entry_start), _ptr(entry_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
-            _ptr(fault), int(PDL), {"auto": 0, "mma": 1, "deep": 2, "shallow": 3}[decode_kernel], int(decode_rows), int(chunk_rows), _stream(),
+            _ptr(fault), int(PDL), {"auto": 0, "mma": 1, "deep": 2, "shallow": 3}[decode_kernel], int(decode_rows), int(chunk_rows),
+            int(decode_splits), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )

@@ -123,6 +123,15 @@ class AttentionItems(StepPlanner):
             if chunk_ctas >= TC_CHUNK_MIN_CTAS or longest <= TC_CHUNK_SHORT_CONTEXT:
                 splits = 1
                 break
+        # Single tokens beside prompt portions that the tcgen05 kernel takes unsplit: their tiles get key ranges of
+        # their own (merged inside that kernel's clusters), or a request far into its context would be walked by one
+        # CTA per kv head while the step waits.
+        decode_splits = splits
+        if (tensor_core and not shape.decode_only and splits == 1 and chunk_rows == kernels.CHUNK_TILE_ROWS_TC
+                and bool(is_decode.any()) and not bool(is_decode.all())):
+            decode_ctas = int(tiles[is_decode].sum()) * self.num_kv_heads
+            blocks = max(1, -(-int((starts + lengths)[is_decode].max()) // kernels.DECODE_TC_KEYS))
+            decode_splits = min(cluster_splits(decode_ctas, self.decode_clusters), 1 << (blocks.bit_length() - 1))
         entry = np.repeat(np.arange(len(lengths), dtype=np.int64), tiles)
         first = np.concatenate(([0], np.cumsum(tiles)[:-1]))
         tile_index = np.arange(int(tiles.sum()), dtype=np.int64) - np.repeat(first, tiles)
@@ -131,19 +140,20 @@ class AttentionItems(StepPlanner):
         # keys a tile has to walk: the tiles with the most go first, so that the last wave is short
         keys = np.repeat(starts, tiles) + (row0 + np.repeat(tile_rows, tiles)) // self.group
 
-        def items(mask: np.ndarray) -> np.ndarray:
+        def items(mask: np.ndarray, ranges: int) -> np.ndarray:
             order = np.flatnonzero(mask)
             order = order[np.argsort(-keys[order], kind="stable")]
             count = len(order)
-            out = np.zeros((count * splits, 4), dtype=np.int32)
-            out[:, 0] = np.repeat(entry[order], splits)
-            out[:, 1] = np.repeat(row0[order], splits)
-            out[:, 2] = np.tile(np.arange(splits, dtype=np.int32), count)
+            out = np.zeros((count * ranges, 4), dtype=np.int32)
+            out[:, 0] = np.repeat(entry[order], ranges)
+            out[:, 1] = np.repeat(row0[order], ranges)
+            out[:, 2] = np.tile(np.arange(ranges, dtype=np.int32), count)
             return out
 
         decode_rows = int(np.minimum(rows[is_decode], kernels.DECODE_TILE_ROWS).max()) if is_decode.any() else 0
-        return {"chunk_items": items(~decode_tile), "decode_items": items(decode_tile), "splits": splits,
-                "decode_rows": decode_rows, "chunk_rows": int(chunk_rows)}
+        return {"chunk_items": items(~decode_tile, splits), "decode_items": items(decode_tile, decode_splits),
+                "splits": splits, "decode_splits": int(decode_splits), "decode_rows": decode_rows,
+                "chunk_rows": int(chunk_rows)}
 
 
 @MIXERS.register("gqa_attention")
@@ -298,6 +308,7 @@ class GQAAttention(Mixer):
                 block_table=group.block_table, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
                 window=self.window, scale=self.scale, fault=batch.fault, decode_rows=plan.get("decode_rows", 0),
                 chunk_rows=plan.get("chunk_rows", kernels.CHUNK_TILE_ROWS),
+                decode_splits=plan.get("decode_splits", 0),
             )
             return
         kernels.attention_generic(

@@ -114,10 +114,21 @@ def test_chunk_tiles_follow_the_kernel_that_will_run():
     for count, start in [(512, 0), (1024, 3072), (512, 7000), (100, 500), (32, 600)]:
         plan = planner.plan(StepShape(np.asarray([count], dtype=np.int32), np.asarray([start], dtype=np.int32), False, page_size=16))
         assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1, (count, start)
-    # a decode token beside such a portion is not split either (one split count per step)
+    # a decode token beside such a portion gets key ranges of its own, merged in the decode kernel's clusters: eight
+    # tiles (one per kv head) run as clusters of ten; the portion's tiles stay unsplit
     mixed = StepShape(np.asarray([700, 1], dtype=np.int32), np.asarray([0, 3000], dtype=np.int32), False, page_size=16)
     plan = planner.plan(mixed)
-    assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1 and len(plan["decode_items"]) == 1
+    assert plan["chunk_rows"] == kernels.CHUNK_TILE_ROWS_TC and plan["splits"] == 1
+    assert plan["decode_splits"] == 10 and len(plan["decode_items"]) == 10 and len(plan["chunk_items"]) == -(-700 * 4 // 256)
+    assert list(plan["decode_items"][:, 2]) == list(range(10)) and set(plan["decode_items"][:, 0]) == {1}
+    # ... as many as its context has blocks of 128 keys, rounded down to a power of two; none for a short one
+    for start, want in [(100, 1), (300, 2), (1100, 8)]:
+        near = StepShape(np.asarray([700, 1], dtype=np.int32), np.asarray([0, start], dtype=np.int32), False, page_size=16)
+        assert planner.plan(near)["decode_splits"] == want, start
+    # sixty-four decode tokens beside a portion are 512 tiles: no cluster size runs that many at one time
+    lengths = np.asarray([700] + [1] * 64, dtype=np.int32)
+    starts = np.asarray([0] + [5000] * 64, dtype=np.int32)
+    assert planner.plan(StepShape(lengths, starts, False, page_size=16))["decode_splits"] == 1
     # other head sizes or page sizes: the mma.sync tiles
     assert AttentionItems(4, 8, 64).plan(whole)["chunk_rows"] == kernels.CHUNK_TILE_ROWS
     odd = StepShape(np.asarray([2048], dtype=np.int32), np.asarray([0], dtype=np.int32), False, page_size=4)

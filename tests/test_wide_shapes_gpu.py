@@ -135,6 +135,57 @@ def test_a_long_context_with_heads_of_128(tmp_path):
     assert at == 3300
 
 
+def test_single_tokens_far_into_their_context_beside_a_prompt_portion(tmp_path):
+    """A step of prompt portions (which the tcgen05 kernel takes unsplit) beside single tokens of requests that are
+    thousands of tokens into their contexts: the single tokens' tiles get key ranges of their own, merged inside the
+    decode kernel's clusters (ten ranges for one such request, six for two), and both kinds of rows agree with the
+    plain implementation."""
+    from rapid_llm_b200.config import EngineConfig, Qwen3Config
+    from rapid_llm_b200.engine.runner import ModelRunner, StepEntry
+    from rapid_llm_b200.parts.base import StepShape
+    from rapid_llm_b200.weights import write_random_model
+
+    raw = wide_config(dict(hidden_size=256, num_attention_heads=16, num_key_value_heads=8, intermediate_size=512))
+    raw.update(num_hidden_layers=2, vocab_size=500, max_position_embeddings=4096)
+    folder = write_random_model(tmp_path / "mixed", Qwen3Config.from_dict(raw), 14, dtype=torch.bfloat16)
+    config, weights = load_model_dir(folder)
+    generator = torch.Generator().manual_seed(16)
+    tokens = {"far": torch.randint(0, 500, (3010,), generator=generator).tolist(),
+              "deep": torch.randint(0, 500, (1500,), generator=generator).tolist(),
+              "new": torch.randint(0, 500, (1800,), generator=generator).tolist()}
+    plain = {name: forward_logits(config, weights, ids) for name, ids in tokens.items()}
+    engine = EngineConfig(dtype=torch.bfloat16, max_seq_len=4096, page_size=16, num_pages=400, max_num_seqs=3,
+                          max_num_batched_tokens=1024, use_cuda_graph=False)
+    runner = ModelRunner.from_folder(folder, engine)
+    tolerance = at_scale("bfloat16", plain["far"])
+    at = {"far": 3000, "deep": 1494, "new": 0}
+    for name in ("far", "deep"):
+        runner.admit(name)
+        fed = 0
+        while fed < at[name]:
+            size = min(1000, at[name] - fed)
+            runner.step([StepEntry(name, tokens[name][fed : fed + size], [])])
+            fed += size
+    runner.admit("new")
+    (planner,) = runner.model.step_planners()      # what the step function asks for the same step
+    plans = []
+    for portion, decoding in ((600, ("far",)), (600, ("far", "deep")), (600, ("far", "deep"))):
+        entries = [StepEntry("new", tokens["new"][at["new"] : at["new"] + portion], [portion - 1])]
+        wanted, starts = [plain["new"][at["new"] + portion - 1]], [at["new"]]
+        at["new"] += portion
+        for name in decoding:
+            entries.append(StepEntry(name, tokens[name][at[name] : at[name] + 1], [0]))
+            wanted.append(plain[name][at[name]])
+            starts.append(at[name])
+            at[name] += 1
+        got = runner.step(entries).float().cpu()
+        torch.testing.assert_close(got, torch.stack(wanted), **tolerance)
+        plan = planner.plan(StepShape([len(entry.tokens) for entry in entries], starts, False, page_size=16))
+        plans.append((plan["splits"], plan["decode_splits"]))
+    assert plans == [(1, 10), (1, 6), (1, 6)]
+    runner.check_fault()
+
+
 def test_a_window_on_one_layer_with_heads_of_128(tmp_path):
     """Two layers with heads of 128, the second with a window of 200 keys: the tcgen05 kernels mask
     the window's edge, the windowed group gives pages back as the window passes them."""
