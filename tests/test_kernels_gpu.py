@@ -415,6 +415,29 @@ def test_gemm_bf16_every_block_of_the_inner_range_counts(t, n, k_, swiglu, split
     torch.testing.assert_close(out.float(), want, rtol=6e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("t,n,k_,swiglu", [(300, 520, 1000, False), (1024, 4096, 4096, False), (1100, 1536, 2048, True),
+                                           (2048, 512, 12288, False)])
+def test_gemm_bf16_pair_every_block_of_the_inner_range_counts(t, n, k_, swiglu):
+    """The same for the kernel on pairs of CTAs: row ``r`` of the input lives in block ``r mod blocks`` alone, so a
+    k-block that a pair skips, reads twice or sums twice where the runs of two pairs meet inside a tile (the left-over
+    tiles' k-ranges are shared) changes whole rows by their full size."""
+    blocks = -(-k_ // 64)
+    x = rand((t, k_), torch.bfloat16, seed=44)
+    keep = torch.zeros((t, k_), dtype=torch.bool)
+    rows = torch.arange(t)
+    for block in range(blocks):
+        keep[rows[rows % blocks == block], block * 64 : (block + 1) * 64] = True
+    x = torch.where(keep, x, torch.zeros_like(x)).to(DEV)
+    w = device_rand(((2 if swiglu else 1) * n, k_), 0.3, seed=45)
+    out = torch.full((t, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    fault = fault_word()
+    k().gemm_bf16_pair(x, w, out, fault, swiglu=swiglu)
+    assert fault.item() == 0
+    want = bf16_product(x, w, n, swiglu)
+    assert float(want.abs().mean()) > (0.05 if swiglu else 0.5)          # a lost block is far outside the bound
+    torch.testing.assert_close(out.float(), want, rtol=6e-3, atol=2e-3 * max(1.0, float(want.abs().max()) / 8))
+
+
 def test_gemm_bf16_rows_do_not_depend_on_the_batch_beyond_rounding():
     x = rand((40, 512), torch.bfloat16, seed=24).to(DEV)
     w = rand((300, 512), torch.bfloat16, scale=0.05, seed=25).to(DEV)
